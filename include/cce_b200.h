@@ -1,0 +1,142 @@
+/*
+ * cce_b200 — C ABI of the B200 (sm_100a) Cut Cross-Entropy kernels.
+ *
+ * The reference (apple/ml-cross-entropy) has no FFI: its Python autograd
+ * function calls three Triton launchers.  Each entry point below replaces one
+ * of those launchers and is what a binding for this path would call:
+ *
+ *   cce_b200_lse_forward      <- cut_cross_entropy/cce_lse_forward.py:163-237
+ *                                (cce_lse_forward_kernel)
+ *   cce_b200_indexed_neg_dot  <- cut_cross_entropy/indexed_dot.py:102-158
+ *                                (indexed_neg_dot_forward_kernel)
+ *   cce_b200_backward         <- cut_cross_entropy/cce_backward.py:346-521
+ *                                (cce_backward_kernel)
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless stated otherwise; the library
+ *     never allocates or frees device memory: outputs and workspace belong to
+ *     the caller (query the *_workspace_bytes functions first);
+ *   - `stream` is a cudaStream_t passed as void*; all work is enqueued on it
+ *     and the call returns without synchronising;
+ *   - return value 0 = success, negative = error (see cce_b200_strerror).
+ *     Nothing throws, traps or aborts;
+ *   - the first 4 bytes of every workspace are a device status word that the
+ *     kernels set to a non-zero code if a bounded wait inside a kernel gave
+ *     up.  cce_b200_read_status copies it to the host (synchronises).
+ */
+#ifndef CCE_B200_H_
+#define CCE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types of e / c (and of the gradient outputs) */
+enum { CCE_DT_F16 = 0, CCE_DT_BF16 = 1, CCE_DT_F32 = 2 };
+/* index types of `valids` */
+enum { CCE_IDX_I32 = 0, CCE_IDX_I64 = 1 };
+
+/* error codes */
+enum {
+    CCE_OK = 0,
+    CCE_ERR_ARG = -1,        /* null pointer, negative size, unsupported dtype */
+    CCE_ERR_ALIGN = -2,      /* a pointer or stride is not aligned as documented */
+    CCE_ERR_WORKSPACE = -3,  /* workspace too small */
+    CCE_ERR_CUDA = -4,       /* a CUDA runtime/driver call failed (see cce_b200_last_cuda_error) */
+    CCE_ERR_DEVICE = -5,     /* not an sm_100 device */
+    CCE_ERR_KERNEL_WAIT = -6 /* status word non-zero: a kernel abandoned a bounded wait */
+};
+
+/* Shape and operand description shared by the three entry points.
+ * Rows of `e` that take part are listed by `valids` (n_rows entries, indices
+ * into the flat [n_total, D] matrix); valids == NULL means rows 0..n_rows-1. */
+typedef struct cce_b200_operands {
+    const void* e;        /* [n_total, D], row stride lde elements, unit column stride */
+    const void* c;        /* [V, D], row stride ldc elements, unit column stride */
+    const void* bias;     /* [V] or NULL */
+    const void* valids;   /* [n_rows] int32/int64 or NULL */
+    int64_t n_total;      /* rows of e (and entries of targets) */
+    int64_t n_rows;       /* rows that enter the loss ("B" in the reference) */
+    int64_t V;            /* classifier rows held by this rank */
+    int64_t D;            /* hidden size */
+    int64_t lde, ldc;     /* row strides in elements */
+    int32_t dtype;        /* CCE_DT_F16 or CCE_DT_BF16: type of e and c */
+    int32_t bias_dtype;   /* CCE_DT_* of bias */
+    int32_t valids_dtype; /* CCE_IDX_* */
+    int32_t has_softcap;  /* 0/1 */
+    float softcap;
+} cce_b200_operands;
+
+/* lse[i] = log sum_v exp(softcap(e[row_i] . c[v] + bias[v])), i < n_rows.
+ * Replaces cce_lse_forward_kernel (cut_cross_entropy/cce_lse_forward.py:163). */
+size_t cce_b200_lse_workspace_bytes(const cce_b200_operands* op);
+int cce_b200_lse_forward(const cce_b200_operands* op, float* lse /* [n_rows] */,
+                         void* workspace, size_t workspace_bytes, void* stream);
+
+/* out[i] = -softcap(e[row_i] . c[t] + bias[t]), t = targets[row_i + shift] - vocab_start;
+ * rows whose t falls outside [0, V) get 0 (vocab-parallel ranks that do not
+ * own the target).  No workspace.
+ * Replaces indexed_neg_dot_forward_kernel (cut_cross_entropy/indexed_dot.py:102). */
+int cce_b200_indexed_neg_dot(const cce_b200_operands* op, const int64_t* targets /* [n_total] */,
+                             int64_t shift, int64_t vocab_start, float* out /* [n_rows] */,
+                             void* stream);
+
+typedef struct cce_b200_backward_args {
+    cce_b200_operands op;
+    const float* lse;        /* [n_rows] full (all-rank) log-sum-exp */
+    const int64_t* targets;  /* [n_total]; entry row_i + shift is the label of row_i */
+    int64_t shift;
+    int64_t vocab_start;     /* first vocabulary index held by this rank (0 without vocab parallelism) */
+    const float* d_out;      /* upstream gradient of the loss: 1 element, or [n_total] indexed at row_i + shift */
+    int64_t d_out_numel;     /* 1 or n_total */
+    const float* d_lse;      /* upstream gradient of the returned lse, [n_total] indexed at row_i + shift, or NULL */
+    float grad_scale;        /* 1/n_rows for reduction=mean, else 1 */
+    int32_t has_filter;      /* 0: exact gradient; 1: skip tiles whose |softmax - onehot| < filter_eps everywhere */
+    float filter_eps;
+    int32_t filter_e;        /* apply the filter to the dE product */
+    int32_t filter_c;        /* apply the filter to the dC product */
+    void* d_e;               /* [n_total, D], row stride D, or NULL; fully written (zeros at rows not in valids) */
+    int32_t d_e_f32;         /* element type of d_e: 0 = op.dtype, 1 = fp32 (for a caller that reduces dE across ranks in fp32) */
+    void* d_c;               /* [V, D] in op.dtype, row stride D, or NULL */
+    float* d_bias;           /* [V] fp32 or NULL */
+} cce_b200_backward_args;
+
+/* Gradient of sum_i d_out_i * grad_scale * (lse_i - logit_i[t_i]) + sum_i d_lse_i * lse_i
+ * with respect to e, c and bias.  Accumulation is fp32 throughout.
+ * Replaces cce_backward_kernel (cut_cross_entropy/cce_backward.py:346). */
+size_t cce_b200_backward_workspace_bytes(const cce_b200_backward_args* a);
+int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t workspace_bytes,
+                      void* stream);
+
+/* Plain tensor-core GEMM through the same TMA/tcgen05 pipeline, exported so
+ * the pipeline can be tested in isolation:  out[M,N] (+)= A * B^T-like product
+ * over K.  a_mn / b_mn select the memory order of the operands:
+ *   a_mn = 0: A is [M, K] row-major (lda);  a_mn = 1: A is [K, M] row-major.
+ *   b_mn = 0: B is [N, K] row-major (ldb);  b_mn = 1: B is [K, N] row-major.
+ * out is fp32 (out_dtype = CCE_DT_F32) or the input type; `accumulate` adds to
+ * an fp32 out.  kflags (optional, bytes [ceil(M/128)][ceil(K/64)]) marks the
+ * 64-wide K blocks that take part for each 128-row block of the output.
+ * The first 4 bytes of `status` receive the kernel status word (may be NULL). */
+int cce_b200_gemm(const void* A, const void* B, void* out, int64_t M, int64_t N, int64_t K,
+                  int64_t lda, int64_t ldb, int64_t ldo, int32_t dtype, int32_t out_dtype,
+                  int32_t a_mn, int32_t b_mn, int32_t accumulate, const uint8_t* kflags,
+                  int32_t* status, void* stream);
+
+/* Synchronises `stream` and returns CCE_OK or CCE_ERR_KERNEL_WAIT; the raw word goes to *word. */
+int cce_b200_read_status(const void* workspace, void* stream, int32_t* word /* host, may be NULL */);
+
+/* Counters since library load (host side): kernels launched by this library. */
+int64_t cce_b200_launch_count(void);
+
+const char* cce_b200_strerror(int code);
+/* cudaError_t / CUresult of the most recent CCE_ERR_CUDA on this thread. */
+int cce_b200_last_cuda_error(void);
+int cce_b200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CCE_B200_H_ */

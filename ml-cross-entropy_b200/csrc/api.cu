@@ -1,0 +1,619 @@
+// Host side of the C ABI declared in include/cce_b200.h: argument checks, workspace
+// planning, TMA descriptor encoding and kernel launches.  No device allocation happens here.
+#include "../../include/cce_b200.h"
+
+#include <atomic>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+
+#include "engine.cuh"
+#include "small_kernels.cuh"
+
+using namespace cce;
+
+namespace {
+
+thread_local int g_last_cuda = 0;
+std::atomic<long long> g_launches{0};
+
+#define CCE_CUDA(expr)                                   \
+    do {                                                 \
+        cudaError_t e__ = (expr);                        \
+        if (e__ != cudaSuccess) {                        \
+            g_last_cuda = int(e__);                      \
+            return CCE_ERR_CUDA;                         \
+        }                                                \
+    } while (0)
+
+#define CCE_LAUNCH_CHECK()                               \
+    do {                                                 \
+        g_launches.fetch_add(1);                         \
+        cudaError_t e__ = cudaGetLastError();            \
+        if (e__ != cudaSuccess) {                        \
+            g_last_cuda = int(e__);                      \
+            return CCE_ERR_CUDA;                         \
+        }                                                \
+    } while (0)
+
+inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+inline long long cdiv(long long a, long long b) { return (a + b - 1) / b; }
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+struct DeviceInfo {
+    int sms = 0;
+    int cc_major = 0;
+    bool attr_set = false;
+};
+
+// Per-device facts, looked up once per device (immutable afterwards).
+int device_info(DeviceInfo** out) {
+    static DeviceInfo info[64];
+    static std::mutex mu;
+    int dev = 0;
+    CCE_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return CCE_ERR_DEVICE;
+    std::lock_guard<std::mutex> lock(mu);
+    DeviceInfo& d = info[dev];
+    if (d.sms == 0) {
+        CCE_CUDA(cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev));
+        CCE_CUDA(cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev));
+    }
+    if (d.cc_major != 10) return CCE_ERR_DEVICE;
+    if (!d.attr_set) {
+        CCE_CUDA(cudaFuncSetAttribute(engine_kernel<MODE_LSE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      ENGINE_SMEM));
+        CCE_CUDA(cudaFuncSetAttribute(engine_kernel<MODE_PGRAD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      ENGINE_SMEM));
+        CCE_CUDA(cudaFuncSetAttribute(engine_kernel<MODE_GEMM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      ENGINE_SMEM));
+        d.attr_set = true;
+    }
+    *out = &d;
+    return CCE_OK;
+}
+
+// 2-D tensor map over a row-major 16-bit matrix: `inner` contiguous elements per row,
+// `outer` rows, `pitch` elements between rows; box = box_inner x box_outer, 128-byte swizzle.
+int make_tmap(CUtensorMap* m, const void* base, int dtype, long long inner, long long outer, long long pitch,
+              int box_inner, int box_outer) {
+    EncodeTiledFn enc = get_encode();
+    if (!enc) {
+        g_last_cuda = -1;
+        return CCE_ERR_CUDA;
+    }
+    if ((reinterpret_cast<uintptr_t>(base) & 15) || (pitch * 2) % 16) return CCE_ERR_ALIGN;
+    cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+    cuuint64_t strides[1] = {(cuuint64_t)pitch * 2};
+    cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(m, dtype == CCE_DT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                     2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        g_last_cuda = int(r);
+        return CCE_ERR_CUDA;
+    }
+    return CCE_OK;
+}
+
+int check_operands(const cce_b200_operands* op) {
+    if (!op || !op->e || !op->c) return CCE_ERR_ARG;
+    if (op->n_total < 0 || op->n_rows < 0 || op->V <= 0 || op->D <= 0) return CCE_ERR_ARG;
+    if (op->n_rows > op->n_total) return CCE_ERR_ARG;
+    if (!op->valids && op->n_rows != op->n_total) return CCE_ERR_ARG;
+    if (op->dtype != CCE_DT_F16 && op->dtype != CCE_DT_BF16) return CCE_ERR_ARG;
+    if (op->bias && (op->bias_dtype < 0 || op->bias_dtype > 2)) return CCE_ERR_ARG;
+    if (op->valids && op->valids_dtype != CCE_IDX_I32 && op->valids_dtype != CCE_IDX_I64) return CCE_ERR_ARG;
+    if (op->lde < op->D || op->ldc < op->D) return CCE_ERR_ARG;
+    if (op->n_total >= (1LL << 31) - 256 || op->V >= (1LL << 31) - 256 || op->D >= (1LL << 30)) return CCE_ERR_ARG;
+    if (op->has_softcap && !(op->softcap > 0.0f)) return CCE_ERR_ARG;
+    return CCE_OK;
+}
+
+// Where the operands the tensor-core kernels read come from: the caller's buffers when TMA
+// can address them, else packed/padded copies in the workspace.
+struct OperandPlan {
+    bool pack_e, pad_c, bias32;
+    long long Dp;  // row length (elements) of the copies, multiple of 8
+    size_t off_e, off_c, off_bias, end;
+};
+
+OperandPlan plan_operands(const cce_b200_operands* op, size_t start) {
+    OperandPlan pl;
+    pl.Dp = (op->D + 7) / 8 * 8;
+    const bool d_ok = (op->D % 8 == 0);
+    pl.pack_e = op->valids || !d_ok || (op->lde % 8) || (reinterpret_cast<uintptr_t>(op->e) & 15);
+    pl.pad_c = !d_ok || (op->ldc % 8) || (reinterpret_cast<uintptr_t>(op->c) & 15);
+    pl.bias32 = op->bias && op->bias_dtype != CCE_DT_F32;
+    size_t off = align_up(start, 256);
+    pl.off_e = off;
+    if (pl.pack_e) off = align_up(off + (size_t)op->n_rows * pl.Dp * 2, 256);
+    pl.off_c = off;
+    if (pl.pad_c) off = align_up(off + (size_t)op->V * pl.Dp * 2, 256);
+    pl.off_bias = off;
+    if (pl.bias32) off = align_up(off + (size_t)op->V * 4, 256);
+    pl.end = off;
+    return pl;
+}
+
+struct Staged {
+    const void* e;
+    long long lde;
+    const void* c;
+    long long ldc;
+    const float* bias;
+    long long Dk;  // reduction extent visible to TMA (D, or the padded length of the copies)
+};
+
+int stage_operands(const cce_b200_operands* op, const OperandPlan& pl, char* ws, cudaStream_t st, Staged* out) {
+    out->Dk = op->D;
+    if (pl.pack_e) {
+        if (op->n_rows > 0) {
+            pack_rows_kernel<<<(unsigned)op->n_rows, 128, 0, st>>>(
+                reinterpret_cast<const uint16_t*>(op->e), op->lde, op->valids, op->valids_dtype == CCE_IDX_I64,
+                reinterpret_cast<uint16_t*>(ws + pl.off_e), pl.Dp, op->D, op->n_rows);
+            CCE_LAUNCH_CHECK();
+        }
+        out->e = ws + pl.off_e;
+        out->lde = pl.Dp;
+    } else {
+        out->e = op->e;
+        out->lde = op->lde;
+    }
+    if (pl.pad_c) {
+        pack_rows_kernel<<<(unsigned)op->V, 128, 0, st>>>(reinterpret_cast<const uint16_t*>(op->c), op->ldc, nullptr, 0,
+                                                         reinterpret_cast<uint16_t*>(ws + pl.off_c), pl.Dp, op->D,
+                                                         op->V);
+        CCE_LAUNCH_CHECK();
+        out->c = ws + pl.off_c;
+        out->ldc = pl.Dp;
+    } else {
+        out->c = op->c;
+        out->ldc = op->ldc;
+    }
+    if (pl.bias32) {
+        to_f32_kernel<<<(unsigned)cdiv(op->V, 256), 256, 0, st>>>(op->bias, op->bias_dtype,
+                                                                 reinterpret_cast<float*>(ws + pl.off_bias), op->V);
+        CCE_LAUNCH_CHECK();
+        out->bias = reinterpret_cast<const float*>(ws + pl.off_bias);
+    } else {
+        out->bias = reinterpret_cast<const float*>(op->bias);
+    }
+    return CCE_OK;
+}
+
+int lse_band_len(long long n_rb, long long n_vt, int sms) {
+    const long long want_items = (long long)sms * 8;
+    const long long n_band_target = cdiv(want_items, n_rb > 0 ? n_rb : 1);
+    long long len = n_vt / (n_band_target > 0 ? n_band_target : 1);
+    if (len < 1) len = 1;
+    if (len > 16) len = 16;
+    return int(len);
+}
+
+constexpr size_t kStatusBytes = 256;
+constexpr int kSmsForPlanning = 148;  // workspace sizes must not depend on the device queried later
+
+struct LsePlan {
+    OperandPlan ops;
+    int band_len, n_band;
+    size_t off_partial, total;
+};
+
+LsePlan plan_lse(const cce_b200_operands* op) {
+    LsePlan pl;
+    pl.ops = plan_operands(op, kStatusBytes);
+    const long long n_rb = cdiv(op->n_rows, BM), n_vt = cdiv(op->V, BN);
+    pl.band_len = lse_band_len(n_rb, n_vt, kSmsForPlanning);
+    pl.n_band = int(cdiv(n_vt, pl.band_len));
+    pl.off_partial = pl.ops.end;
+    pl.total = align_up(pl.off_partial + (size_t)pl.n_band * op->n_rows * sizeof(float2), 256);
+    return pl;
+}
+
+template <int MODE>
+int launch_engine(const CUtensorMap& a, const CUtensorMap& b, const EngineParams& p, int sms, cudaStream_t st) {
+    long long items;
+    if (MODE == MODE_LSE)
+        items = cdiv(p.n_nblk, p.band_len) * p.n_mblk;
+    else
+        items = (long long)p.n_mblk * p.n_nblk;
+    if (items <= 0) return CCE_OK;
+    const unsigned grid = (unsigned)(items < sms ? items : sms);
+    engine_kernel<MODE><<<grid, ENGINE_THREADS, ENGINE_SMEM, st>>>(a, b, p);
+    CCE_LAUNCH_CHECK();
+    return CCE_OK;
+}
+
+void base_params(EngineParams* p, long long M, long long N, long long K, int fmt, int a_mn, int b_mn, int* status) {
+    memset(p, 0, sizeof(*p));
+    p->M = int(M);
+    p->N = int(N);
+    p->K = int(K);
+    p->n_mblk = int(cdiv(M, BM));
+    p->n_nblk = int(cdiv(N, BN));
+    p->n_kblk = int(cdiv(K, BK));
+    p->a_mn_major = a_mn;
+    p->b_mn_major = b_mn;
+    p->idesc = make_idesc(fmt == CCE_DT_BF16 ? 1u : 0u, a_mn, b_mn, BM, BN);
+    p->status = status;
+    p->filter_eps = -1.0f;
+    p->band_len = 1;
+}
+
+// ---- backward planning
+struct BwdPlan {
+    OperandPlan ops;
+    long long Vc;  // vocabulary columns per chunk (multiple of 256)
+    int n_chunk;
+    int ld_flag_e, ld_flag_c;
+    size_t off_g, off_flag_e, off_flag_c, off_de32, total;
+    size_t flag_bytes;  // flag_e and flag_c are adjacent: one memset clears both
+};
+
+long long pick_chunk(long long n_rows, long long V, long long D) {
+    const long long v_round = cdiv(V, BN) * BN;
+    long long cap_bytes = 256LL << 20;
+    if (const char* env = getenv("CCE_B200_GBUF_MB")) {
+        long long mb = atoll(env);
+        if (mb >= 1) cap_bytes = mb << 20;
+    }
+    long long cap = cap_bytes / (2 * (n_rows > 0 ? n_rows : 1)) / BN * BN;
+    if (cap < BN) cap = BN;
+    if (cap >= v_round) return v_round;
+    // among widths within [cap/2, cap] prefer the one whose dC product fills whole waves of CTAs
+    const long long n_nblk = cdiv(D, BN);
+    long long best = cap;
+    double best_eff = -1.0;
+    for (long long w = cap; w >= BN && w * 2 >= cap; w -= BN) {
+        const long long tiles = (w / BM) * n_nblk;
+        const double eff = double(tiles) / double(cdiv(tiles, kSmsForPlanning) * kSmsForPlanning);
+        if (eff > best_eff + 1e-9) {
+            best_eff = eff;
+            best = w;
+        }
+    }
+    return best;
+}
+
+BwdPlan plan_bwd(const cce_b200_backward_args* a) {
+    const cce_b200_operands* op = &a->op;
+    BwdPlan pl;
+    pl.ops = plan_operands(op, kStatusBytes);
+    pl.Vc = pick_chunk(op->n_rows, op->V, op->D);
+    pl.n_chunk = int(cdiv(op->V, pl.Vc));
+    const long long n_rb = cdiv(op->n_rows, BM);
+    pl.ld_flag_e = int(pl.Vc / 64);
+    pl.ld_flag_c = int(align_up((size_t)cdiv(op->n_rows, 64) + 1, 16));
+    size_t off = pl.ops.end;
+    pl.off_g = off;
+    off = align_up(off + (size_t)(n_rb * BM) * pl.Vc * 2, 256);
+    pl.off_flag_e = off;
+    off = align_up(off + (size_t)n_rb * pl.ld_flag_e, 256);
+    pl.off_flag_c = off;
+    off = align_up(off + (size_t)(pl.Vc / 128) * pl.ld_flag_c, 256);
+    pl.flag_bytes = off - pl.off_flag_e;
+    pl.off_de32 = off;
+    if (a->d_e) off = align_up(off + (size_t)op->n_rows * op->D * 4, 256);
+    pl.total = off;
+    return pl;
+}
+
+}  // namespace
+
+extern "C" {
+
+int cce_b200_version(void) { return 1; }
+int cce_b200_last_cuda_error(void) { return g_last_cuda; }
+int64_t cce_b200_launch_count(void) { return (int64_t)g_launches.load(); }
+
+const char* cce_b200_strerror(int code) {
+    switch (code) {
+        case CCE_OK: return "ok";
+        case CCE_ERR_ARG: return "invalid argument (null pointer, bad size or unsupported dtype)";
+        case CCE_ERR_ALIGN: return "pointer or stride not aligned as required";
+        case CCE_ERR_WORKSPACE: return "workspace too small";
+        case CCE_ERR_CUDA: return "CUDA call failed (see cce_b200_last_cuda_error)";
+        case CCE_ERR_DEVICE: return "device is not sm_100";
+        case CCE_ERR_KERNEL_WAIT: return "a kernel abandoned a bounded wait (status word non-zero)";
+        default: return "unknown error";
+    }
+}
+
+int cce_b200_read_status(const void* workspace, void* stream, int32_t* word) {
+    if (!workspace) return CCE_ERR_ARG;
+    int32_t w = 0;
+    CCE_CUDA(cudaMemcpyAsync(&w, workspace, sizeof(w), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    CCE_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    if (word) *word = w;
+    return w == 0 ? CCE_OK : CCE_ERR_KERNEL_WAIT;
+}
+
+size_t cce_b200_lse_workspace_bytes(const cce_b200_operands* op) {
+    if (check_operands(op) != CCE_OK) return 0;
+    return plan_lse(op).total;
+}
+
+int cce_b200_lse_forward(const cce_b200_operands* op, float* lse, void* workspace, size_t workspace_bytes,
+                         void* stream) {
+    int rc = check_operands(op);
+    if (rc != CCE_OK) return rc;
+    if (!workspace || (op->n_rows > 0 && !lse)) return CCE_ERR_ARG;
+    if (reinterpret_cast<uintptr_t>(workspace) & 255) return CCE_ERR_ALIGN;
+    const LsePlan pl = plan_lse(op);
+    if (workspace_bytes < pl.total) return CCE_ERR_WORKSPACE;
+    DeviceInfo* dev = nullptr;
+    rc = device_info(&dev);
+    if (rc != CCE_OK) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    char* ws = reinterpret_cast<char*>(workspace);
+    CCE_CUDA(cudaMemsetAsync(ws, 0, kStatusBytes, st));
+    if (op->n_rows == 0) return CCE_OK;
+
+    Staged sg;
+    rc = stage_operands(op, pl.ops, ws, st, &sg);
+    if (rc != CCE_OK) return rc;
+
+    CUtensorMap tmA, tmB;
+    rc = make_tmap(&tmA, sg.e, op->dtype, sg.Dk, op->n_rows, sg.lde, BK, BM);
+    if (rc != CCE_OK) return rc;
+    rc = make_tmap(&tmB, sg.c, op->dtype, sg.Dk, op->V, sg.ldc, BK, BN);
+    if (rc != CCE_OK) return rc;
+
+    EngineParams p;
+    base_params(&p, op->n_rows, op->V, sg.Dk, op->dtype, 0, 0, reinterpret_cast<int*>(ws));
+    p.bias = sg.bias;
+    p.has_softcap = op->has_softcap;
+    p.softcap = op->softcap;
+    p.band_len = pl.band_len;
+    p.partial = reinterpret_cast<float2*>(ws + pl.off_partial);
+    rc = launch_engine<MODE_LSE>(tmA, tmB, p, dev->sms, st);
+    if (rc != CCE_OK) return rc;
+
+    lse_combine_kernel<<<(unsigned)cdiv(op->n_rows, 256), 256, 0, st>>>(p.partial, pl.n_band, op->n_rows, lse);
+    CCE_LAUNCH_CHECK();
+    return CCE_OK;
+}
+
+int cce_b200_indexed_neg_dot(const cce_b200_operands* op, const int64_t* targets, int64_t shift,
+                             int64_t vocab_start, float* out, void* stream) {
+    int rc = check_operands(op);
+    if (rc != CCE_OK) return rc;
+    if (!targets || (op->n_rows > 0 && !out) || shift < 0) return CCE_ERR_ARG;
+    if (op->n_rows == 0) return CCE_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    const unsigned blocks = (unsigned)cdiv(op->n_rows, 8);  // 8 warps per block
+    if (op->dtype == CCE_DT_BF16) {
+        indexed_neg_dot_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(
+            reinterpret_cast<const __nv_bfloat16*>(op->e), op->lde, reinterpret_cast<const __nv_bfloat16*>(op->c),
+            op->ldc, op->bias, op->bias_dtype, op->valids, op->valids_dtype == CCE_IDX_I64,
+            reinterpret_cast<const long long*>(targets), shift, vocab_start, op->V, op->D, op->n_rows,
+            op->has_softcap, op->softcap, out);
+    } else {
+        indexed_neg_dot_kernel<__half><<<blocks, 256, 0, st>>>(
+            reinterpret_cast<const __half*>(op->e), op->lde, reinterpret_cast<const __half*>(op->c), op->ldc,
+            op->bias, op->bias_dtype, op->valids, op->valids_dtype == CCE_IDX_I64,
+            reinterpret_cast<const long long*>(targets), shift, vocab_start, op->V, op->D, op->n_rows,
+            op->has_softcap, op->softcap, out);
+    }
+    CCE_LAUNCH_CHECK();
+    return CCE_OK;
+}
+
+size_t cce_b200_backward_workspace_bytes(const cce_b200_backward_args* a) {
+    if (!a || check_operands(&a->op) != CCE_OK) return 0;
+    return plan_bwd(a).total;
+}
+
+int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t workspace_bytes, void* stream) {
+    if (!a) return CCE_ERR_ARG;
+    const cce_b200_operands* op = &a->op;
+    int rc = check_operands(op);
+    if (rc != CCE_OK) return rc;
+    if (!workspace || !a->targets || !a->d_out || a->shift < 0) return CCE_ERR_ARG;
+    if (op->n_rows > 0 && !a->lse) return CCE_ERR_ARG;
+    if (a->d_out_numel != 1 && a->d_out_numel != op->n_total) return CCE_ERR_ARG;
+    if (a->d_bias && !op->bias) return CCE_ERR_ARG;
+    if (a->has_filter && !(a->filter_eps >= 0.0f)) return CCE_ERR_ARG;
+    if (reinterpret_cast<uintptr_t>(workspace) & 255) return CCE_ERR_ALIGN;
+    const BwdPlan pl = plan_bwd(a);
+    if (workspace_bytes < pl.total) return CCE_ERR_WORKSPACE;
+    DeviceInfo* dev = nullptr;
+    rc = device_info(&dev);
+    if (rc != CCE_OK) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    char* ws = reinterpret_cast<char*>(workspace);
+    const long long D = op->D, V = op->V, B = op->n_rows;
+    const size_t esz = 2;
+
+    CCE_CUDA(cudaMemsetAsync(ws, 0, kStatusBytes, st));
+    const size_t de_esz = a->d_e_f32 ? 4 : esz;
+    if (a->d_e && (op->valids || B == 0)) CCE_CUDA(cudaMemsetAsync(a->d_e, 0, (size_t)op->n_total * D * de_esz, st));
+    if (a->d_bias) CCE_CUDA(cudaMemsetAsync(a->d_bias, 0, (size_t)V * 4, st));
+    if (B == 0) {
+        if (a->d_c) CCE_CUDA(cudaMemsetAsync(a->d_c, 0, (size_t)V * D * esz, st));
+        return CCE_OK;
+    }
+
+    Staged sg;
+    rc = stage_operands(op, pl.ops, ws, st, &sg);
+    if (rc != CCE_OK) return rc;
+
+    const bool use_flags = a->has_filter && ((a->filter_e && a->d_e) || (a->filter_c && a->d_c));
+    int* status = reinterpret_cast<int*>(ws);
+    char* g_buf = ws + pl.off_g;
+    uint8_t* flag_e = reinterpret_cast<uint8_t*>(ws + pl.off_flag_e);
+    uint8_t* flag_c = reinterpret_cast<uint8_t*>(ws + pl.off_flag_c);
+    float* de32 = reinterpret_cast<float*>(ws + pl.off_de32);
+
+    // operand maps that do not change from chunk to chunk
+    CUtensorMap tmE_k, tmC_k, tmE_mn, tmC_mn;
+    rc = make_tmap(&tmE_k, sg.e, op->dtype, sg.Dk, B, sg.lde, BK, BM);
+    if (rc != CCE_OK) return rc;
+    rc = make_tmap(&tmC_k, sg.c, op->dtype, sg.Dk, V, sg.ldc, BK, BN);
+    if (rc != CCE_OK) return rc;
+    rc = make_tmap(&tmE_mn, sg.e, op->dtype, D, B, sg.lde, 64, BK);
+    if (rc != CCE_OK) return rc;
+    rc = make_tmap(&tmC_mn, sg.c, op->dtype, D, V, sg.ldc, 64, BK);
+    if (rc != CCE_OK) return rc;
+
+    for (int ch = 0; ch < pl.n_chunk; ++ch) {
+        const long long v0 = (long long)ch * pl.Vc;
+        const long long Vw = (V - v0 < pl.Vc) ? (V - v0) : pl.Vc;
+        if (use_flags) CCE_CUDA(cudaMemsetAsync(flag_e, 0, pl.flag_bytes, st));
+
+        // phase 1: G = dLoss/dLogits for columns [v0, v0 + Vw)
+        {
+            EngineParams p;
+            base_params(&p, B, Vw, sg.Dk, op->dtype, 0, 0, status);
+            p.b_mn_off = int(v0);
+            p.bias = sg.bias;
+            p.col_off = int(v0);
+            p.has_softcap = op->has_softcap;
+            p.softcap = op->softcap;
+            p.lse = a->lse;
+            p.targets = reinterpret_cast<const long long*>(a->targets);
+            p.valids = op->valids;
+            p.valids_i64 = op->valids_dtype == CCE_IDX_I64;
+            p.shift = a->shift;
+            p.vocab_start = a->vocab_start;
+            p.d_out = a->d_out;
+            p.d_out_scalar = a->d_out_numel == 1;
+            p.d_lse = a->d_lse;
+            p.grad_scale = a->grad_scale;
+            p.filter_eps = use_flags ? a->filter_eps : -1.0f;
+            p.g_out = g_buf;
+            p.ldg = pl.Vc;
+            p.g_is_bf16 = op->dtype == CCE_DT_BF16;
+            p.flag_e = flag_e;
+            p.ld_flag_e = pl.ld_flag_e;
+            p.flag_c = flag_c;
+            p.ld_flag_c = pl.ld_flag_c;
+            rc = launch_engine<MODE_PGRAD>(tmE_k, tmC_k, p, dev->sms, st);
+            if (rc != CCE_OK) return rc;
+        }
+
+        // phase 2: dC[v0 : v0 + Vw, :] = G^T E   (M = Vw, N = D, K = B; both operands MN-major)
+        if (a->d_c) {
+            CUtensorMap tmG_mn;
+            rc = make_tmap(&tmG_mn, g_buf, op->dtype, Vw, B, pl.Vc, 64, BK);
+            if (rc != CCE_OK) return rc;
+            EngineParams p;
+            base_params(&p, Vw, D, B, op->dtype, 1, 1, status);
+            p.out = reinterpret_cast<char*>(a->d_c) + (size_t)v0 * D * esz;
+            p.ldo = D;
+            p.out_dtype = op->dtype;
+            p.accumulate = 0;
+            if (a->has_filter && a->filter_c) {
+                p.kflags = flag_c;
+                p.ld_kflags = pl.ld_flag_c;
+            }
+            rc = launch_engine<MODE_GEMM>(tmG_mn, tmE_mn, p, dev->sms, st);
+            if (rc != CCE_OK) return rc;
+        }
+
+        // phase 3: dE += G C[v0 : v0 + Vw, :]    (M = B, N = D, K = Vw; A K-major, B MN-major)
+        if (a->d_e) {
+            CUtensorMap tmG_k;
+            rc = make_tmap(&tmG_k, g_buf, op->dtype, Vw, B, pl.Vc, BK, BM);
+            if (rc != CCE_OK) return rc;
+            EngineParams p;
+            base_params(&p, B, D, Vw, op->dtype, 0, 1, status);
+            p.b_k_off = int(v0);
+            p.out = de32;
+            p.ldo = D;
+            p.out_dtype = CCE_DT_F32;
+            p.accumulate = ch > 0;
+            if (a->has_filter && a->filter_e) {
+                p.kflags = flag_e;
+                p.ld_kflags = pl.ld_flag_e;
+            }
+            rc = launch_engine<MODE_GEMM>(tmG_k, tmC_mn, p, dev->sms, st);
+            if (rc != CCE_OK) return rc;
+        }
+
+        // bias gradient: column sums of G
+        if (a->d_bias) {
+            const int rows_per_block = 512;
+            dim3 grid((unsigned)cdiv(Vw, 256), (unsigned)cdiv(B, rows_per_block));
+            if (op->dtype == CCE_DT_BF16)
+                colsum_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(g_buf),
+                                                                   pl.Vc, B, int(Vw), rows_per_block,
+                                                                   a->d_bias + v0);
+            else
+                colsum_kernel<__half><<<grid, 128, 0, st>>>(reinterpret_cast<const __half*>(g_buf), pl.Vc, B,
+                                                            int(Vw), rows_per_block, a->d_bias + v0);
+            CCE_LAUNCH_CHECK();
+        }
+    }
+
+    if (a->d_e) {
+        if (a->d_e_f32)
+            scatter_cast_kernel<float><<<(unsigned)B, 128, 0, st>>>(
+                de32, D, op->valids, op->valids_dtype == CCE_IDX_I64, reinterpret_cast<float*>(a->d_e), D, D, B);
+        else if (op->dtype == CCE_DT_BF16)
+            scatter_cast_kernel<__nv_bfloat16><<<(unsigned)B, 128, 0, st>>>(
+                de32, D, op->valids, op->valids_dtype == CCE_IDX_I64, reinterpret_cast<__nv_bfloat16*>(a->d_e), D, D, B);
+        else
+            scatter_cast_kernel<__half><<<(unsigned)B, 128, 0, st>>>(
+                de32, D, op->valids, op->valids_dtype == CCE_IDX_I64, reinterpret_cast<__half*>(a->d_e), D, D, B);
+        CCE_LAUNCH_CHECK();
+    }
+    return CCE_OK;
+}
+
+int cce_b200_gemm(const void* A, const void* Bm, void* out, int64_t M, int64_t N, int64_t K, int64_t lda,
+                  int64_t ldb, int64_t ldo, int32_t dtype, int32_t out_dtype, int32_t a_mn, int32_t b_mn,
+                  int32_t accumulate, const uint8_t* kflags, int32_t* status, void* stream) {
+    if (!A || !Bm || !out || M <= 0 || N <= 0 || K <= 0) return CCE_ERR_ARG;
+    if (dtype != CCE_DT_F16 && dtype != CCE_DT_BF16) return CCE_ERR_ARG;
+    if (out_dtype != CCE_DT_F32 && out_dtype != dtype) return CCE_ERR_ARG;
+    if (accumulate && out_dtype != CCE_DT_F32) return CCE_ERR_ARG;
+    DeviceInfo* dev = nullptr;
+    int rc = device_info(&dev);
+    if (rc != CCE_OK) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    CUtensorMap tmA, tmB;
+    if (!a_mn)
+        rc = make_tmap(&tmA, A, dtype, K, M, lda, BK, BM);
+    else
+        rc = make_tmap(&tmA, A, dtype, M, K, lda, 64, BK);
+    if (rc != CCE_OK) return rc;
+    if (!b_mn)
+        rc = make_tmap(&tmB, Bm, dtype, K, N, ldb, BK, BN);
+    else
+        rc = make_tmap(&tmB, Bm, dtype, N, K, ldb, 64, BK);
+    if (rc != CCE_OK) return rc;
+    if (status) CCE_CUDA(cudaMemsetAsync(status, 0, 4, st));
+    EngineParams p;
+    base_params(&p, M, N, K, dtype, a_mn, b_mn, status);
+    p.out = out;
+    p.ldo = ldo;
+    p.out_dtype = out_dtype;
+    p.accumulate = accumulate;
+    p.kflags = kflags;
+    p.ld_kflags = int(cdiv(K, BK));
+    return launch_engine<MODE_GEMM>(tmA, tmB, p, dev->sms, st);
+}
+
+}  // extern "C"

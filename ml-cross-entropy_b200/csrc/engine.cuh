@@ -1,0 +1,561 @@
+// Persistent, warp-specialised TMA + tcgen05 contraction pipeline with three epilogues.
+//
+//   warp 0      : TMA producer  (global -> 128B-swizzled shared-memory ring)
+//   warp 1      : tcgen05.mma issuer, owns the TMEM allocation (2 accumulators of 128x256 fp32)
+//   warps 2..5  : epilogue; warp w reads TMEM lanes 32*(w%4)..+31, one output row per thread
+//
+// MODE_LSE   : S = E * C^T (+bias, softcap) -> running (max, sum-exp) per row over a band of
+//              vocabulary tiles -> partial[band][row]                 (forward log-sum-exp)
+// MODE_PGRAD : S recomputed -> G = dLoss/dS in bf16/fp16 -> G[row][col] plus per-block
+//              "has a value >= eps" flags                             (backward, phase 1)
+// MODE_GEMM  : out (+)= A * B over K with optional per-(row block, K block) skip flags
+//              (backward, phases 2 and 3: dC = G^T E, dE += G C)
+#pragma once
+#include "ptx.cuh"
+
+namespace cce {
+
+constexpr int BM = 128;  // rows of the A side per tile  (TMEM lanes)
+constexpr int BN = 256;  // rows of the B side per tile  (TMEM columns)
+constexpr int BK = 64;   // reduction elements per stage (one 128-byte swizzle row of 16-bit data)
+constexpr int UMMA_K = 16;
+constexpr int NSTAGE = 4;
+constexpr int A_BYTES = BM * BK * 2;
+constexpr int B_BYTES = BN * BK * 2;
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int ATOM_BYTES = 64 * 128;  // one MN-major swizzle atom column: 64 K rows x 128 bytes
+constexpr int ENGINE_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr int ENGINE_SMEM = NSTAGE * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+
+enum { MODE_LSE = 0, MODE_PGRAD = 1, MODE_GEMM = 2 };
+
+struct EngineParams {
+    // extents of this launch
+    int M;       // valid rows on the A side (TMEM lanes direction)
+    int N;       // valid rows on the B side (TMEM columns direction)
+    int K;       // reduction length
+    int n_mblk;  // ceil(M / 128)
+    int n_nblk;  // ceil(N / 256)
+    int n_kblk;  // ceil(K / 64)
+    // coordinate offsets added to the TMA coordinates of each operand
+    int a_mn_off, a_k_off, b_mn_off, b_k_off;
+    int a_mn_major, b_mn_major;  // 0: K contiguous in memory, 1: M/N contiguous in memory
+    uint32_t idesc;
+    int* status;
+
+    // ---- MODE_LSE / MODE_PGRAD
+    const float* bias;  // fp32 [>= col_off + N] or null
+    int col_off;        // first local vocabulary index of this launch (chunk start)
+    int has_softcap;
+    float softcap;
+    int band_len;       // vocabulary tiles per work item (MODE_LSE)
+    float2* partial;    // [n_band][M]  (running max in log2 units, sum)
+    // ---- MODE_PGRAD
+    const float* lse;          // [M]
+    const long long* targets;  // [n_total]
+    const void* valids;        // null, int32 or int64 [M]
+    int valids_i64;
+    long long shift;
+    long long vocab_start;
+    const float* d_out;  // 1 element or indexed at (row + shift)
+    int d_out_scalar;
+    const float* d_lse;  // null or indexed at (row + shift)
+    float grad_scale;
+    float filter_eps;  // < 0: no flags are produced
+    void* g_out;       // [M][ldg] 16-bit
+    long long ldg;
+    int g_is_bf16;
+    uint8_t* flag_e;  // [n_mblk][ld_flag_e]: (128-row block, 64-column block) has a value >= eps
+    int ld_flag_e;
+    uint8_t* flag_c;  // [N/128][ld_flag_c]:   (128-column block, 64-row block) has a value >= eps
+    int ld_flag_c;
+    // ---- MODE_GEMM
+    void* out;
+    long long ldo;
+    int out_dtype;   // CCE_DT_*
+    int accumulate;  // fp32 out only
+    const uint8_t* kflags;  // null or [n_mblk][ld_kflags]
+    int ld_kflags;
+};
+
+struct EngineSmem {
+    uint8_t* stages;
+    uint64_t* full;    // [NSTAGE] TMA -> MMA
+    uint64_t* empty;   // [NSTAGE] MMA -> TMA
+    uint64_t* tfull;   // [2] MMA -> epilogue
+    uint64_t* tempty;  // [2] epilogue -> MMA
+    uint64_t* tdown;   // [1] tear-down
+    uint32_t* tmem_base;
+    int* abort_flag;
+    int* acc_empty;  // [2] accumulator holds no product (all K blocks skipped)
+};
+
+template <int MODE>
+struct TileIter {
+    const EngineParams& p;
+    int item, n_items, sub, sub_end;
+    int mblk, nblk, band;
+    bool first, last;
+    __device__ TileIter(const EngineParams& p_) : p(p_) {
+        item = int(blockIdx.x) - int(gridDim.x);
+        sub = 0;
+        sub_end = 0;
+        if (MODE == MODE_LSE) {
+            const int n_band = (p.n_nblk + p.band_len - 1) / p.band_len;
+            n_items = n_band * p.n_mblk;
+        } else {
+            n_items = p.n_mblk * p.n_nblk;
+        }
+    }
+    __device__ bool next() {
+        if (MODE == MODE_LSE) {
+            if (sub + 1 < sub_end) {
+                ++sub;
+            } else {
+                item += gridDim.x;
+                if (item >= n_items) return false;
+                band = item / p.n_mblk;
+                mblk = item % p.n_mblk;
+                sub = band * p.band_len;
+                sub_end = min(p.n_nblk, sub + p.band_len);
+            }
+            nblk = sub;
+            first = (sub == band * p.band_len);
+            last = (sub + 1 == sub_end);
+            return true;
+        } else {
+            item += gridDim.x;
+            if (item >= n_items) return false;
+            if (MODE == MODE_PGRAD) {
+                nblk = item / p.n_mblk;  // concurrent CTAs share the classifier tile
+                mblk = item % p.n_mblk;
+            } else {
+                mblk = item / p.n_nblk;
+                nblk = item % p.n_nblk;
+            }
+            first = last = true;
+            band = 0;
+            return true;
+        }
+    }
+};
+
+// 32-wide activity mask of K blocks [kb0, kb0+32) for the current tile.
+__device__ __forceinline__ uint32_t kblock_mask(const EngineParams& p, int mblk, int kb0, int lane) {
+    const int kb = kb0 + lane;
+    bool act = kb < p.n_kblk;
+    if (act && p.kflags) act = p.kflags[(size_t)mblk * p.ld_kflags + kb] != 0;
+    return __ballot_sync(0xffffffffu, act);
+}
+
+template <int MODE>
+__device__ void producer_loop(const CUtensorMap* tmA, const CUtensorMap* tmB, const EngineParams& p,
+                              const EngineSmem& s) {
+    const int lane = threadIdx.x & 31;
+    int stage = 0;
+    uint32_t phase = 0;
+    TileIter<MODE> it(p);
+    while (it.next()) {
+        for (int kb0 = 0; kb0 < p.n_kblk; kb0 += 32) {
+            uint32_t mask = (MODE == MODE_GEMM) ? kblock_mask(p, it.mblk, kb0, lane)
+                                                : (p.n_kblk - kb0 >= 32 ? 0xffffffffu
+                                                                        : ((1u << (p.n_kblk - kb0)) - 1u));
+            while (mask) {
+                const int kb = kb0 + __ffs(mask) - 1;
+                mask &= mask - 1;
+                int ok = 1;
+                if (lane == 0) {
+                    ok = mbar_wait(smem_u32(&s.empty[stage]), phase ^ 1u, s.abort_flag, p.status,
+                                   ERR_WAIT_SMEM_EMPTY);
+                    if (ok) {
+                        const uint32_t bar = smem_u32(&s.full[stage]);
+                        const uint32_t sa = smem_u32(s.stages + stage * STAGE_BYTES);
+                        const uint32_t sb = sa + A_BYTES;
+                        mbar_expect_tx(bar, STAGE_BYTES);
+                        if (!p.a_mn_major) {
+                            tma_load_2d(sa, tmA, bar, p.a_k_off + kb * BK, p.a_mn_off + it.mblk * BM);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < BM / 64; ++j)
+                                tma_load_2d(sa + j * ATOM_BYTES, tmA, bar,
+                                            p.a_mn_off + it.mblk * BM + j * 64, p.a_k_off + kb * BK);
+                        }
+                        if (!p.b_mn_major) {
+                            tma_load_2d(sb, tmB, bar, p.b_k_off + kb * BK, p.b_mn_off + it.nblk * BN);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < BN / 64; ++j)
+                                tma_load_2d(sb + j * ATOM_BYTES, tmB, bar,
+                                            p.b_mn_off + it.nblk * BN + j * 64, p.b_k_off + kb * BK);
+                        }
+                    }
+                }
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) return;
+                if (++stage == NSTAGE) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
+    }
+}
+
+template <int MODE>
+__device__ void mma_loop(const EngineParams& p, const EngineSmem& s, uint32_t tmem_base) {
+    const int lane = threadIdx.x & 31;
+    int stage = 0;
+    uint32_t phase = 0;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    // descriptor constants
+    const uint32_t a_lbo = p.a_mn_major ? ATOM_BYTES : 16, b_lbo = p.b_mn_major ? ATOM_BYTES : 16;
+    const uint32_t a_kstep = p.a_mn_major ? (UMMA_K / 8) * 1024 : UMMA_K * 2;  // bytes per UMMA_K
+    const uint32_t b_kstep = p.b_mn_major ? (UMMA_K / 8) * 1024 : UMMA_K * 2;
+    TileIter<MODE> it(p);
+    while (it.next()) {
+        int ok = 1;
+        if (lane == 0) {
+            ok = mbar_wait(smem_u32(&s.tempty[acc]), acc_phase ^ 1u, s.abort_flag, p.status,
+                           ERR_WAIT_TMEM_EMPTY);
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) return;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        int n_issued = 0;
+        for (int kb0 = 0; kb0 < p.n_kblk; kb0 += 32) {
+            uint32_t mask = (MODE == MODE_GEMM) ? kblock_mask(p, it.mblk, kb0, lane)
+                                                : (p.n_kblk - kb0 >= 32 ? 0xffffffffu
+                                                                        : ((1u << (p.n_kblk - kb0)) - 1u));
+            while (mask) {
+                mask &= mask - 1;
+                if (lane == 0) {
+                    ok = mbar_wait(smem_u32(&s.full[stage]), phase, s.abort_flag, p.status,
+                                   ERR_WAIT_SMEM_FULL);
+                    if (ok) {
+                        tc_fence_after();
+                        const uint32_t sa = smem_u32(s.stages + stage * STAGE_BYTES);
+                        const uint32_t sb = sa + A_BYTES;
+#pragma unroll
+                        for (int k = 0; k < BK / UMMA_K; ++k) {
+                            const uint64_t ad = make_smem_desc(sa + k * a_kstep, a_lbo, 1024);
+                            const uint64_t bd = make_smem_desc(sb + k * b_kstep, b_lbo, 1024);
+                            tc_mma_f16(d_tmem, ad, bd, p.idesc, (n_issued | k) ? 1u : 0u);
+                        }
+                        tc_commit(smem_u32(&s.empty[stage]));  // frees the stage once the MMAs have read it
+                    }
+                }
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) return;
+                ++n_issued;
+                if (++stage == NSTAGE) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
+        if (lane == 0) {
+            s.acc_empty[acc] = (n_issued == 0);
+            __threadfence_block();
+            if (n_issued)
+                tc_commit(smem_u32(&s.tfull[acc]));  // arrives when the accumulator is complete
+            else
+                mbar_arrive(smem_u32(&s.tfull[acc]));
+        }
+        __syncwarp();
+        if (++acc == 2) {
+            acc = 0;
+            acc_phase ^= 1u;
+        }
+    }
+}
+
+__device__ __forceinline__ float apply_softcap(float x, float softcap, float inv_softcap) {
+    return softcap * tanh_fast(x * inv_softcap);
+}
+
+__device__ __forceinline__ void store_g16(void* dst, const float (&v)[32], bool is_bf16) {
+    uint4 o[4];
+    uint32_t* w = reinterpret_cast<uint32_t*>(o);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        if (is_bf16) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+            w[j] = *reinterpret_cast<uint32_t*>(&h);
+        } else {
+            __half2 h = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
+            w[j] = *reinterpret_cast<uint32_t*>(&h);
+        }
+    }
+    uint4* d = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) d[j] = o[j];
+}
+
+template <int MODE>
+__device__ void epilogue_loop(const EngineParams& p, const EngineSmem& s, uint32_t tmem_base) {
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const float inv_softcap = p.has_softcap ? 1.0f / p.softcap : 0.0f;
+
+    // MODE_LSE running state (log2 units)
+    float run_m = -INFINITY, run_s = 0.0f;
+
+    TileIter<MODE> it(p);
+    while (it.next()) {
+        const int row = it.mblk * BM + q * 32 + lane;
+        const bool row_ok = row < p.M;
+
+        // per-row constants (loaded before the wait so the latency overlaps the MMAs)
+        float row_l2 = 0.0f, row_g = 0.0f, row_dl = 0.0f;
+        int row_t = -1;
+        if (MODE == MODE_PGRAD) {
+            if (row_ok) {
+                long long src = row;
+                if (p.valids)
+                    src = p.valids_i64 ? reinterpret_cast<const long long*>(p.valids)[row]
+                                       : (long long)reinterpret_cast<const int*>(p.valids)[row];
+                const long long ti = src + p.shift;
+                const long long t = p.targets[ti] - p.vocab_start;
+                row_t = (t >= 0 && t < 0x7fffffffLL) ? int(t) : -1;
+                row_l2 = p.lse[row] * kLog2e;
+                row_g = p.grad_scale * (p.d_out_scalar ? p.d_out[0] : p.d_out[ti]);
+                row_dl = p.d_lse ? p.d_lse[ti] : 0.0f;
+            }
+        }
+        if (MODE == MODE_LSE) {
+            if (it.first) {
+                run_m = -INFINITY;
+                run_s = 0.0f;
+            }
+        }
+
+        // every epilogue thread observes the barrier itself before touching TMEM
+        int ok = mbar_wait(smem_u32(&s.tfull[acc]), acc_phase, s.abort_flag, p.status,
+                           ERR_WAIT_TMEM_FULL);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) return;
+        tc_fence_after();
+        const bool acc_is_empty =
+            (MODE == MODE_GEMM) ? (reinterpret_cast<volatile int*>(s.acc_empty)[acc] != 0) : false;
+        const uint32_t taddr = tmem_base + acc * BN + (uint32_t(q * 32) << 16);
+
+        if (MODE == MODE_GEMM && acc_is_empty && p.accumulate) {
+            // nothing to add
+        } else {
+            uint32_t flag_bits = 0;  // MODE_PGRAD: activity of the current 64-column group
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                const int col0 = it.nblk * BN + c * 32;  // column within this launch
+                if (col0 >= p.N) break;                 // warp-uniform
+                uint32_t r[32];
+                if (!(MODE == MODE_GEMM && acc_is_empty)) {
+                    tmem_ld32(taddr + c * 32, r);
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) r[j] = 0u;
+                }
+                float x[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(r[j]);
+
+                if (MODE == MODE_LSE || MODE == MODE_PGRAD) {
+                    if (p.bias) {
+                        const float* bp = p.bias + p.col_off + col0;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col0 + j < p.N) x[j] += __ldg(bp + j);
+                    }
+                    if (p.has_softcap) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) x[j] = apply_softcap(x[j], p.softcap, inv_softcap);
+                    }
+                }
+
+                if (MODE == MODE_LSE) {
+                    float cmax = -INFINITY;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        x[j] = (col0 + j < p.N) ? x[j] * kLog2e : -INFINITY;
+                        cmax = fmaxf(cmax, x[j]);
+                    }
+                    if (cmax > run_m) {
+                        run_s *= ex2f(run_m - cmax);  // run_m = -inf gives 0
+                        run_m = cmax;
+                    }
+                    if (run_m > -INFINITY) {
+                        float acc_s = 0.0f;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) acc_s += ex2f(x[j] - run_m);
+                        run_s += acc_s;
+                    }
+                } else if (MODE == MODE_PGRAD) {
+                    const float gsum = row_g + row_dl;
+                    bool active = false;
+                    float g[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int col = p.col_off + col0 + j;  // local vocabulary index
+                        const bool in_range = (col0 + j < p.N);
+                        float prob = in_range ? ex2f(x[j] * kLog2e - row_l2) : 0.0f;
+                        const bool is_t = in_range && (col == row_t);
+                        const float d0 = prob - (is_t ? 1.0f : 0.0f);
+                        active |= (fabsf(d0) >= p.filter_eps);
+                        float d = d0 * gsum + (is_t ? row_dl : 0.0f);
+                        if (p.has_softcap) {
+                            const float tt = x[j] * inv_softcap;
+                            d *= (1.0f - tt * tt);
+                        }
+                        g[j] = row_ok ? d : 0.0f;
+                    }
+                    if (row_ok) {
+                        char* dst = reinterpret_cast<char*>(p.g_out) + ((size_t)row * p.ldg + col0) * 2;
+                        store_g16(dst, g, p.g_is_bf16 != 0);
+                    }
+                    if (p.filter_eps >= 0.0f) {
+                        flag_bits |= __ballot_sync(0xffffffffu, active && row_ok);
+                        if (c & 1) {
+                            if (flag_bits && lane == 0) {
+                                const int cb64 = it.nblk * (BN / 64) + (c >> 1);
+                                p.flag_e[(size_t)it.mblk * p.ld_flag_e + cb64] = 1;
+                                p.flag_c[(size_t)(cb64 >> 1) * p.ld_flag_c + it.mblk * 2 + (q >> 1)] = 1;
+                            }
+                            flag_bits = 0;
+                        }
+                    }
+                } else {  // MODE_GEMM
+                    if (row_ok) {
+                        const int ncol = min(32, p.N - col0);
+                        if (p.out_dtype == 2) {
+                            float* dst = reinterpret_cast<float*>(p.out) + (size_t)row * p.ldo + col0;
+                            const bool vec = (ncol == 32) && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
+                            if (vec) {
+                                float4* d4 = reinterpret_cast<float4*>(dst);
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) {
+                                    float4 v = make_float4(x[4 * j], x[4 * j + 1], x[4 * j + 2], x[4 * j + 3]);
+                                    if (p.accumulate) {
+                                        const float4 o = d4[j];
+                                        v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                                    }
+                                    d4[j] = v;
+                                }
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 32; ++j)
+                                    if (j < ncol) dst[j] = p.accumulate ? dst[j] + x[j] : x[j];
+                            }
+                        } else {
+                            char* dst = reinterpret_cast<char*>(p.out) + ((size_t)row * p.ldo + col0) * 2;
+                            const bool vec = (ncol == 32) && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
+                            if (vec) {
+                                store_g16(dst, x, p.out_dtype == 1);
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 32; ++j) {
+                                    if (j < ncol) {
+                                        if (p.out_dtype == 1)
+                                            reinterpret_cast<__nv_bfloat16*>(dst)[j] = __float2bfloat16_rn(x[j]);
+                                        else
+                                            reinterpret_cast<__half*>(dst)[j] = __float2half_rn(x[j]);
+                                    }
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+        }
+
+        // accumulator consumed: hand it back to the MMA warp
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&s.tempty[acc]));
+        if (++acc == 2) {
+            acc = 0;
+            acc_phase ^= 1u;
+        }
+
+        if (MODE == MODE_LSE) {
+            if (it.last && row_ok) p.partial[(size_t)it.band * p.M + row] = make_float2(run_m, run_s);
+        }
+    }
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(ENGINE_THREADS, 1)
+engine_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+              const EngineParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    EngineSmem s;
+    s.stages = base;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(base + NSTAGE * STAGE_BYTES);
+    s.full = bars;
+    s.empty = bars + NSTAGE;
+    s.tfull = bars + 2 * NSTAGE;
+    s.tempty = bars + 2 * NSTAGE + 2;
+    s.tdown = bars + 2 * NSTAGE + 4;
+    s.tmem_base = reinterpret_cast<uint32_t*>(bars + 2 * NSTAGE + 5);
+    s.abort_flag = reinterpret_cast<int*>(s.tmem_base + 1);
+    s.acc_empty = s.abort_flag + 1;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < NSTAGE; ++i) {
+            mbar_init(smem_u32(&s.full[i]), 1);
+            mbar_init(smem_u32(&s.empty[i]), 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(smem_u32(&s.tfull[i]), 1);
+            mbar_init(smem_u32(&s.tempty[i]), 4);  // one arrival per epilogue warp
+        }
+        mbar_init(smem_u32(s.tdown), 1);
+        *s.abort_flag = 0;
+        s.acc_empty[0] = 0;
+        s.acc_empty[1] = 0;
+        fence_barrier_init();
+        fence_proxy_async();
+        tma_prefetch_desc(&tmA);
+        tma_prefetch_desc(&tmB);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(s.tmem_base), TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(s.tmem_base);
+
+    if (warp == 0) {
+        producer_loop<MODE>(&tmA, &tmB, p, s);
+    } else if (warp == 1) {
+        mma_loop<MODE>(p, s, tmem_base);
+    } else {
+        epilogue_loop<MODE>(p, s, tmem_base);
+    }
+
+    // tear-down: wait (bounded) for every MMA this CTA issued, then release TMEM
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        if (lane == 0) {
+            tc_commit(smem_u32(s.tdown));
+            mbar_wait(smem_u32(s.tdown), 0, s.abort_flag, p.status, ERR_WAIT_TEARDOWN);
+        }
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+}  // namespace cce

@@ -1,0 +1,220 @@
+"""Autograd glue of the Cut Cross-Entropy loss on the B200 backend.
+
+Follows ``cut_cross_entropy/cce.py:26-319`` of the reference: the same
+parameters, saved tensors, reductions and gradient scaling; the three kernel
+launchers it calls are this package's C-ABI wrappers.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import cast
+
+import torch
+import torch.amp
+
+from .cce_backward import cce_backward_kernel
+from .cce_lse_forward import cce_lse_forward_kernel
+from .constants import IGNORE_INDEX
+from .indexed_dot import indexed_neg_dot_forward_kernel
+from .utils import TensorInfo, _build_flat_valids, _handle_eps, handle_reduction_none
+from .vocab_parallel.utils import VocabParallelOptions, vp_merge_forward
+
+
+@dataclass
+class CCEParams:
+    targets: torch.Tensor
+    valids: torch.Tensor | None
+    softcap: float | None
+    reduction: str
+    filter_eps: float | None
+    shift: int
+    batch_shape: torch.Size
+    accum_e_fp32: bool
+    accum_c_fp32: bool
+    filter_e_grad: bool
+    filter_c_grad: bool
+    vocab_parallel_options: VocabParallelOptions | None
+    return_lse: bool
+
+
+def _reduce_loss(nll: torch.Tensor, params: CCEParams) -> torch.Tensor:
+    if params.reduction == "mean":
+        return nll.mean()
+    if params.reduction == "sum":
+        return nll.sum()
+    if params.reduction == "none":
+        return handle_reduction_none(params.batch_shape, params.valids, params.shift, nll)
+    raise ValueError(f"Unknown reduction {params.reduction}")
+
+
+class LinearCrossEntropyFunction(torch.autograd.Function):
+    @staticmethod
+    @torch.amp.custom_fwd(device_type="cuda")
+    def forward(
+        ctx,
+        e: torch.Tensor,
+        c: torch.Tensor,
+        bias: torch.Tensor | None,
+        params: CCEParams,
+    ) -> tuple[torch.Tensor, torch.Tensor | None]:
+        e_info = TensorInfo(e.dtype, e.requires_grad)
+        c_info = TensorInfo(c.dtype, c.requires_grad)
+        bias_info = TensorInfo(bias.dtype, bias.requires_grad) if bias is not None else None
+
+        if torch.is_autocast_enabled():
+            amp_dtype = torch.get_autocast_gpu_dtype()
+            e, c = e.to(dtype=amp_dtype), c.to(dtype=amp_dtype)
+            if bias is not None:
+                bias = bias.to(dtype=amp_dtype)
+
+        vp = params.vocab_parallel_options
+        vocab_start = vp.start if vp is not None else 0
+
+        lse = cce_lse_forward_kernel(e=e, c=c, bias=bias, valids=params.valids, softcap=params.softcap)
+        assert isinstance(lse, torch.Tensor)
+        # labels this rank does not own give 0, so the same call serves the vocab-parallel case
+        neg_dot = indexed_neg_dot_forward_kernel(
+            e=e,
+            c=c,
+            inds=params.targets,
+            bias=bias,
+            shift=params.shift,
+            valids=params.valids,
+            softcap=params.softcap,
+            out_dtype=lse.dtype,
+            vocab_start=vocab_start,
+        )
+        if vp is not None:
+            lse, neg_dot = vp_merge_forward(lse, neg_dot, vp.group)
+
+        nll = neg_dot.add_(lse)
+
+        ctx.save_for_backward(e, c, bias, lse, params.targets, params.valids)
+        ctx.params = params
+        ctx.e_info, ctx.c_info, ctx.bias_info = e_info, c_info, bias_info
+
+        lse_out = None
+        if params.return_lse:
+            lse_out = handle_reduction_none(params.batch_shape, params.valids, params.shift, lse)
+        return _reduce_loss(nll, params), lse_out
+
+    @staticmethod
+    @torch.amp.custom_bwd(device_type="cuda")
+    def backward(
+        ctx, grad_out: torch.Tensor, grad_lse_out: torch.Tensor | None
+    ) -> tuple[torch.Tensor | None, torch.Tensor | None, torch.Tensor | None, None]:
+        e, c, bias, lse, targets, valids = ctx.saved_tensors
+        params = cast(CCEParams, ctx.params)
+
+        if params.reduction == "mean":
+            grad_scale = 1.0 / max(lse.numel(), 1)
+        elif params.reduction in ("sum", "none"):
+            grad_scale = 1.0
+        else:
+            raise ValueError(f"Unknown reduction {params.reduction}")
+        if params.reduction == "none":
+            grad_out = grad_out.reshape(-1)
+        if grad_lse_out is not None:
+            grad_lse_out = grad_lse_out.reshape(-1)
+
+        vp = params.vocab_parallel_options
+        de, dc, dbias = cce_backward_kernel(
+            do=grad_out,
+            dlse=grad_lse_out,
+            e=e,
+            e_info=ctx.e_info,
+            c=c,
+            c_info=ctx.c_info,
+            bias=bias,
+            bias_info=ctx.bias_info,
+            lse=lse,
+            valids=valids,
+            softcap=params.softcap,
+            filter_eps=params.filter_eps,
+            targets=targets,
+            shift=params.shift,
+            vocab_ordering=None,
+            grad_scale=grad_scale,
+            accum_e_fp32=params.accum_e_fp32,
+            accum_c_fp32=params.accum_c_fp32,
+            filter_e_grad=params.filter_e_grad,
+            filter_c_grad=params.filter_c_grad,
+            reduce_e_grad=vp.reduce_e_grad if vp is not None else False,
+            pg=vp.group if vp is not None else None,
+            vocab_start=vp.start if vp is not None else 0,
+        )
+        return de, dc, dbias, None
+
+
+def linear_cross_entropy_apply(
+    e: torch.Tensor,
+    c: torch.Tensor,
+    bias: torch.Tensor | None,
+    params: CCEParams,
+) -> tuple[torch.Tensor, torch.Tensor | None]:
+    loss, lse = cast(
+        tuple[torch.Tensor, torch.Tensor | None],
+        LinearCrossEntropyFunction.apply(e, c, bias, params),
+    )
+    # with a shift, position j of the outputs belongs to label j: drop the first `shift` slots
+    if params.shift != 0 and params.reduction == "none":
+        loss = loss[..., params.shift :]
+    if params.return_lse and params.shift != 0:
+        assert lse is not None
+        lse = lse[..., params.shift :]
+    return loss, lse
+
+
+def cce_linear_cross_entropy(
+    e: torch.Tensor,
+    c: torch.Tensor,
+    targets: torch.Tensor,
+    bias: torch.Tensor | None = None,
+    ignore_index: int = IGNORE_INDEX,
+    softcap: float | None = None,
+    reduction: str = "mean",
+    shift: bool | int = 0,
+    return_lse: bool = False,
+    filter_eps: float | str | None = "auto",
+    accum_e_fp32: bool = False,
+    accum_c_fp32: bool = False,
+    filter_e_grad: bool = True,
+    filter_c_grad: bool = True,
+    vocab_parallel_options: VocabParallelOptions | None = None,
+) -> tuple[torch.Tensor, torch.Tensor | None]:
+    """Loss (and optionally the log-sum-exp) of ``softcap(e @ c.T + bias)`` against ``targets``
+    without materialising the logits.  See :func:`cut_cross_entropy.linear_cross_entropy`."""
+    assert e.size()[0:-1] == targets.size()
+    assert e.size(-1) == c.size(1)
+    if not (torch.cuda.is_available() and e.is_cuda):
+        raise RuntimeError(
+            "Cut Cross Entropy (B200 backend) requires CUDA tensors on an sm_100 GPU; there is no CPU path."
+        )
+
+    batch_shape = targets.size()
+    e = e.contiguous()
+    targets = targets.contiguous()
+    shift = int(shift)
+    valids = _build_flat_valids(targets, ignore_index, shift)
+
+    e = e.flatten(0, -2)
+    targets = targets.flatten()
+
+    amp_dtype = torch.get_autocast_gpu_dtype() if torch.is_autocast_enabled() else e.dtype
+    params = CCEParams(
+        targets=targets,
+        valids=valids,
+        softcap=softcap,
+        reduction=reduction,
+        filter_eps=_handle_eps(filter_eps, amp_dtype),
+        shift=shift,
+        batch_shape=batch_shape,
+        accum_e_fp32=accum_e_fp32,
+        accum_c_fp32=accum_c_fp32,
+        filter_e_grad=filter_e_grad and filter_eps is not None,
+        filter_c_grad=filter_c_grad and filter_eps is not None,
+        vocab_parallel_options=vocab_parallel_options,
+        return_lse=return_lse,
+    )
+    return linear_cross_entropy_apply(e, c, bias, params)

@@ -1,0 +1,124 @@
+"""Gradients of the loss with respect to ``e``, ``c`` and ``bias``.
+
+Same call as the reference launcher ``cce_backward_kernel``
+(``cut_cross_entropy/cce_backward.py:346-521``); the work is done by
+``cce_b200_backward``: per vocabulary chunk the logit tile is recomputed on the
+tensor cores, turned into the logit gradient in registers, and fed to two more
+tensor-core products (dC = G^T E, dE += G C) that skip blocks the filter cleared.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import _native
+from .utils import TensorInfo
+from .vocab_parallel.utils import vp_reduce_e_grad_
+
+
+def cce_backward_kernel(
+    do: torch.Tensor,
+    dlse: torch.Tensor | None,
+    e: torch.Tensor,
+    e_info: TensorInfo,
+    c: torch.Tensor,
+    c_info: TensorInfo,
+    bias: torch.Tensor | None,
+    bias_info: TensorInfo | None,
+    lse: torch.Tensor,
+    valids: torch.Tensor | None,
+    softcap: float | None,
+    filter_eps: float | None,
+    targets: torch.Tensor | None = None,
+    shift: int = 0,
+    vocab_ordering: torch.Tensor | None = None,
+    grad_scale: float = 1.0,
+    accum_e_fp32: bool = False,
+    accum_c_fp32: bool = False,
+    filter_e_grad: bool = True,
+    filter_c_grad: bool = True,
+    reduce_e_grad: bool = False,
+    pg: "torch.distributed.ProcessGroup | None" = None,
+    vocab_start: int = 0,
+) -> tuple[torch.Tensor | None, torch.Tensor | None, torch.Tensor | None]:
+    """Returns ``(de, dc, dbias)``, each ``None`` unless its ``*_info.requires_grad``.
+
+    ``do`` is the upstream gradient of the loss (one element, or one per entry of
+    ``targets`` and read at the label position), ``dlse`` the upstream gradient of
+    the returned log-sum-exp (or ``None``).  ``targets`` holds global labels;
+    ``vocab_start`` is the first label this rank's ``c`` covers.  ``vocab_ordering``
+    and the ``accum_*_fp32`` switches are accepted and ignored: blocks are filtered
+    in natural vocabulary order and every accumulation is fp32.  With
+    ``reduce_e_grad`` the fp32 partial ``de`` is summed over ``pg`` before the cast.
+    """
+    assert targets is not None
+    assert do.numel() in (e.size(0), 1)
+    assert c.size(1) == e.size(1)
+    assert lse.size(0) == e.size(0) or (valids is not None and lse.size(0) == valids.size(0))
+    if dlse is not None and do.numel() > 1:
+        assert dlse.numel() == do.numel()
+
+    dev = e.device
+    if e.stride(1) != 1 or (e.size(0) > 1 and e.stride(0) < e.size(1)):
+        e = e.contiguous()
+    if c.stride(1) != 1:
+        c = c.contiguous()
+    do = do.reshape(-1).to(dtype=torch.float32).contiguous()
+    lse = lse.to(dtype=torch.float32).contiguous()
+    if dlse is not None:
+        dlse = dlse.reshape(-1).to(dtype=torch.float32).contiguous()
+    targets = targets.contiguous()
+    if targets.dtype != torch.int64:
+        targets = targets.long()
+    if bias is not None:
+        bias = bias.contiguous()
+    if valids is not None:
+        valids = valids.contiguous()
+
+    want_de = e_info.requires_grad
+    want_dc = c_info.requires_grad
+    want_dbias = bias is not None and bias_info is not None and bias_info.requires_grad
+    de_f32 = bool(reduce_e_grad and want_de)
+
+    de = torch.empty(e.shape, dtype=torch.float32 if de_f32 else e.dtype, device=dev) if want_de else None
+    dc = torch.empty((c.size(0), c.size(1)), dtype=c.dtype, device=dev) if want_dc else None
+    dbias = torch.empty((c.size(0),), dtype=torch.float32, device=dev) if want_dbias else None
+
+    if want_de or want_dc or want_dbias:
+        a = _native.BackwardArgs()
+        a.op = _native.make_operands(e, c, bias, valids, softcap)
+        a.lse = lse.data_ptr()
+        a.targets = targets.data_ptr()
+        a.shift = int(shift)
+        a.vocab_start = int(vocab_start)
+        a.d_out = do.data_ptr()
+        a.d_out_numel = do.numel()
+        a.d_lse = _native._ptr(dlse)
+        a.grad_scale = float(grad_scale)
+        a.has_filter = int(filter_eps is not None)
+        a.filter_eps = float(filter_eps) if filter_eps is not None else 0.0
+        a.filter_e = int(bool(filter_e_grad))
+        a.filter_c = int(bool(filter_c_grad))
+        a.d_e = _native._ptr(de)
+        a.d_e_f32 = int(de_f32)
+        a.d_c = _native._ptr(dc)
+        a.d_bias = _native._ptr(dbias)
+        L = _native.lib()
+        ws = _native.workspace(L.cce_b200_backward_workspace_bytes(a), dev)
+        with torch.cuda.device(dev):
+            rc = L.cce_b200_backward(a, ws.data_ptr(), ws.numel(), _native.stream_ptr(dev))
+        _native.check(rc, "cce_b200_backward")
+        _native.finish(ws, "cce_b200_backward")
+
+    if de_f32:
+        assert de is not None
+        vp_reduce_e_grad_(de, pg)
+
+    if dbias is not None:
+        assert bias_info is not None
+        dbias = dbias.to(dtype=bias_info.dtype)
+    if dc is not None:
+        dc = dc.to(dtype=c_info.dtype)
+    if de is not None:
+        de = de.to(dtype=e_info.dtype)
+    return de, dc, dbias

@@ -1,0 +1,51 @@
+"""Log-sum-exp of the (never materialised) logits, on the B200 tensor-core pipeline.
+
+Same call as the reference launcher ``cce_lse_forward_kernel``
+(``cut_cross_entropy/cce_lse_forward.py:163-237``); the work is done by
+``cce_b200_lse_forward`` in ``libcce_b200.so``.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import _native
+
+
+def cce_lse_forward_kernel(
+    e: torch.Tensor,
+    c: torch.Tensor,
+    bias: torch.Tensor | None = None,
+    valids: torch.Tensor | None = None,
+    softcap: float | None = None,
+    return_logit_avg: bool = False,
+) -> tuple[torch.Tensor, torch.Tensor | None] | torch.Tensor:
+    """``lse[i] = logsumexp_v(softcap(e[valids[i]] @ c[v] + bias[v]))`` as float32 ``[B]``.
+
+    ``return_logit_avg`` exists for call compatibility.  The reference uses the
+    per-column mean logit only to reorder the vocabulary before filtering
+    (``cce.py:171-174``); this backend filters in natural vocabulary order, so the
+    second return value is always ``None``.
+    """
+    assert e.shape[1] == c.shape[1], "Incompatible dimensions"
+    assert e.is_contiguous(), "Matrix A must be contiguous"
+    if bias is not None:
+        assert bias.ndim == 1 and c.shape[0] == bias.shape[0]
+        bias = bias.contiguous()
+    if c.stride(1) != 1:
+        c = c.contiguous()
+    if valids is not None:
+        assert valids.ndim == 1
+        valids = valids.contiguous()
+
+    op = _native.make_operands(e, c, bias, valids, softcap)
+    lse = torch.empty((op.n_rows,), dtype=torch.float32, device=e.device)
+    L = _native.lib()
+    ws = _native.workspace(L.cce_b200_lse_workspace_bytes(op), e.device)
+    with torch.cuda.device(e.device):
+        rc = L.cce_b200_lse_forward(op, lse.data_ptr(), ws.data_ptr(), ws.numel(), _native.stream_ptr(e.device))
+    _native.check(rc, "cce_b200_lse_forward")
+    _native.finish(ws, "cce_b200_lse_forward")
+    if return_logit_avg:
+        return lse, None
+    return lse

@@ -1,0 +1,103 @@
+"""Small host-side helpers of the loss path.
+
+Reference behaviour followed here: ``cut_cross_entropy/utils.py:12-120``
+(softcapping, filter-eps resolution, valid-row list, scatter for
+``reduction="none"``, z-loss).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from .constants import IGNORE_INDEX
+
+
+def softcapping(logits: torch.Tensor, softcap: float) -> torch.Tensor:
+    """tanh soft-capping, ``softcap * tanh(logits / softcap)`` (reference utils.py:12-14)."""
+    return torch.tanh(logits / softcap) * softcap
+
+
+def _handle_eps(filter_eps: float | str | None, dtype: torch.dtype) -> float | None:
+    """Resolve the gradient-filter threshold (reference utils.py:17-25).
+
+    ``"auto"`` is 1/32 of the machine epsilon of ``dtype``: 2**-12 for bf16,
+    2**-15 for fp16.
+    """
+    if filter_eps is None:
+        return None
+    if isinstance(filter_eps, float):
+        return filter_eps
+    if filter_eps == "auto":
+        return torch.finfo(dtype).eps / 32
+    raise RuntimeError(f"Unknown eps {filter_eps=}")
+
+
+def _build_flat_valids(targets: torch.Tensor, ignore_index: int, shift: int) -> torch.Tensor | None:
+    """Rows of the flattened ``e`` that enter the loss (reference utils.py:28-49).
+
+    Row ``r`` of ``e`` is paired with label ``targets.flatten()[r + shift]``.
+    Without a shift the result is ``None`` when no label is ignored, else int32
+    row numbers; with a shift it is always an int64 tensor (rows whose label
+    would fall past the end of their sequence are never listed).  The
+    ``nonzero`` inside synchronises the stream, as it does in the reference.
+    """
+    if shift == 0:
+        keep = (targets.reshape(-1) != ignore_index).nonzero().squeeze(1)
+        if keep.numel() == targets.numel():
+            return None
+        return keep.to(torch.int32)
+    seq = targets.size(-1)
+    rows = torch.arange(targets.numel(), device=targets.device).view(targets.shape)[..., : seq - shift]
+    keep = targets[..., shift:] != ignore_index
+    return rows[keep]
+
+
+def handle_reduction_none(
+    batch_shape: torch.Size, valids: torch.Tensor | None, shift: int, loss: torch.Tensor
+) -> torch.Tensor:
+    """Scatter per-valid-row values back to ``batch_shape`` with zeros elsewhere
+    (reference utils.py:52-61).  With a shift the value of row ``r`` lands at the
+    position of its label, ``r + shift``."""
+    if valids is None:
+        return loss.view(batch_shape)
+    full = loss.new_zeros((batch_shape.numel(),))
+    full[(valids + shift).long() if shift != 0 else valids.long()] = loss
+    return full.view(batch_shape)
+
+
+def compute_z_loss(
+    lse: torch.Tensor,
+    targets: torch.Tensor | None = None,
+    shift: bool | int = False,
+    ignore_index: int = IGNORE_INDEX,
+    reduction: str = "mean",
+) -> torch.Tensor:
+    """z-loss ``lse**2`` (reference utils.py:64-102).
+
+    Given ``targets``, positions whose label is ``ignore_index`` contribute zero
+    and the mean is taken over the kept positions only.
+    """
+    z = lse.pow(2)
+    if targets is not None:
+        shift = int(shift)
+        if shift != 0:
+            targets = targets[..., shift:]
+        keep = targets != ignore_index
+        z = torch.where(keep, z, torch.zeros((), dtype=z.dtype, device=z.device))
+        if reduction == "mean":
+            z = z * (z.numel() / keep.count_nonzero().to(z.dtype))
+    if reduction == "mean":
+        return z.mean()
+    if reduction == "sum":
+        return z.sum()
+    if reduction == "none":
+        return z
+    raise ValueError(f"Invalid reduction: {reduction}")
+
+
+@dataclass
+class TensorInfo:
+    dtype: torch.dtype
+    requires_grad: bool
