@@ -128,6 +128,14 @@ int cce_b200_gemm(const void* A, const void* B, void* out, int64_t M, int64_t N,
 /* Synchronises `stream` and returns CCE_OK or CCE_ERR_KERNEL_WAIT; the raw word goes to *word. */
 int cce_b200_read_status(const void* workspace, void* stream, int32_t* word /* host, may be NULL */);
 
+/* Per-kernel timing of the tensor-core launches, for benchmarks.  While enabled, every launch
+ * of the pipeline kernel is bracketed by a CUDA event pair on its stream.  cce_b200_profile_read
+ * waits for the recorded launches, writes the summed milliseconds and the launch counts per
+ * kernel mode (index 0: forward log-sum-exp, 1: logit-gradient recompute, 2: dE/dC products)
+ * into host arrays of 3 entries each, and forgets the records. */
+int cce_b200_profile_enable(int on);
+int cce_b200_profile_read(double* ms /* host [3] */, int64_t* launches /* host [3] */);
+
 /* Counters since library load (host side): kernels launched by this library. */
 int64_t cce_b200_launch_count(void);
 

@@ -7,6 +7,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <vector>
 
 #include "engine.cuh"
 #include "small_kernels.cuh"
@@ -36,6 +37,16 @@ std::atomic<long long> g_launches{0};
             return CCE_ERR_CUDA;                         \
         }                                                \
     } while (0)
+
+// Optional per-kernel timing of the tensor-core launches (off by default): one CUDA event pair
+// per launch, recorded on the launch stream, summed per kernel mode when read.
+struct ProfRecord {
+    cudaEvent_t start, stop;
+    int mode;
+};
+std::mutex g_prof_mu;
+bool g_prof_on = false;
+std::vector<ProfRecord> g_prof;
 
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 inline long long cdiv(long long a, long long b) { return (a + b - 1) / b; }
@@ -120,7 +131,7 @@ int check_operands(const cce_b200_operands* op) {
     if (!op || !op->e || !op->c) return CCE_ERR_ARG;
     if (op->n_total < 0 || op->n_rows < 0 || op->V <= 0 || op->D <= 0) return CCE_ERR_ARG;
     if (op->n_rows > op->n_total) return CCE_ERR_ARG;
-    if (!op->valids && op->n_rows != op->n_total) return CCE_ERR_ARG;
+    if (!op->valids && op->n_rows != 0 && op->n_rows != op->n_total) return CCE_ERR_ARG;
     if (op->dtype != CCE_DT_F16 && op->dtype != CCE_DT_BF16) return CCE_ERR_ARG;
     if (op->bias && (op->bias_dtype < 0 || op->bias_dtype > 2)) return CCE_ERR_ARG;
     if (op->valids && op->valids_dtype != CCE_IDX_I32 && op->valids_dtype != CCE_IDX_I64) return CCE_ERR_ARG;
@@ -240,8 +251,24 @@ int launch_engine(const CUtensorMap& a, const CUtensorMap& b, const EngineParams
         items = (long long)p.n_mblk * p.n_nblk;
     if (items <= 0) return CCE_OK;
     const unsigned grid = (unsigned)(items < sms ? items : sms);
+    ProfRecord rec{nullptr, nullptr, MODE};
+    bool prof = false;
+    {
+        std::lock_guard<std::mutex> lock(g_prof_mu);
+        prof = g_prof_on;
+    }
+    if (prof) {
+        CCE_CUDA(cudaEventCreate(&rec.start));
+        CCE_CUDA(cudaEventCreate(&rec.stop));
+        CCE_CUDA(cudaEventRecord(rec.start, st));
+    }
     engine_kernel<MODE><<<grid, ENGINE_THREADS, ENGINE_SMEM, st>>>(a, b, p);
     CCE_LAUNCH_CHECK();
+    if (prof) {
+        CCE_CUDA(cudaEventRecord(rec.stop, st));
+        std::lock_guard<std::mutex> lock(g_prof_mu);
+        g_prof.push_back(rec);
+    }
     return CCE_OK;
 }
 
@@ -347,6 +374,41 @@ int cce_b200_read_status(const void* workspace, void* stream, int32_t* word) {
     CCE_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
     if (word) *word = w;
     return w == 0 ? CCE_OK : CCE_ERR_KERNEL_WAIT;
+}
+
+int cce_b200_profile_enable(int on) {
+    std::lock_guard<std::mutex> lock(g_prof_mu);
+    g_prof_on = on != 0;
+    return CCE_OK;
+}
+
+int cce_b200_profile_read(double* ms, int64_t* launches) {
+    if (!ms || !launches) return CCE_ERR_ARG;
+    std::vector<ProfRecord> recs;
+    {
+        std::lock_guard<std::mutex> lock(g_prof_mu);
+        recs.swap(g_prof);
+    }
+    for (int i = 0; i < 3; ++i) {
+        ms[i] = 0.0;
+        launches[i] = 0;
+    }
+    int rc = CCE_OK;
+    for (ProfRecord& r : recs) {
+        float t = 0.0f;
+        cudaError_t e = cudaEventSynchronize(r.stop);
+        if (e == cudaSuccess) e = cudaEventElapsedTime(&t, r.start, r.stop);
+        if (e != cudaSuccess) {
+            g_last_cuda = int(e);
+            rc = CCE_ERR_CUDA;
+        } else {
+            ms[r.mode] += t;
+            launches[r.mode] += 1;
+        }
+        cudaEventDestroy(r.start);
+        cudaEventDestroy(r.stop);
+    }
+    return rc;
 }
 
 size_t cce_b200_lse_workspace_bytes(const cce_b200_operands* op) {

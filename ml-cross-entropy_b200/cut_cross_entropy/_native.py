@@ -30,6 +30,8 @@ EXPORTS = (
     "cce_b200_gemm",
     "cce_b200_read_status",
     "cce_b200_launch_count",
+    "cce_b200_profile_enable",
+    "cce_b200_profile_read",
     "cce_b200_strerror",
     "cce_b200_last_cuda_error",
     "cce_b200_version",
@@ -114,6 +116,10 @@ def lib() -> ctypes.CDLL:
     ]  # fmt: skip
     L.cce_b200_read_status.restype = c_int32
     L.cce_b200_read_status.argtypes = [c_void_p, c_void_p, POINTER(c_int32)]
+    L.cce_b200_profile_enable.restype = c_int32
+    L.cce_b200_profile_enable.argtypes = [c_int32]
+    L.cce_b200_profile_read.restype = c_int32
+    L.cce_b200_profile_read.argtypes = [POINTER(ctypes.c_double), POINTER(c_int64)]
     L.cce_b200_launch_count.restype = c_int64
     L.cce_b200_launch_count.argtypes = []
     L.cce_b200_strerror.restype = c_char_p

@@ -16,6 +16,36 @@ from .utils import TensorInfo
 from .vocab_parallel.utils import vp_reduce_e_grad_
 
 
+def _launch(do, dlse, e, c, bias, lse, valids, softcap, filter_eps, targets, shift, grad_scale,
+            filter_e, filter_c, vocab_start, de, dc, dbias) -> None:
+    """Fill the (pre-allocated, possibly ``None``) outputs ``de``/``dc``/``dbias`` through the C ABI."""
+    dev = e.device
+    a = _native.BackwardArgs()
+    a.op = _native.make_operands(e, c, bias, valids, softcap)
+    a.lse = lse.data_ptr()
+    a.targets = targets.data_ptr()
+    a.shift = shift
+    a.vocab_start = vocab_start
+    a.d_out = do.data_ptr()
+    a.d_out_numel = do.numel()
+    a.d_lse = _native._ptr(dlse)
+    a.grad_scale = grad_scale
+    a.has_filter = int(filter_eps is not None)
+    a.filter_eps = float(filter_eps) if filter_eps is not None else 0.0
+    a.filter_e = int(filter_e)
+    a.filter_c = int(filter_c)
+    a.d_e = _native._ptr(de)
+    a.d_e_f32 = int(de is not None and de.dtype == torch.float32)
+    a.d_c = _native._ptr(dc)
+    a.d_bias = _native._ptr(dbias)
+    L = _native.lib()
+    ws = _native.workspace(L.cce_b200_backward_workspace_bytes(a), dev)
+    with torch.cuda.device(dev):
+        rc = L.cce_b200_backward(a, ws.data_ptr(), ws.numel(), _native.stream_ptr(dev))
+    _native.check(rc, "cce_b200_backward")
+    _native.finish(ws, "cce_b200_backward")
+
+
 def cce_backward_kernel(
     do: torch.Tensor,
     dlse: torch.Tensor | None,
@@ -85,30 +115,8 @@ def cce_backward_kernel(
     dbias = torch.empty((c.size(0),), dtype=torch.float32, device=dev) if want_dbias else None
 
     if want_de or want_dc or want_dbias:
-        a = _native.BackwardArgs()
-        a.op = _native.make_operands(e, c, bias, valids, softcap)
-        a.lse = lse.data_ptr()
-        a.targets = targets.data_ptr()
-        a.shift = int(shift)
-        a.vocab_start = int(vocab_start)
-        a.d_out = do.data_ptr()
-        a.d_out_numel = do.numel()
-        a.d_lse = _native._ptr(dlse)
-        a.grad_scale = float(grad_scale)
-        a.has_filter = int(filter_eps is not None)
-        a.filter_eps = float(filter_eps) if filter_eps is not None else 0.0
-        a.filter_e = int(bool(filter_e_grad))
-        a.filter_c = int(bool(filter_c_grad))
-        a.d_e = _native._ptr(de)
-        a.d_e_f32 = int(de_f32)
-        a.d_c = _native._ptr(dc)
-        a.d_bias = _native._ptr(dbias)
-        L = _native.lib()
-        ws = _native.workspace(L.cce_b200_backward_workspace_bytes(a), dev)
-        with torch.cuda.device(dev):
-            rc = L.cce_b200_backward(a, ws.data_ptr(), ws.numel(), _native.stream_ptr(dev))
-        _native.check(rc, "cce_b200_backward")
-        _native.finish(ws, "cce_b200_backward")
+        _launch(do, dlse, e, c, bias, lse, valids, softcap, filter_eps, targets, int(shift), float(grad_scale),
+                bool(filter_e_grad), bool(filter_c_grad), int(vocab_start), de, dc, dbias)
 
     if de_f32:
         assert de is not None

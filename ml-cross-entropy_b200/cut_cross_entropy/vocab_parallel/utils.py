@@ -59,9 +59,10 @@ def vp_merge_forward(
     ``vp_reduce_lse`` + ``vp_reduce_correct_logit`` of the reference.
     """
     world = dist.get_world_size(pg)
-    mine = torch.stack((local_lse.float(), local_neg_dot.float()))
-    gathered = mine.new_empty((world,) + tuple(mine.shape))
-    dist.all_gather_into_tensor(gathered, mine.contiguous(), group=pg)
+    mine = torch.stack((local_lse.float(), local_neg_dot.float())).contiguous()
+    flat = mine.new_empty((world * 2, mine.size(1)))  # rank r fills rows 2r, 2r+1
+    dist.all_gather_into_tensor(flat, mine, group=pg)
+    gathered = flat.view(world, 2, mine.size(1))
     lse = torch.logsumexp(gathered[:, 0], dim=0)
     neg_dot = gathered[:, 1].sum(dim=0)
     return lse, neg_dot

@@ -1,0 +1,174 @@
+"""GPU parity tests of the individual kernels, called through the C ABI.
+
+Layout follows the reference's per-kernel tests (tests/test_cce_lse.py,
+tests/test_cce_indexed_dot.py): ground truth in float32, a same-dtype PyTorch
+result as the yardstick, and the rule  |gt - ours| <= |gt - torch_lowp| + tol.
+"""
+
+from __future__ import annotations
+
+import pytest
+import torch
+from conftest import planted_inputs
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def _gemm(A, B, M, N, K, a_mn, b_mn, out_dtype=torch.float32, accumulate=False, kflags=None, out=None):
+    from cut_cross_entropy import _native
+
+    L = _native.lib()
+    status = torch.zeros(64, dtype=torch.int32, device=DEV)
+    if out is None:
+        out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+    rc = L.cce_b200_gemm(
+        A.data_ptr(), B.data_ptr(), out.data_ptr(), M, N, K, A.stride(0), B.stride(0), out.stride(0),
+        _native._DTYPE_CODE[A.dtype], _native._DTYPE_CODE[out_dtype], int(a_mn), int(b_mn), int(accumulate),
+        None if kflags is None else kflags.data_ptr(), status.data_ptr(), torch.cuda.current_stream().cuda_stream,
+    )  # fmt: skip
+    torch.cuda.synchronize()
+    assert rc == 0, L.cce_b200_strerror(rc)
+    assert int(status[0]) == 0, f"kernel status word {int(status[0]):#x}"
+    return out
+
+
+def _pad_pitch(t):
+    """Same values, row pitch rounded up to 8 elements (TMA needs 16-byte row strides)."""
+    pitch = (t.size(1) + 7) // 8 * 8
+    buf = torch.zeros(t.size(0), pitch, dtype=t.dtype, device=t.device)
+    buf[:, : t.size(1)] = t
+    return buf[:, : t.size(1)]
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("a_mn", [0, 1])
+@pytest.mark.parametrize("b_mn", [0, 1])
+@pytest.mark.parametrize("shape", [(128, 256, 64), (300, 700, 200), (1, 9, 24), (1024, 2304, 1000)])
+def test_gemm_pipeline_all_operand_orders(dtype, a_mn, b_mn, shape):
+    M, N, K = shape
+    torch.manual_seed(0)
+    A = (torch.randn(M, K, device=DEV) * 0.5).to(dtype)
+    B = (torch.randn(N, K, device=DEV) * 0.5).to(dtype)
+    ref = A.float() @ B.float().T
+    Ain = _pad_pitch(A.t().contiguous() if a_mn else A)
+    Bin = _pad_pitch(B.t().contiguous() if b_mn else B)
+    out = _gemm(Ain, Bin, M, N, K, a_mn, b_mn)
+    torch.testing.assert_close(out, ref, rtol=1e-5, atol=1e-5 * K**0.5)
+
+
+def test_gemm_pipeline_kblock_flags_accumulate_and_16bit_out():
+    M, N, K = 512, 520, 1024
+    torch.manual_seed(1)
+    A = (torch.randn(M, K, device=DEV) * 0.5).bfloat16()
+    B = (torch.randn(N, K, device=DEV) * 0.5).bfloat16()
+    kf = (torch.rand(M // 128, K // 64, device=DEV) > 0.5).to(torch.uint8)
+    kf[1] = 0  # a row block with nothing to add
+    mask = kf.repeat_interleave(128, 0).repeat_interleave(64, 1).float()
+    ref = (A.float() * mask) @ B.float().T
+    out = _gemm(A, B, M, N, K, 0, 0, kflags=kf)
+    torch.testing.assert_close(out, ref, rtol=1e-5, atol=1e-3)
+    assert torch.count_nonzero(out[128:256]) == 0
+    base = torch.randn(M, N, device=DEV)
+    out = _gemm(A, B, M, N, K, 0, 0, kflags=kf, accumulate=True, out=base.clone())
+    torch.testing.assert_close(out, ref + base, rtol=1e-5, atol=1e-3)
+    out16 = _gemm(A, B, M, N, K, 0, 0, out_dtype=torch.bfloat16)
+    full = A.float() @ B.float().T
+    torch.testing.assert_close(out16.float(), full.bfloat16().float(), rtol=1e-2, atol=1e-2)
+
+
+SHAPES = [(256, 512, 128), (255, 507, 128), (255, 507, 123)]
+
+
+def _logits(e, c, bias, softcap):
+    x = e @ c.T
+    if bias is not None:
+        x = x + bias
+    if softcap is not None:
+        x = torch.tanh(x / softcap) * softcap
+    return x
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("softcap", [None, 20.0])
+@pytest.mark.parametrize("has_bias", [False, True])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_lse_kernel(dtype, softcap, has_bias, shape):
+    from cut_cross_entropy.cce_lse_forward import cce_lse_forward_kernel
+
+    torch.backends.cuda.matmul.allow_tf32 = False
+    N, V, D = shape
+    e, c, bias, _ = planted_inputs(N, V, D, dtype, DEV, bias=has_bias)
+    gt = torch.logsumexp(_logits(e.float(), c.float(), None if bias is None else bias.float(), softcap), -1)
+    ref = torch.logsumexp(_logits(e, c, bias, softcap).float(), -1)
+    lse = cce_lse_forward_kernel(e, c, bias, softcap=softcap)
+    assert lse.dtype == torch.float32 and lse.shape == (N,)
+    assert ((gt - lse).abs() <= (gt - ref).abs() + 1e-5).all(), (gt - lse).abs().max()
+    # a list of valid rows (int32 and int64) selects rows
+    valids = torch.randperm(N, device=DEV)[: N // 2].sort().values
+    for v in (valids.to(torch.int32), valids):
+        lse_v = cce_lse_forward_kernel(e, c, bias, valids=v, softcap=softcap)
+        torch.testing.assert_close(lse_v, lse[valids], rtol=0, atol=1e-6)
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float16, 1e-3), (torch.bfloat16, 1e-2)])
+@pytest.mark.parametrize("softcap", [None, 20.0])
+@pytest.mark.parametrize("has_bias", [False, True])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_indexed_dot_kernel(dtype, tol, softcap, has_bias, shape):
+    from cut_cross_entropy.indexed_dot import indexed_neg_dot_forward_kernel
+
+    N, V, D = shape
+    e, c, bias, t = planted_inputs(N, V, D, dtype, DEV, bias=has_bias)
+    fb = None if bias is None else bias.float()
+    gt = -_logits(e.float(), c.float(), fb, softcap)[torch.arange(N), t]
+    ref = -_logits(e, c, bias, softcap).float()[torch.arange(N), t]
+    out = indexed_neg_dot_forward_kernel(e, c, t, bias, softcap=softcap, out_dtype=torch.float32)
+    assert ((gt - out).abs() <= (gt - ref).abs() + tol).all()
+    # the kernel accumulates in fp32: it should in fact be close to the float32 answer
+    torch.testing.assert_close(out, gt, rtol=1e-4, atol=1e-4)
+    # shift + valid rows + a vocabulary shard that owns only labels >= V/2
+    shift = 3
+    valids = torch.arange(0, N - shift, 2, device=DEV)
+    out_s = indexed_neg_dot_forward_kernel(
+        e, c[V // 2 :], t, None if bias is None else bias[V // 2 :], shift=shift, valids=valids,
+        softcap=softcap, out_dtype=torch.float32, vocab_start=V // 2,
+    )  # fmt: skip
+    lab = t[valids + shift]
+    want = -_logits(e.float(), c.float(), fb, softcap)[valids, lab]
+    want = torch.where(lab >= V // 2, want, torch.zeros_like(want))
+    torch.testing.assert_close(out_s, want, rtol=1e-4, atol=1e-4)
+
+
+def test_lse_kernel_strided_and_misaligned_inputs():
+    """Inputs TMA cannot address directly (odd pitch, unaligned base) go through the packed copy."""
+    from cut_cross_entropy.cce_lse_forward import cce_lse_forward_kernel
+
+    N, V, D = 200, 400, 64
+    e, c, _, _ = planted_inputs(N, V, D, torch.bfloat16, DEV)
+    gt = torch.logsumexp(e.float() @ c.float().T, -1)
+    c_wide = torch.zeros(V, D + 3, dtype=c.dtype, device=DEV)
+    c_wide[:, 1 : D + 1] = c
+    lse = cce_lse_forward_kernel(e, c_wide[:, 1 : D + 1])
+    torch.testing.assert_close(lse, gt, rtol=1e-5, atol=2e-5)
+
+
+def test_workspace_too_small_and_bad_arguments_are_reported():
+    from cut_cross_entropy import _native
+
+    L = _native.lib()
+    e, c, _, _ = planted_inputs(128, 256, 64, torch.bfloat16, DEV)
+    op = _native.make_operands(e, c, None, None, None)
+    lse = torch.empty(128, device=DEV)
+    ws = _native.workspace(256, e.device)
+    need = L.cce_b200_lse_workspace_bytes(op)
+    assert need > 256
+    rc = L.cce_b200_lse_forward(op, lse.data_ptr(), ws.data_ptr(), 256, torch.cuda.current_stream().cuda_stream)
+    assert rc == -3 and b"workspace" in L.cce_b200_strerror(rc)
+    op.dtype = _native.DT_F32
+    assert L.cce_b200_lse_workspace_bytes(op) == 0
+    rc = L.cce_b200_lse_forward(op, lse.data_ptr(), ws.data_ptr(), 256, torch.cuda.current_stream().cuda_stream)
+    assert rc == -1
+    with pytest.raises(_native.NativeError):
+        _native.check(rc, "lse")
