@@ -47,7 +47,8 @@ enum {
     CCE_ERR_WORKSPACE = -3,  /* workspace too small */
     CCE_ERR_CUDA = -4,       /* a CUDA runtime/driver call failed (see cce_b200_last_cuda_error) */
     CCE_ERR_DEVICE = -5,     /* not an sm_100 device */
-    CCE_ERR_KERNEL_WAIT = -6 /* status word non-zero: a kernel abandoned a bounded wait */
+    CCE_ERR_KERNEL_WAIT = -6, /* status word non-zero: a kernel abandoned a bounded wait */
+    CCE_ERR_TOO_LARGE = -7    /* problem needs more scratch than the fixed buffer of cce_b200_lse_forward_static */
 };
 
 /* Shape and operand description shared by the three entry points.
@@ -75,6 +76,33 @@ typedef struct cce_b200_operands {
 size_t cce_b200_lse_workspace_bytes(const cce_b200_operands* op);
 int cce_b200_lse_forward(const cce_b200_operands* op, float* lse /* [n_rows] */,
                          void* workspace, size_t workspace_bytes, void* stream);
+
+/* Same result as cce_b200_lse_forward, for callers that cannot hand over a workspace.
+ * (No counterpart in the reference, whose launcher allocates its own buffers through PyTorch.)
+ *
+ * Who needs it: a host program that binds this library without a device allocator of its own
+ * (a thin FFI caller in another language), a process in which another component has reserved
+ * all device memory so that a new driver allocation would fail, or a latency-critical loop that
+ * must not hit the implicit device-wide synchronisation of cudaMalloc/cudaFree.  This entry
+ * point calls no cudaMalloc, no cudaFree and no allocating library routine: its scratch memory
+ * is a fixed array of CCE_B200_STATIC_SCRATCH_BYTES bytes that lives inside the library image on
+ * every GPU that loads the library, until the process exits.  The caller passes only the inputs
+ * and the output.
+ *
+ * Limits and rules:
+ *  - the scratch the problem needs (what cce_b200_lse_workspace_bytes reports: the per-band
+ *    partial sums, plus staged copies when `valids` is given or the operands are not 16-byte
+ *    aligned) must fit in the array; otherwise nothing runs and CCE_ERR_TOO_LARGE is returned.
+ *    Aligned, dense operands of the Gemma-2-2B head shape (8192 x 2304 against 256000 rows) need
+ *    about 4 MiB;
+ *  - the first call on each device looks up the device address of the array (with that device
+ *    current).  Make that first call outside any stream capture;
+ *  - all calls on a device share the one array and it keeps the previous call's contents (the
+ *    status word at its start is cleared by every call, everything else that is read is first
+ *    written by the same call).  Two calls that overlap on the GPU (different streams, or
+ *    different host threads without ordering) race on it: order them. */
+#define CCE_B200_STATIC_SCRATCH_BYTES (8u << 20)
+int cce_b200_lse_forward_static(const cce_b200_operands* op, float* lse /* [n_rows] */, void* stream);
 
 /* out[i] = -softcap(e[row_i] . c[t] + bias[t]), t = targets[row_i + shift] - vocab_start;
  * rows whose t falls outside [0, V) get 0 (vocab-parallel ranks that do not

@@ -348,6 +348,32 @@ BwdPlan plan_bwd(const cce_b200_backward_args* a) {
 
 }  // namespace
 
+// Scratch of cce_b200_lse_forward_static.  In host code this name is only a handle: the device
+// address is obtained per device with cudaGetSymbolAddress (static_scratch_ptr below).
+static __device__ __align__(256) unsigned char g_static_scratch[CCE_B200_STATIC_SCRATCH_BYTES];
+
+namespace {
+
+// Device address of g_static_scratch on the current device, looked up once per device.
+int static_scratch_ptr(void** out) {
+    static void* ptrs[64] = {nullptr};
+    static std::mutex mu;
+    int dev = 0;
+    CCE_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return CCE_ERR_DEVICE;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!ptrs[dev]) {
+        void* p = nullptr;
+        CCE_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+        if (!p || (reinterpret_cast<uintptr_t>(p) & 255)) return CCE_ERR_ALIGN;
+        ptrs[dev] = p;
+    }
+    *out = ptrs[dev];
+    return CCE_OK;
+}
+
+}  // namespace
+
 extern "C" {
 
 int cce_b200_version(void) { return 1; }
@@ -363,6 +389,8 @@ const char* cce_b200_strerror(int code) {
         case CCE_ERR_CUDA: return "CUDA call failed (see cce_b200_last_cuda_error)";
         case CCE_ERR_DEVICE: return "device is not sm_100";
         case CCE_ERR_KERNEL_WAIT: return "a kernel abandoned a bounded wait (status word non-zero)";
+        case CCE_ERR_TOO_LARGE:
+            return "problem needs more scratch than the fixed buffer of cce_b200_lse_forward_static";
         default: return "unknown error";
     }
 }
@@ -455,6 +483,17 @@ int cce_b200_lse_forward(const cce_b200_operands* op, float* lse, void* workspac
     lse_combine_kernel<<<(unsigned)cdiv(op->n_rows, 256), 256, 0, st>>>(p.partial, pl.n_band, op->n_rows, lse);
     CCE_LAUNCH_CHECK();
     return CCE_OK;
+}
+
+int cce_b200_lse_forward_static(const cce_b200_operands* op, float* lse, void* stream) {
+    int rc = check_operands(op);
+    if (rc != CCE_OK) return rc;
+    if (plan_lse(op).total > (size_t)CCE_B200_STATIC_SCRATCH_BYTES) return CCE_ERR_TOO_LARGE;
+    void* scratch = nullptr;
+    rc = static_scratch_ptr(&scratch);
+    if (rc != CCE_OK) return rc;
+    // same launches as the workspace form; it clears the status word at the start of the scratch
+    return cce_b200_lse_forward(op, lse, scratch, (size_t)CCE_B200_STATIC_SCRATCH_BYTES, stream);
 }
 
 int cce_b200_indexed_neg_dot(const cce_b200_operands* op, const int64_t* targets, int64_t shift,

@@ -24,6 +24,7 @@ _DTYPE_CODE = {torch.float16: DT_F16, torch.bfloat16: DT_BF16, torch.float32: DT
 EXPORTS = (
     "cce_b200_lse_workspace_bytes",
     "cce_b200_lse_forward",
+    "cce_b200_lse_forward_static",
     "cce_b200_indexed_neg_dot",
     "cce_b200_backward_workspace_bytes",
     "cce_b200_backward",
@@ -103,6 +104,8 @@ def lib() -> ctypes.CDLL:
     L.cce_b200_lse_workspace_bytes.argtypes = [POINTER(Operands)]
     L.cce_b200_lse_forward.restype = c_int32
     L.cce_b200_lse_forward.argtypes = [POINTER(Operands), c_void_p, c_void_p, c_size_t, c_void_p]
+    L.cce_b200_lse_forward_static.restype = c_int32
+    L.cce_b200_lse_forward_static.argtypes = [POINTER(Operands), c_void_p, c_void_p]
     L.cce_b200_indexed_neg_dot.restype = c_int32
     L.cce_b200_indexed_neg_dot.argtypes = [POINTER(Operands), c_void_p, c_int64, c_int64, c_void_p, c_void_p]
     L.cce_b200_backward_workspace_bytes.restype = c_size_t
