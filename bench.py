@@ -214,6 +214,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--config", default=DEFAULT_CONFIG, choices=sorted(CONFIGS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--variant", default=None, help="override the configuration's impl (cce, cce_exact, ...)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--profile-mode", action="store_true",
@@ -258,6 +259,8 @@ def main() -> None:
     if bias is not None:
         bias.requires_grad_(True)
     kw = dict(cfg["kw"])
+    if args.variant:
+        kw["impl"] = args.variant
     z_coef = cfg.get("z_loss")
     shift = kw.get("shift", 0)
 

@@ -75,7 +75,14 @@ typedef struct cce_b200_operands {
  * Replaces cce_lse_forward_kernel (cut_cross_entropy/cce_lse_forward.py:163). */
 size_t cce_b200_lse_workspace_bytes(const cce_b200_operands* op);
 int cce_b200_lse_forward(const cce_b200_operands* op, float* lse /* [n_rows] */,
+                         float* tile_max /* [cce_b200_tile_max_elems(op)] or NULL */,
                          void* workspace, size_t workspace_bytes, void* stream);
+/* Optional by-product of the forward for a filtered backward: the largest logit (in log2 units)
+ * of every (32-row group, 256-column tile) block, [4*ceil(n_rows/128)][ceil(V/256)] floats.
+ * Given to cce_b200_backward it lets the backward skip the recomputation of tiles in which every
+ * softmax value is provably below filter_eps and no label falls.  (The reference keeps a
+ * different by-product for its filter, the mean logit per column, cce_lse_forward.py:95-97.) */
+size_t cce_b200_tile_max_elems(const cce_b200_operands* op);
 
 /* Same result as cce_b200_lse_forward, for callers that cannot hand over a workspace.
  * (No counterpart in the reference, whose launcher allocates its own buffers through PyTorch.)
@@ -130,6 +137,7 @@ typedef struct cce_b200_backward_args {
     int32_t d_e_f32;         /* element type of d_e: 0 = op.dtype, 1 = fp32 (for a caller that reduces dE across ranks in fp32) */
     void* d_c;               /* [V, D] in op.dtype, row stride D, or NULL */
     float* d_bias;           /* [V] fp32 or NULL */
+    const float* tile_max;   /* by-product of cce_b200_lse_forward for the same operands, or NULL */
 } cce_b200_backward_args;
 
 /* Gradient of sum_i d_out_i * grad_scale * (lse_i - logit_i[t_i]) + sum_i d_lse_i * lse_i

@@ -2,7 +2,9 @@
 // planning, TMA descriptor encoding and kernel launches.  No device allocation happens here.
 #include "../../include/cce_b200.h"
 
+#include <algorithm>
 #include <atomic>
+#include <cmath>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -296,11 +298,15 @@ struct BwdPlan {
     int ld_flag_e, ld_flag_c;
     size_t off_g, off_flag_e, off_flag_c, off_de32, total;
     size_t flag_bytes;  // flag_e and flag_c are adjacent: one memset clears both
+    // recompute skipping (needs the forward's tile_max)
+    int n_vt, tiles_per_chunk;
+    size_t off_minlse, off_act, off_counts, off_lists;
+    size_t skip_zero_bytes;  // act and counts are adjacent: one memset clears both
 };
 
 long long pick_chunk(long long n_rows, long long V, long long D) {
     const long long v_round = cdiv(V, BN) * BN;
-    long long cap_bytes = 256LL << 20;
+    long long cap_bytes = 512LL << 20;
     if (const char* env = getenv("CCE_B200_GBUF_MB")) {
         long long mb = atoll(env);
         if (mb >= 1) cap_bytes = mb << 20;
@@ -342,6 +348,17 @@ BwdPlan plan_bwd(const cce_b200_backward_args* a) {
     pl.flag_bytes = off - pl.off_flag_e;
     pl.off_de32 = off;
     if (a->d_e) off = align_up(off + (size_t)op->n_rows * op->D * 4, 256);
+    pl.n_vt = int(cdiv(op->V, BN));
+    pl.tiles_per_chunk = int(pl.Vc / BN);
+    pl.off_minlse = off;
+    off = align_up(off + (size_t)n_rb * 4 * sizeof(float), 256);
+    pl.off_act = off;
+    off = align_up(off + (size_t)n_rb * pl.n_vt, 256);
+    pl.off_counts = off;
+    off = align_up(off + (size_t)pl.n_chunk * sizeof(int), 256);
+    pl.skip_zero_bytes = off - pl.off_act;
+    pl.off_lists = off;
+    off = align_up(off + (size_t)pl.n_chunk * n_rb * pl.tiles_per_chunk * sizeof(int), 256);
     pl.total = off;
     return pl;
 }
@@ -444,8 +461,13 @@ size_t cce_b200_lse_workspace_bytes(const cce_b200_operands* op) {
     return plan_lse(op).total;
 }
 
-int cce_b200_lse_forward(const cce_b200_operands* op, float* lse, void* workspace, size_t workspace_bytes,
-                         void* stream) {
+size_t cce_b200_tile_max_elems(const cce_b200_operands* op) {
+    if (check_operands(op) != CCE_OK) return 0;
+    return (size_t)cdiv(op->n_rows, BM) * 4 * (size_t)cdiv(op->V, BN);
+}
+
+int cce_b200_lse_forward(const cce_b200_operands* op, float* lse, float* tile_max, void* workspace,
+                         size_t workspace_bytes, void* stream) {
     int rc = check_operands(op);
     if (rc != CCE_OK) return rc;
     if (!workspace || (op->n_rows > 0 && !lse)) return CCE_ERR_ARG;
@@ -477,6 +499,7 @@ int cce_b200_lse_forward(const cce_b200_operands* op, float* lse, void* workspac
     p.softcap = op->softcap;
     p.band_len = pl.band_len;
     p.partial = reinterpret_cast<float2*>(ws + pl.off_partial);
+    p.tile_max = tile_max;
     rc = launch_engine<MODE_LSE>(tmA, tmB, p, dev->sms, st);
     if (rc != CCE_OK) return rc;
 
@@ -493,7 +516,7 @@ int cce_b200_lse_forward_static(const cce_b200_operands* op, float* lse, void* s
     rc = static_scratch_ptr(&scratch);
     if (rc != CCE_OK) return rc;
     // same launches as the workspace form; it clears the status word at the start of the scratch
-    return cce_b200_lse_forward(op, lse, scratch, (size_t)CCE_B200_STATIC_SCRATCH_BYTES, stream);
+    return cce_b200_lse_forward(op, lse, nullptr, scratch, (size_t)CCE_B200_STATIC_SCRATCH_BYTES, stream);
 }
 
 int cce_b200_indexed_neg_dot(const cce_b200_operands* op, const int64_t* targets, int64_t shift,
@@ -561,6 +584,10 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
     if (rc != CCE_OK) return rc;
 
     const bool use_flags = a->has_filter && ((a->filter_e && a->d_e) || (a->filter_c && a->d_c));
+    // Tiles of G that provably hold nothing >= eps need not be recomputed when nobody reads them:
+    // every requested product is filtered and no bias gradient sums the whole of G.
+    const bool skip_tiles = a->tile_max && a->has_filter && a->filter_eps > 0.0f && (!a->d_e || a->filter_e) &&
+                            (!a->d_c || a->filter_c) && !a->d_bias && (a->d_e || a->d_c);
     int* status = reinterpret_cast<int*>(ws);
     char* g_buf = ws + pl.off_g;
     uint8_t* flag_e = reinterpret_cast<uint8_t*>(ws + pl.off_flag_e);
@@ -577,6 +604,26 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
     if (rc != CCE_OK) return rc;
     rc = make_tmap(&tmC_mn, sg.c, op->dtype, D, V, sg.ldc, 64, BK);
     if (rc != CCE_OK) return rc;
+
+    int* tile_counts = reinterpret_cast<int*>(ws + pl.off_counts);
+    int* tile_lists = reinterpret_cast<int*>(ws + pl.off_lists);
+    if (skip_tiles) {
+        const int n_rb = int(cdiv(B, BM)), n_groups = n_rb * 4;
+        float* minlse = reinterpret_cast<float*>(ws + pl.off_minlse);
+        uint8_t* act = reinterpret_cast<uint8_t*>(ws + pl.off_act);
+        CCE_CUDA(cudaMemsetAsync(act, 0, pl.skip_zero_bytes, st));
+        rowgroup_min_lse_kernel<<<(unsigned)cdiv(n_groups, 8), 256, 0, st>>>(a->lse, B, minlse, n_groups);
+        CCE_LAUNCH_CHECK();
+        const long long n_thr = std::max<long long>(B, (long long)n_groups * pl.n_vt);
+        tile_mark_kernel<<<(unsigned)cdiv(n_thr, 256), 256, 0, st>>>(
+            a->tile_max, minlse, n_groups, pl.n_vt, log2f(a->filter_eps), reinterpret_cast<const long long*>(a->targets),
+            op->valids, op->valids_dtype == CCE_IDX_I64, a->shift, a->vocab_start, V, B, act);
+        CCE_LAUNCH_CHECK();
+        tile_compact_kernel<<<(unsigned)cdiv((long long)n_rb * pl.n_vt, 256), 256, 0, st>>>(
+            act, n_rb, pl.n_vt, pl.tiles_per_chunk, tile_lists, tile_counts);
+        CCE_LAUNCH_CHECK();
+    }
+    if (a->d_e) CCE_CUDA(cudaMemsetAsync(de32, 0, (size_t)B * D * 4, st));
 
     for (int ch = 0; ch < pl.n_chunk; ++ch) {
         const long long v0 = (long long)ch * pl.Vc;
@@ -610,6 +657,11 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
             p.ld_flag_e = pl.ld_flag_e;
             p.flag_c = flag_c;
             p.ld_flag_c = pl.ld_flag_c;
+            if (skip_tiles) {
+                p.tile_list = tile_lists + (size_t)ch * cdiv(B, BM) * pl.tiles_per_chunk;
+                p.tile_count = tile_counts + ch;
+                p.tile_div = pl.tiles_per_chunk;
+            }
             rc = launch_engine<MODE_PGRAD>(tmE_k, tmC_k, p, dev->sms, st);
             if (rc != CCE_OK) return rc;
         }
@@ -644,7 +696,7 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
             p.out = de32;
             p.ldo = D;
             p.out_dtype = CCE_DT_F32;
-            p.accumulate = ch > 0;
+            p.accumulate = 2;  // fp32 scratch was zeroed above; every chunk adds with vector red
             if (a->has_filter && a->filter_e) {
                 p.kflags = flag_e;
                 p.ld_kflags = pl.ld_flag_e;

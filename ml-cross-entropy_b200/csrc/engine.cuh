@@ -51,6 +51,11 @@ struct EngineParams {
     float softcap;
     int band_len;       // vocabulary tiles per work item (MODE_LSE)
     float2* partial;    // [n_band][M]  (running max in log2 units, sum)
+    float* tile_max;    // null or [n_mblk*4][n_nblk]: max logit (log2 units) of each 32-row x 256-col block
+    // ---- MODE_PGRAD: optional compact list of the tiles to visit (mblk * n_nblk + nblk)
+    const int* tile_list;
+    const int* tile_count;
+    int tile_div;  // tile id = mblk * tile_div + nblk
     // ---- MODE_PGRAD
     const float* lse;          // [M]
     const long long* targets;  // [n_total]
@@ -74,7 +79,7 @@ struct EngineParams {
     void* out;
     long long ldo;
     int out_dtype;   // CCE_DT_*
-    int accumulate;  // fp32 out only
+    int accumulate;  // fp32 out only: 0 store, 1 read-add-store, 2 vector red.add (out pre-zeroed)
     const uint8_t* kflags;  // null or [n_mblk][ld_kflags]
     int ld_kflags;
 };
@@ -104,6 +109,8 @@ struct TileIter {
         if (MODE == MODE_LSE) {
             const int n_band = (p.n_nblk + p.band_len - 1) / p.band_len;
             n_items = n_band * p.n_mblk;
+        } else if (MODE == MODE_PGRAD && p.tile_list) {
+            n_items = *p.tile_count;
         } else {
             n_items = p.n_mblk * p.n_nblk;
         }
@@ -128,8 +135,14 @@ struct TileIter {
             item += gridDim.x;
             if (item >= n_items) return false;
             if (MODE == MODE_PGRAD) {
-                nblk = item / p.n_mblk;  // concurrent CTAs share the classifier tile
-                mblk = item % p.n_mblk;
+                if (p.tile_list) {
+                    const int t = p.tile_list[item];
+                    mblk = t / p.tile_div;
+                    nblk = t % p.tile_div;
+                } else {
+                    nblk = item / p.n_mblk;  // concurrent CTAs share the classifier tile
+                    mblk = item % p.n_mblk;
+                }
             } else {
                 mblk = item / p.n_nblk;
                 nblk = item % p.n_nblk;
@@ -345,6 +358,7 @@ __device__ void epilogue_loop(const EngineParams& p, const EngineSmem& s, uint32
             (MODE == MODE_GEMM) ? (reinterpret_cast<volatile int*>(s.acc_empty)[acc] != 0) : false;
         const uint32_t taddr = tmem_base + acc * BN + (uint32_t(q * 32) << 16);
 
+        float tile_rowmax = -INFINITY;  // MODE_LSE: max logit (log2 units) of this row within the tile
         if (MODE == MODE_GEMM && acc_is_empty && p.accumulate) {
             // nothing to add
         } else {
@@ -385,6 +399,7 @@ __device__ void epilogue_loop(const EngineParams& p, const EngineSmem& s, uint32
                         x[j] = (col0 + j < p.N) ? x[j] * kLog2e : -INFINITY;
                         cmax = fmaxf(cmax, x[j]);
                     }
+                    tile_rowmax = fmaxf(tile_rowmax, cmax);
                     if (cmax > run_m) {
                         run_s *= ex2f(run_m - cmax);  // run_m = -inf gives 0
                         run_m = cmax;
@@ -420,7 +435,8 @@ __device__ void epilogue_loop(const EngineParams& p, const EngineSmem& s, uint32
                     }
                     if (p.filter_eps >= 0.0f) {
                         flag_bits |= __ballot_sync(0xffffffffu, active && row_ok);
-                        if (c & 1) {
+                        // publish at the end of each 64-column group, and at the tile's last chunk
+                        if ((c & 1) || (col0 + 32 >= p.N)) {
                             if (flag_bits && lane == 0) {
                                 const int cb64 = it.nblk * (BN / 64) + (c >> 1);
                                 p.flag_e[(size_t)it.mblk * p.ld_flag_e + cb64] = 1;
@@ -435,7 +451,11 @@ __device__ void epilogue_loop(const EngineParams& p, const EngineSmem& s, uint32
                         if (p.out_dtype == 2) {
                             float* dst = reinterpret_cast<float*>(p.out) + (size_t)row * p.ldo + col0;
                             const bool vec = (ncol == 32) && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
-                            if (vec) {
+                            if (vec && p.accumulate == 2) {
+#pragma unroll
+                                for (int j = 0; j < 8; ++j)
+                                    red_add_v4(dst + 4 * j, x[4 * j], x[4 * j + 1], x[4 * j + 2], x[4 * j + 3]);
+                            } else if (vec) {
                                 float4* d4 = reinterpret_cast<float4*>(dst);
 #pragma unroll
                                 for (int j = 0; j < 8; ++j) {
@@ -477,6 +497,14 @@ __device__ void epilogue_loop(const EngineParams& p, const EngineSmem& s, uint32
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&s.tempty[acc]));
+        if (MODE == MODE_LSE) {
+            if (p.tile_max) {
+                float m = row_ok ? tile_rowmax : -INFINITY;
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+                if (lane == 0) p.tile_max[(size_t)(it.mblk * 4 + q) * p.n_nblk + it.nblk] = m;
+            }
+        }
         if (++acc == 2) {
             acc = 0;
             acc_phase ^= 1u;

@@ -103,6 +103,53 @@ __global__ void indexed_neg_dot_kernel(const T* __restrict__ e, long long lde, c
     }
 }
 
+// out[g] = log2(e) * min(lse[32g .. 32g+31]); one warp per group of 32 rows.
+__global__ void rowgroup_min_lse_kernel(const float* __restrict__ lse, long long n_rows,
+                                        float* __restrict__ out, int n_groups) {
+    const int g = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (g >= n_groups) return;
+    const long long r = (long long)g * 32 + lane;
+    float v = r < n_rows ? lse[r] * kLog2e : INFINITY;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fminf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    if (lane == 0) out[g] = v;
+}
+
+// Marks the (128-row block, 256-column tile) pairs of the logit-gradient matrix that can hold an
+// entry with |softmax - onehot| >= eps:  act[rb][vt] = 1 if the tile holds a label of one of its
+// rows, or if for one of its four 32-row groups  tile_max - min_lse >= log2(eps)  (an upper
+// bound of every softmax value in the group).  Thread i handles row i (labels) and pair i (bound).
+__global__ void tile_mark_kernel(const float* __restrict__ tile_max, const float* __restrict__ min_lse2,
+                                 int n_groups, int n_vt, float log2_eps, const long long* __restrict__ targets,
+                                 const void* __restrict__ valids, int valids_i64, long long shift,
+                                 long long vocab_start, long long V, long long n_rows,
+                                 uint8_t* __restrict__ act) {
+    const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    if (i < n_rows) {
+        const long long r = valids ? load_index(valids, valids_i64, i) : i;
+        const long long t = targets[r + shift] - vocab_start;
+        if (t >= 0 && t < V) act[(i >> 7) * n_vt + (t >> 8)] = 1;
+    }
+    if (i < (long long)n_groups * n_vt) {
+        const int g = int(i / n_vt), vt = int(i % n_vt);
+        if (tile_max[i] - min_lse2[g] >= log2_eps) act[(size_t)(g >> 2) * n_vt + vt] = 1;
+    }
+}
+
+// Per vocabulary chunk, the compact list of active tiles: id = rb * tiles_per_chunk + tile-in-chunk.
+// Thread index runs vocabulary-tile-major so that neighbours in a list share classifier tiles.
+__global__ void tile_compact_kernel(const uint8_t* __restrict__ act, int n_rb, int n_vt, int tiles_per_chunk,
+                                    int* __restrict__ lists, int* __restrict__ counts) {
+    const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    if (i >= (long long)n_rb * n_vt) return;
+    const int vt = int(i / n_rb), rb = int(i % n_rb);
+    if (!act[(size_t)rb * n_vt + vt]) return;
+    const int ch = vt / tiles_per_chunk;
+    const int slot = atomicAdd(counts + ch, 1);
+    lists[(size_t)ch * n_rb * tiles_per_chunk + slot] = rb * tiles_per_chunk + (vt - ch * tiles_per_chunk);
+}
+
 // dbias[col] += sum_rows G[row][col] for a [n_rows][width] 16-bit block with pitch ldg.
 // grid = (ceil(width/256), ceil(n_rows/rows_per_block)); 128 threads, two columns each.
 template <typename T>

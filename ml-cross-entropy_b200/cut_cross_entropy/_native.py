@@ -24,6 +24,7 @@ _DTYPE_CODE = {torch.float16: DT_F16, torch.bfloat16: DT_BF16, torch.float32: DT
 EXPORTS = (
     "cce_b200_lse_workspace_bytes",
     "cce_b200_lse_forward",
+    "cce_b200_tile_max_elems",
     "cce_b200_lse_forward_static",
     "cce_b200_indexed_neg_dot",
     "cce_b200_backward_workspace_bytes",
@@ -78,6 +79,7 @@ class BackwardArgs(Structure):
         ("d_e_f32", c_int32),
         ("d_c", c_void_p),
         ("d_bias", c_void_p),
+        ("tile_max", c_void_p),
     ]
 
 
@@ -103,7 +105,9 @@ def lib() -> ctypes.CDLL:
     L.cce_b200_lse_workspace_bytes.restype = c_size_t
     L.cce_b200_lse_workspace_bytes.argtypes = [POINTER(Operands)]
     L.cce_b200_lse_forward.restype = c_int32
-    L.cce_b200_lse_forward.argtypes = [POINTER(Operands), c_void_p, c_void_p, c_size_t, c_void_p]
+    L.cce_b200_lse_forward.argtypes = [POINTER(Operands), c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]
+    L.cce_b200_tile_max_elems.restype = c_size_t
+    L.cce_b200_tile_max_elems.argtypes = [POINTER(Operands)]
     L.cce_b200_lse_forward_static.restype = c_int32
     L.cce_b200_lse_forward_static.argtypes = [POINTER(Operands), c_void_p, c_void_p]
     L.cce_b200_indexed_neg_dot.restype = c_int32

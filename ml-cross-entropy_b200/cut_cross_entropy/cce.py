@@ -71,7 +71,21 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
         vp = params.vocab_parallel_options
         vocab_start = vp.start if vp is not None else 0
 
-        lse = cce_lse_forward_kernel(e=e, c=c, bias=bias, valids=params.valids, softcap=params.softcap)
+        # The filtered backward can skip recomputing logit tiles that provably hold nothing above the
+        # threshold if the forward records each tile's largest logit; worth it only when every
+        # gradient that will be asked for is filtered (and the bias, whose gradient sums every
+        # entry, asks for none).
+        want_tile_max = (
+            params.filter_eps is not None
+            and (e_info.requires_grad or c_info.requires_grad)
+            and (params.filter_e_grad or not e_info.requires_grad)
+            and (params.filter_c_grad or not c_info.requires_grad)
+            and not (bias_info is not None and bias_info.requires_grad)
+        )
+        ret = cce_lse_forward_kernel(
+            e=e, c=c, bias=bias, valids=params.valids, softcap=params.softcap, return_tile_max=want_tile_max
+        )
+        lse, tile_max = ret if want_tile_max else (ret, None)
         assert isinstance(lse, torch.Tensor)
         # labels this rank does not own give 0, so the same call serves the vocab-parallel case
         neg_dot = indexed_neg_dot_forward_kernel(
@@ -90,7 +104,7 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
 
         nll = neg_dot.add_(lse)
 
-        ctx.save_for_backward(e, c, bias, lse, params.targets, params.valids)
+        ctx.save_for_backward(e, c, bias, lse, params.targets, params.valids, tile_max)
         ctx.params = params
         ctx.e_info, ctx.c_info, ctx.bias_info = e_info, c_info, bias_info
 
@@ -104,7 +118,7 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
     def backward(
         ctx, grad_out: torch.Tensor, grad_lse_out: torch.Tensor | None
     ) -> tuple[torch.Tensor | None, torch.Tensor | None, torch.Tensor | None, None]:
-        e, c, bias, lse, targets, valids = ctx.saved_tensors
+        e, c, bias, lse, targets, valids, tile_max = ctx.saved_tensors
         params = cast(CCEParams, ctx.params)
 
         if params.reduction == "mean":
@@ -143,6 +157,7 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
             reduce_e_grad=vp.reduce_e_grad if vp is not None else False,
             pg=vp.group if vp is not None else None,
             vocab_start=vp.start if vp is not None else 0,
+            tile_max=tile_max,
         )
         return de, dc, dbias, None
 

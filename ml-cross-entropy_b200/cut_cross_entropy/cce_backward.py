@@ -17,7 +17,7 @@ from .vocab_parallel.utils import vp_reduce_e_grad_
 
 
 def _launch(do, dlse, e, c, bias, lse, valids, softcap, filter_eps, targets, shift, grad_scale,
-            filter_e, filter_c, vocab_start, de, dc, dbias) -> None:
+            filter_e, filter_c, vocab_start, de, dc, dbias, tile_max=None) -> None:
     """Fill the (pre-allocated, possibly ``None``) outputs ``de``/``dc``/``dbias`` through the C ABI."""
     dev = e.device
     a = _native.BackwardArgs()
@@ -38,6 +38,7 @@ def _launch(do, dlse, e, c, bias, lse, valids, softcap, filter_eps, targets, shi
     a.d_e_f32 = int(de is not None and de.dtype == torch.float32)
     a.d_c = _native._ptr(dc)
     a.d_bias = _native._ptr(dbias)
+    a.tile_max = _native._ptr(tile_max)
     L = _native.lib()
     ws = _native.workspace(L.cce_b200_backward_workspace_bytes(a), dev)
     with torch.cuda.device(dev):
@@ -70,6 +71,7 @@ def cce_backward_kernel(
     reduce_e_grad: bool = False,
     pg: "torch.distributed.ProcessGroup | None" = None,
     vocab_start: int = 0,
+    tile_max: torch.Tensor | None = None,
 ) -> tuple[torch.Tensor | None, torch.Tensor | None, torch.Tensor | None]:
     """Returns ``(de, dc, dbias)``, each ``None`` unless its ``*_info.requires_grad``.
 
@@ -80,6 +82,7 @@ def cce_backward_kernel(
     and the ``accum_*_fp32`` switches are accepted and ignored: blocks are filtered
     in natural vocabulary order and every accumulation is fp32.  With
     ``reduce_e_grad`` the fp32 partial ``de`` is summed over ``pg`` before the cast.
+    ``tile_max`` is the optional by-product of ``cce_lse_forward_kernel(return_tile_max=True)``.
     """
     assert targets is not None
     assert do.numel() in (e.size(0), 1)
@@ -116,7 +119,7 @@ def cce_backward_kernel(
 
     if want_de or want_dc or want_dbias:
         _launch(do, dlse, e, c, bias, lse, valids, softcap, filter_eps, targets, int(shift), float(grad_scale),
-                bool(filter_e_grad), bool(filter_c_grad), int(vocab_start), de, dc, dbias)
+                bool(filter_e_grad), bool(filter_c_grad), int(vocab_start), de, dc, dbias, tile_max)
 
     if de_f32:
         assert de is not None

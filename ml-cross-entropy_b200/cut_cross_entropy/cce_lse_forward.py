@@ -19,6 +19,7 @@ def cce_lse_forward_kernel(
     valids: torch.Tensor | None = None,
     softcap: float | None = None,
     return_logit_avg: bool = False,
+    return_tile_max: bool = False,
 ) -> tuple[torch.Tensor, torch.Tensor | None] | torch.Tensor:
     """``lse[i] = logsumexp_v(softcap(e[valids[i]] @ c[v] + bias[v]))`` as float32 ``[B]``.
 
@@ -26,6 +27,10 @@ def cce_lse_forward_kernel(
     per-column mean logit only to reorder the vocabulary before filtering
     (``cce.py:171-174``); this backend filters in natural vocabulary order, so the
     second return value is always ``None``.
+
+    ``return_tile_max`` asks for this backend's own by-product instead: the largest logit (in
+    log2 units) of every (32-row group, 256-column tile) block, which lets the filtered
+    backward skip recomputing tiles that cannot hold a value above the filter threshold.
     """
     assert e.shape[1] == c.shape[1], "Incompatible dimensions"
     assert e.is_contiguous(), "Matrix A must be contiguous"
@@ -41,11 +46,18 @@ def cce_lse_forward_kernel(
     op = _native.make_operands(e, c, bias, valids, softcap)
     lse = torch.empty((op.n_rows,), dtype=torch.float32, device=e.device)
     L = _native.lib()
+    tile_max = None
+    if return_tile_max:
+        tile_max = torch.empty((L.cce_b200_tile_max_elems(op),), dtype=torch.float32, device=e.device)
     ws = _native.workspace(L.cce_b200_lse_workspace_bytes(op), e.device)
     with torch.cuda.device(e.device):
-        rc = L.cce_b200_lse_forward(op, lse.data_ptr(), ws.data_ptr(), ws.numel(), _native.stream_ptr(e.device))
+        rc = L.cce_b200_lse_forward(
+            op, lse.data_ptr(), _native._ptr(tile_max), ws.data_ptr(), ws.numel(), _native.stream_ptr(e.device)
+        )
     _native.check(rc, "cce_b200_lse_forward")
     _native.finish(ws, "cce_b200_lse_forward")
+    if return_tile_max:
+        return lse, tile_max
     if return_logit_avg:
         return lse, None
     return lse

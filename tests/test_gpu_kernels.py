@@ -164,11 +164,11 @@ def test_workspace_too_small_and_bad_arguments_are_reported():
     ws = _native.workspace(256, e.device)
     need = L.cce_b200_lse_workspace_bytes(op)
     assert need > 256
-    rc = L.cce_b200_lse_forward(op, lse.data_ptr(), ws.data_ptr(), 256, torch.cuda.current_stream().cuda_stream)
+    rc = L.cce_b200_lse_forward(op, lse.data_ptr(), None, ws.data_ptr(), 256, torch.cuda.current_stream().cuda_stream)
     assert rc == -3 and b"workspace" in L.cce_b200_strerror(rc)
     op.dtype = _native.DT_F32
     assert L.cce_b200_lse_workspace_bytes(op) == 0
-    rc = L.cce_b200_lse_forward(op, lse.data_ptr(), ws.data_ptr(), 256, torch.cuda.current_stream().cuda_stream)
+    rc = L.cce_b200_lse_forward(op, lse.data_ptr(), None, ws.data_ptr(), 256, torch.cuda.current_stream().cuda_stream)
     assert rc == -1
     with pytest.raises(_native.NativeError):
         _native.check(rc, "lse")

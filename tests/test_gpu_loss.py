@@ -111,7 +111,7 @@ IMPLS = ["cce", "cce_exact", "cce_kahan", "cce_kahan_full_c", "cce_kahan_full_e"
 @pytest.mark.parametrize("invalids", [False, True])
 @pytest.mark.parametrize("reduction", ["none", "mean", "sum"])
 @pytest.mark.parametrize("z_loss", [True, False])
-@pytest.mark.parametrize("shape", [(256, 512, 128), (252, 507, 123)])
+@pytest.mark.parametrize("shape", [(256, 512, 128), (252, 507, 123), (252, 276, 72)])
 def test_loss_backward_bf16(impl, softcap, has_bias, shift, invalids, reduction, z_loss, shape):
     _backward_case(torch.bfloat16, 1e-2, impl, softcap, has_bias, shift, invalids, reduction, z_loss, shape)
 
@@ -299,3 +299,94 @@ def test_error_behaviour_matches_reference():
         linear_cross_entropy(e, c[:, :16], t)
     with pytest.raises(NotImplementedError):
         linear_cross_entropy(e.float(), c.float(), t)
+
+
+@pytest.mark.parametrize("softcap", [None, 30.0])
+@pytest.mark.parametrize("shape", [(1024, 6000, 256), (700, 2500, 192)])
+def test_recompute_skipping_changes_nothing(softcap, shape):
+    """With the forward's per-tile maxima the filtered backward skips recomputing tiles that cannot
+    reach the threshold; the blocks it skips are blocks the filter drops anyway, so the gradients
+    are the same numbers as without the by-product."""
+    from cut_cross_entropy.cce_backward import cce_backward_kernel
+    from cut_cross_entropy.cce_lse_forward import cce_lse_forward_kernel
+    from cut_cross_entropy.utils import TensorInfo
+
+    N, V, D = shape
+    g = torch.Generator().manual_seed(5)
+    e = torch.randn(N, D, generator=g).bfloat16().to(DEV)
+    c = (torch.randn(V, D, generator=g) * 0.02).bfloat16().to(DEV)
+    t = torch.randint(0, V, (N,), generator=g).to(DEV)
+    valids = torch.arange(0, N, device=DEV, dtype=torch.int32)[torch.rand(N, generator=g).to(DEV) > 0.1]
+    lse, tile_max = cce_lse_forward_kernel(e, c, valids=valids, softcap=softcap, return_tile_max=True)
+    assert tile_max.numel() == ((valids.numel() + 127) // 128) * 4 * ((V + 255) // 256)
+    # the by-product is what it says: block maxima of the (soft-capped) logits in log2 units
+    x = e[valids.long()].float() @ c.float().T
+    if softcap is not None:
+        x = torch.tanh(x / softcap) * softcap
+    B = valids.numel()
+    n_g, n_vt = ((B + 127) // 128) * 4, (V + 255) // 256
+    xp = torch.full((n_g * 32, n_vt * 256), float("-inf"), device=DEV)
+    xp[:B, :V] = x * 1.4426950408889634
+    want = xp.view(n_g, 32, n_vt, 256).amax(dim=(1, 3))
+    torch.testing.assert_close(tile_max.view(n_g, n_vt), want, rtol=1e-5, atol=1e-4)
+
+    do = torch.ones((), device=DEV)
+    info = TensorInfo(torch.bfloat16, True)
+    kw = dict(do=do, dlse=None, e=e, e_info=info, c=c, c_info=info, bias=None, bias_info=None, lse=lse,
+              valids=valids, softcap=softcap, filter_eps=2.0**-12, targets=t, grad_scale=1.0 / B)
+    de0, dc0, _ = cce_backward_kernel(**kw)
+    de1, dc1, _ = cce_backward_kernel(**kw, tile_max=tile_max)
+    torch.testing.assert_close(de1, de0, rtol=0, atol=0)
+    torch.testing.assert_close(dc1, dc0, rtol=0, atol=0)
+    # and both stay within the filter's error bound of the exact gradient
+    de2, dc2, _ = cce_backward_kernel(**{**kw, "filter_eps": None})
+    assert (de1.float() - de2.float()).abs().max() <= 1e-2 * de2.float().abs().max()
+    assert (dc1.float() - dc2.float()).abs().max() <= 1e-2 * dc2.float().abs().max()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+@pytest.mark.parametrize("impl_filter", [None, 2.0**-12])
+def test_vocabulary_shards_on_one_gpu(world, impl_filter):
+    """The per-rank arithmetic of vocab parallelism, run shard after shard on one GPU: per-shard
+    log-sum-exp and correct logit merge to the unsharded values; with the global lse each shard's
+    dC is the matching slice of the unsharded dC and the dE partial sums add up."""
+    from cut_cross_entropy.cce_backward import cce_backward_kernel
+    from cut_cross_entropy.cce_lse_forward import cce_lse_forward_kernel
+    from cut_cross_entropy.indexed_dot import indexed_neg_dot_forward_kernel
+    from cut_cross_entropy.utils import TensorInfo
+    from cut_cross_entropy.vocab_parallel import partition_n_into_range
+
+    N, V, D = 512, 1003, 128
+    e, c, bias, t = planted_inputs(N, V, D, torch.bfloat16, DEV, seed=3, bias=True, ignored=0.2)
+    valids = (t != IGNORE).nonzero().squeeze(1).to(torch.int32)
+    B = valids.numel()
+    info = TensorInfo(torch.bfloat16, True)
+    do = torch.ones((), device=DEV)
+
+    def bwd(cs, bs, lse, start):
+        return cce_backward_kernel(do=do, dlse=None, e=e, e_info=info, c=cs, c_info=info, bias=bs, bias_info=info,
+                                   lse=lse, valids=valids, softcap=20.0, filter_eps=impl_filter, targets=t,
+                                   grad_scale=1.0 / B, vocab_start=start, reduce_e_grad=False)  # fmt: skip
+
+    lse_full = cce_lse_forward_kernel(e, c, bias, valids, 20.0)
+    dot_full = indexed_neg_dot_forward_kernel(e, c, t, bias, 0, valids, 20.0, torch.float32)
+    de_full, dc_full, db_full = bwd(c, bias, lse_full, 0)
+
+    lses, dots, shards = [], [], []
+    for r in range(world):
+        s0, s1 = partition_n_into_range(V, r, world)
+        cs, bs = c[s0:s1].contiguous(), bias[s0:s1].contiguous()
+        lses.append(cce_lse_forward_kernel(e, cs, bs, valids, 20.0))
+        dots.append(indexed_neg_dot_forward_kernel(e, cs, t, bs, 0, valids, 20.0, torch.float32, vocab_start=s0))
+        shards.append((s0, s1, cs, bs))
+    lse = torch.logsumexp(torch.stack(lses), 0)
+    torch.testing.assert_close(lse, lse_full, rtol=0, atol=1e-5)
+    torch.testing.assert_close(torch.stack(dots).sum(0), dot_full, rtol=0, atol=0)
+    de_sum = torch.zeros_like(de_full, dtype=torch.float32)
+    for s0, s1, cs, bs in shards:
+        de, dc, db = bwd(cs, bs, lse_full, s0)
+        scale = dc_full.float().abs().max().item()
+        assert (dc.float() - dc_full[s0:s1].float()).abs().max().item() <= 1e-2 * scale
+        torch.testing.assert_close(db.float(), db_full[s0:s1].float(), rtol=2e-2, atol=1e-4)
+        de_sum += de.float()
+    assert (de_sum - de_full.float()).abs().max().item() <= 1e-2 * de_full.float().abs().max().item()

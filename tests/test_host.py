@@ -41,7 +41,7 @@ def test_ctypes_structs_match_the_header_layout():
     L = _native.lib()
     op = _native.Operands()
     assert L.cce_b200_lse_workspace_bytes(op) == 0
-    assert L.cce_b200_lse_forward(op, None, None, 0, None) == -1
+    assert L.cce_b200_lse_forward(op, None, None, None, 0, None) == -1
     assert L.cce_b200_backward(None, None, 0, None) == -1
 
 

@@ -31,14 +31,15 @@ def _install_cpu_stand_ins():
     import cut_cross_entropy.cce as cce_mod
     import cut_cross_entropy.cce_backward as bwd_mod
 
-    def lse_kernel(e, c, bias=None, valids=None, softcap=None, return_logit_avg=False):
+    def lse_kernel(e, c, bias=None, valids=None, softcap=None, return_logit_avg=False, return_tile_max=False):
+        assert not return_tile_max
         return O.lse_forward(e, c, bias, valids, softcap).float()
 
     def dot_kernel(e, c, inds, bias=None, shift=0, valids=None, softcap=None, out_dtype=None, vocab_start=0):
         return O.indexed_neg_dot(e, c, inds, bias, shift, valids, softcap, vocab_start=vocab_start).to(out_dtype)
 
     def launch(do, dlse, e, c, bias, lse, valids, softcap, filter_eps, targets, shift, grad_scale,
-               filter_e, filter_c, vocab_start, de, dc, dbias):
+               filter_e, filter_c, vocab_start, de, dc, dbias, tile_max=None):
         # restates one rank of cce_backward.py:182-310 with the global lse
         n = e.size(0)
         rows = torch.arange(n) if valids is None else valids.long()
