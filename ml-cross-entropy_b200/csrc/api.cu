@@ -291,27 +291,18 @@ void base_params(EngineParams* p, long long M, long long N, long long K, int fmt
 }
 
 // ---- backward planning
-struct BwdPlan {
-    OperandPlan ops;
-    long long Vc;  // vocabulary columns per chunk (multiple of 256)
-    int n_chunk;
-    int ld_flag_e, ld_flag_c;
-    size_t off_g, off_flag_e, off_flag_c, off_de32, total;
-    size_t flag_bytes;  // flag_e and flag_c are adjacent: one memset clears both
-    // recompute skipping (needs the forward's tile_max)
-    int n_vt, tiles_per_chunk;
-    size_t off_minlse, off_act, off_counts, off_lists;
-    size_t skip_zero_bytes;  // act and counts are adjacent: one memset clears both
-};
-
-long long pick_chunk(long long n_rows, long long V, long long D) {
-    const long long v_round = cdiv(V, BN) * BN;
+long long gbuf_cap_bytes() {
     long long cap_bytes = 512LL << 20;
     if (const char* env = getenv("CCE_B200_GBUF_MB")) {
         long long mb = atoll(env);
         if (mb >= 1) cap_bytes = mb << 20;
     }
-    long long cap = cap_bytes / (2 * (n_rows > 0 ? n_rows : 1)) / BN * BN;
+    return cap_bytes;
+}
+
+long long pick_chunk(long long n_rows, long long V, long long D) {
+    const long long v_round = cdiv(V, BN) * BN;
+    long long cap = gbuf_cap_bytes() / (2 * (n_rows > 0 ? n_rows : 1)) / BN * BN;
     if (cap < BN) cap = BN;
     if (cap >= v_round) return v_round;
     // among widths within [cap/2, cap] prefer the one whose dC product fills whole waves of CTAs
@@ -329,36 +320,94 @@ long long pick_chunk(long long n_rows, long long V, long long D) {
     return best;
 }
 
+constexpr size_t kSlotBytes = (size_t)BM * BN * 2;  // one 128x256 16-bit tile of the pool
+
+// Two shapes of the backward.
+//  dense : the vocabulary is cut into chunks of Vc columns; G[B][Vc] is recomputed in full for a
+//          chunk and fed to the two products.  Serves every variant.
+//  sparse: when every requested product is filtered, no bias gradient is wanted and the forward's
+//          per-tile maxima are at hand, only the tiles that can hold a value >= eps are
+//          recomputed, into a pool of tile slots, and the products walk lists of those slots.
+struct BwdPlan {
+    OperandPlan ops;
+    bool sparse;
+    // dense
+    long long Vc;  // vocabulary columns per chunk (multiple of 256)
+    int n_chunk;
+    int ld_flag_e, ld_flag_c;
+    size_t off_flag_e, off_flag_c, flag_bytes;  // flag_e and flag_c are adjacent: one memset clears both
+    // sparse
+    int n_rb, n_vt, capacity, max_pass;
+    size_t off_minlse, off_act, off_col_ptr, off_row_ptr, off_slot_tile, off_slot_of, off_row_slots, off_pass,
+        off_sflags, off_de_list, off_dc_list, off_de_cnt, off_dc_cnt;
+    // both
+    size_t off_g, off_de32, total;
+};
+
+bool wants_sparse(const cce_b200_backward_args* a) {
+    return a->tile_max && a->has_filter && a->filter_eps > 0.0f && (!a->d_e || a->filter_e) &&
+           (!a->d_c || a->filter_c) && !a->d_bias && (a->d_e || a->d_c);
+}
+
 BwdPlan plan_bwd(const cce_b200_backward_args* a) {
     const cce_b200_operands* op = &a->op;
     BwdPlan pl;
+    memset(&pl, 0, sizeof(pl));
     pl.ops = plan_operands(op, kStatusBytes);
-    pl.Vc = pick_chunk(op->n_rows, op->V, op->D);
-    pl.n_chunk = int(cdiv(op->V, pl.Vc));
-    const long long n_rb = cdiv(op->n_rows, BM);
-    pl.ld_flag_e = int(pl.Vc / 64);
-    pl.ld_flag_c = int(align_up((size_t)cdiv(op->n_rows, 64) + 1, 16));
+    pl.n_rb = int(cdiv(op->n_rows, BM));
+    pl.n_vt = int(cdiv(op->V, BN));
     size_t off = pl.ops.end;
-    pl.off_g = off;
-    off = align_up(off + (size_t)(n_rb * BM) * pl.Vc * 2, 256);
-    pl.off_flag_e = off;
-    off = align_up(off + (size_t)n_rb * pl.ld_flag_e, 256);
-    pl.off_flag_c = off;
-    off = align_up(off + (size_t)(pl.Vc / 128) * pl.ld_flag_c, 256);
-    pl.flag_bytes = off - pl.off_flag_e;
     pl.off_de32 = off;
     if (a->d_e) off = align_up(off + (size_t)op->n_rows * op->D * 4, 256);
-    pl.n_vt = int(cdiv(op->V, BN));
-    pl.tiles_per_chunk = int(pl.Vc / BN);
-    pl.off_minlse = off;
-    off = align_up(off + (size_t)n_rb * 4 * sizeof(float), 256);
-    pl.off_act = off;
-    off = align_up(off + (size_t)n_rb * pl.n_vt, 256);
-    pl.off_counts = off;
-    off = align_up(off + (size_t)pl.n_chunk * sizeof(int), 256);
-    pl.skip_zero_bytes = off - pl.off_act;
-    pl.off_lists = off;
-    off = align_up(off + (size_t)pl.n_chunk * n_rb * pl.tiles_per_chunk * sizeof(int), 256);
+
+    const long long total_tiles = (long long)pl.n_rb * pl.n_vt;
+    long long cap = gbuf_cap_bytes() / (long long)kSlotBytes;
+    if (cap > total_tiles) cap = total_tiles;
+    pl.sparse = wants_sparse(a) && total_tiles > 0 && cap >= 2LL * pl.n_rb && std::max(pl.n_rb, pl.n_vt) < 12000;
+    if (pl.sparse) {
+        pl.capacity = int(cap);
+        pl.max_pass = int(total_tiles / (cap - pl.n_rb + 1)) + 2;
+        pl.off_minlse = off;
+        off = align_up(off + (size_t)pl.n_rb * 4 * sizeof(float), 256);
+        pl.off_act = off;
+        off = align_up(off + (size_t)total_tiles, 256);
+        pl.off_col_ptr = off;
+        off = align_up(off + (size_t)(pl.n_vt + 1) * 4, 256);
+        pl.off_row_ptr = off;
+        off = align_up(off + (size_t)(pl.n_rb + 1) * 4, 256);
+        pl.off_slot_tile = off;
+        off = align_up(off + (size_t)total_tiles * 4, 256);
+        pl.off_slot_of = off;
+        off = align_up(off + (size_t)total_tiles * 4, 256);
+        pl.off_row_slots = off;
+        off = align_up(off + (size_t)total_tiles * 4, 256);
+        pl.off_pass = off;
+        off = align_up(off + (size_t)pl.max_pass * 4 * sizeof(int), 256);
+        pl.off_sflags = off;  // [capacity][4] for dE, then [capacity][4] for dC
+        off = align_up(off + (size_t)pl.capacity * 8, 256);
+        pl.off_de_list = off;
+        off = align_up(off + (size_t)total_tiles * 4 * sizeof(int2), 256);
+        pl.off_dc_list = off;
+        off = align_up(off + (size_t)total_tiles * 4 * sizeof(int2), 256);
+        pl.off_de_cnt = off;
+        off = align_up(off + (size_t)pl.n_rb * sizeof(int), 256);
+        pl.off_dc_cnt = off;
+        off = align_up(off + (size_t)pl.n_vt * 2 * sizeof(int), 256);
+        pl.off_g = off;
+        off = align_up(off + (size_t)pl.capacity * kSlotBytes, 1024);
+    } else {
+        pl.Vc = pick_chunk(op->n_rows, op->V, op->D);
+        pl.n_chunk = int(cdiv(op->V, pl.Vc));
+        pl.ld_flag_e = int(pl.Vc / 64);
+        pl.ld_flag_c = int(align_up((size_t)cdiv(op->n_rows, 64) + 1, 16));
+        pl.off_g = off;
+        off = align_up(off + (size_t)(pl.n_rb * BM) * pl.Vc * 2, 256);
+        pl.off_flag_e = off;
+        off = align_up(off + (size_t)pl.n_rb * pl.ld_flag_e, 256);
+        pl.off_flag_c = off;
+        off = align_up(off + (size_t)(pl.Vc / 128) * pl.ld_flag_c, 256);
+        pl.flag_bytes = off - pl.off_flag_e;
+    }
     pl.total = off;
     return pl;
 }
@@ -584,15 +633,10 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
     if (rc != CCE_OK) return rc;
 
     const bool use_flags = a->has_filter && ((a->filter_e && a->d_e) || (a->filter_c && a->d_c));
-    // Tiles of G that provably hold nothing >= eps need not be recomputed when nobody reads them:
-    // every requested product is filtered and no bias gradient sums the whole of G.
-    const bool skip_tiles = a->tile_max && a->has_filter && a->filter_eps > 0.0f && (!a->d_e || a->filter_e) &&
-                            (!a->d_c || a->filter_c) && !a->d_bias && (a->d_e || a->d_c);
     int* status = reinterpret_cast<int*>(ws);
     char* g_buf = ws + pl.off_g;
-    uint8_t* flag_e = reinterpret_cast<uint8_t*>(ws + pl.off_flag_e);
-    uint8_t* flag_c = reinterpret_cast<uint8_t*>(ws + pl.off_flag_c);
     float* de32 = reinterpret_cast<float*>(ws + pl.off_de32);
+    if (a->d_e) CCE_CUDA(cudaMemsetAsync(de32, 0, (size_t)B * D * 4, st));  // every product adds with red
 
     // operand maps that do not change from chunk to chunk
     CUtensorMap tmE_k, tmC_k, tmE_mn, tmC_mn;
@@ -605,13 +649,44 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
     rc = make_tmap(&tmC_mn, sg.c, op->dtype, D, V, sg.ldc, 64, BK);
     if (rc != CCE_OK) return rc;
 
-    int* tile_counts = reinterpret_cast<int*>(ws + pl.off_counts);
-    int* tile_lists = reinterpret_cast<int*>(ws + pl.off_lists);
-    if (skip_tiles) {
-        const int n_rb = int(cdiv(B, BM)), n_groups = n_rb * 4;
+    // phase-1 parameters shared by both shapes
+    EngineParams pg;
+    base_params(&pg, B, V, sg.Dk, op->dtype, 0, 0, status);
+    pg.bias = sg.bias;
+    pg.has_softcap = op->has_softcap;
+    pg.softcap = op->softcap;
+    pg.lse = a->lse;
+    pg.targets = reinterpret_cast<const long long*>(a->targets);
+    pg.valids = op->valids;
+    pg.valids_i64 = op->valids_dtype == CCE_IDX_I64;
+    pg.shift = a->shift;
+    pg.vocab_start = a->vocab_start;
+    pg.d_out = a->d_out;
+    pg.d_out_scalar = a->d_out_numel == 1;
+    pg.d_lse = a->d_lse;
+    pg.grad_scale = a->grad_scale;
+    pg.filter_eps = use_flags ? a->filter_eps : -1.0f;
+    pg.g_out = g_buf;
+    pg.g_is_bf16 = op->dtype == CCE_DT_BF16;
+
+    if (pl.sparse) {
+        // ---- index of the tiles worth recomputing
+        const int n_groups = pl.n_rb * 4;
         float* minlse = reinterpret_cast<float*>(ws + pl.off_minlse);
         uint8_t* act = reinterpret_cast<uint8_t*>(ws + pl.off_act);
-        CCE_CUDA(cudaMemsetAsync(act, 0, pl.skip_zero_bytes, st));
+        int* col_ptr = reinterpret_cast<int*>(ws + pl.off_col_ptr);
+        int* row_ptr = reinterpret_cast<int*>(ws + pl.off_row_ptr);
+        int* slot_tile = reinterpret_cast<int*>(ws + pl.off_slot_tile);
+        int* slot_of = reinterpret_cast<int*>(ws + pl.off_slot_of);
+        int* row_slots = reinterpret_cast<int*>(ws + pl.off_row_slots);
+        int* pass_info = reinterpret_cast<int*>(ws + pl.off_pass);
+        uint8_t* sflag_e = reinterpret_cast<uint8_t*>(ws + pl.off_sflags);
+        uint8_t* sflag_c = sflag_e + (size_t)pl.capacity * 4;
+        int2* de_list = reinterpret_cast<int2*>(ws + pl.off_de_list);
+        int2* dc_list = reinterpret_cast<int2*>(ws + pl.off_dc_list);
+        int* de_cnt = reinterpret_cast<int*>(ws + pl.off_de_cnt);
+        int* dc_cnt = reinterpret_cast<int*>(ws + pl.off_dc_cnt);
+        CCE_CUDA(cudaMemsetAsync(act, 0, (size_t)pl.n_rb * pl.n_vt, st));
         rowgroup_min_lse_kernel<<<(unsigned)cdiv(n_groups, 8), 256, 0, st>>>(a->lse, B, minlse, n_groups);
         CCE_LAUNCH_CHECK();
         const long long n_thr = std::max<long long>(B, (long long)n_groups * pl.n_vt);
@@ -619,104 +694,146 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
             a->tile_max, minlse, n_groups, pl.n_vt, log2f(a->filter_eps), reinterpret_cast<const long long*>(a->targets),
             op->valids, op->valids_dtype == CCE_IDX_I64, a->shift, a->vocab_start, V, B, act);
         CCE_LAUNCH_CHECK();
-        tile_compact_kernel<<<(unsigned)cdiv((long long)n_rb * pl.n_vt, 256), 256, 0, st>>>(
-            act, n_rb, pl.n_vt, pl.tiles_per_chunk, tile_lists, tile_counts);
+        const size_t sm_bytes = (size_t)(std::max(pl.n_rb, pl.n_vt) + 1) * sizeof(int);
+        tile_index_kernel<<<1, 1024, sm_bytes, st>>>(act, pl.n_rb, pl.n_vt, pl.capacity, pl.max_pass, col_ptr, slot_tile,
+                                                    slot_of, row_ptr, row_slots, pass_info);
         CCE_LAUNCH_CHECK();
-    }
-    if (a->d_e) CCE_CUDA(cudaMemsetAsync(de32, 0, (size_t)B * D * 4, st));
 
-    for (int ch = 0; ch < pl.n_chunk; ++ch) {
-        const long long v0 = (long long)ch * pl.Vc;
-        const long long Vw = (V - v0 < pl.Vc) ? (V - v0) : pl.Vc;
-        if (use_flags) CCE_CUDA(cudaMemsetAsync(flag_e, 0, pl.flag_bytes, st));
+        CUtensorMap tmP_k, tmP_mn;  // the pool seen as a [capacity*128][256] matrix
+        rc = make_tmap(&tmP_k, g_buf, op->dtype, BN, (long long)pl.capacity * BM, BN, BK, BM);
+        if (rc != CCE_OK) return rc;
+        rc = make_tmap(&tmP_mn, g_buf, op->dtype, BN, (long long)pl.capacity * BM, BN, 64, BK);
+        if (rc != CCE_OK) return rc;
 
-        // phase 1: G = dLoss/dLogits for columns [v0, v0 + Vw)
-        {
-            EngineParams p;
-            base_params(&p, B, Vw, sg.Dk, op->dtype, 0, 0, status);
-            p.b_mn_off = int(v0);
-            p.bias = sg.bias;
-            p.col_off = int(v0);
-            p.has_softcap = op->has_softcap;
-            p.softcap = op->softcap;
-            p.lse = a->lse;
-            p.targets = reinterpret_cast<const long long*>(a->targets);
-            p.valids = op->valids;
-            p.valids_i64 = op->valids_dtype == CCE_IDX_I64;
-            p.shift = a->shift;
-            p.vocab_start = a->vocab_start;
-            p.d_out = a->d_out;
-            p.d_out_scalar = a->d_out_numel == 1;
-            p.d_lse = a->d_lse;
-            p.grad_scale = a->grad_scale;
-            p.filter_eps = use_flags ? a->filter_eps : -1.0f;
-            p.g_out = g_buf;
-            p.ldg = pl.Vc;
-            p.g_is_bf16 = op->dtype == CCE_DT_BF16;
-            p.flag_e = flag_e;
-            p.ld_flag_e = pl.ld_flag_e;
-            p.flag_c = flag_c;
-            p.ld_flag_c = pl.ld_flag_c;
-            if (skip_tiles) {
-                p.tile_list = tile_lists + (size_t)ch * cdiv(B, BM) * pl.tiles_per_chunk;
-                p.tile_count = tile_counts + ch;
-                p.tile_div = pl.tiles_per_chunk;
+        for (int ps = 0; ps < pl.max_pass; ++ps) {
+            const int* pinfo = pass_info + 4 * ps;
+            CCE_CUDA(cudaMemsetAsync(sflag_e, 0, (size_t)pl.capacity * 8, st));
+            {
+                EngineParams p = pg;
+                p.sparse = 1;
+                p.pass_info = pinfo;
+                p.slot_tile = slot_tile;
+                p.n_vt = pl.n_vt;
+                p.sflag_e = sflag_e;
+                p.sflag_c = sflag_c;
+                rc = launch_engine<MODE_PGRAD>(tmE_k, tmC_k, p, dev->sms, st);
+                if (rc != CCE_OK) return rc;
             }
-            rc = launch_engine<MODE_PGRAD>(tmE_k, tmC_k, p, dev->sms, st);
-            if (rc != CCE_OK) return rc;
-        }
-
-        // phase 2: dC[v0 : v0 + Vw, :] = G^T E   (M = Vw, N = D, K = B; both operands MN-major)
-        if (a->d_c) {
-            CUtensorMap tmG_mn;
-            rc = make_tmap(&tmG_mn, g_buf, op->dtype, Vw, B, pl.Vc, 64, BK);
-            if (rc != CCE_OK) return rc;
-            EngineParams p;
-            base_params(&p, Vw, D, B, op->dtype, 1, 1, status);
-            p.out = reinterpret_cast<char*>(a->d_c) + (size_t)v0 * D * esz;
-            p.ldo = D;
-            p.out_dtype = op->dtype;
-            p.accumulate = 0;
-            if (a->has_filter && a->filter_c) {
-                p.kflags = flag_c;
-                p.ld_kflags = pl.ld_flag_c;
-            }
-            rc = launch_engine<MODE_GEMM>(tmG_mn, tmE_mn, p, dev->sms, st);
-            if (rc != CCE_OK) return rc;
-        }
-
-        // phase 3: dE += G C[v0 : v0 + Vw, :]    (M = B, N = D, K = Vw; A K-major, B MN-major)
-        if (a->d_e) {
-            CUtensorMap tmG_k;
-            rc = make_tmap(&tmG_k, g_buf, op->dtype, Vw, B, pl.Vc, BK, BM);
-            if (rc != CCE_OK) return rc;
-            EngineParams p;
-            base_params(&p, B, D, Vw, op->dtype, 0, 1, status);
-            p.b_k_off = int(v0);
-            p.out = de32;
-            p.ldo = D;
-            p.out_dtype = CCE_DT_F32;
-            p.accumulate = 2;  // fp32 scratch was zeroed above; every chunk adds with vector red
-            if (a->has_filter && a->filter_e) {
-                p.kflags = flag_e;
-                p.ld_kflags = pl.ld_flag_e;
-            }
-            rc = launch_engine<MODE_GEMM>(tmG_k, tmC_mn, p, dev->sms, st);
-            if (rc != CCE_OK) return rc;
-        }
-
-        // bias gradient: column sums of G
-        if (a->d_bias) {
-            const int rows_per_block = 512;
-            dim3 grid((unsigned)cdiv(Vw, 256), (unsigned)cdiv(B, rows_per_block));
-            if (op->dtype == CCE_DT_BF16)
-                colsum_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(g_buf),
-                                                                   pl.Vc, B, int(Vw), rows_per_block,
-                                                                   a->d_bias + v0);
-            else
-                colsum_kernel<__half><<<grid, 128, 0, st>>>(reinterpret_cast<const __half*>(g_buf), pl.Vc, B,
-                                                            int(Vw), rows_per_block, a->d_bias + v0);
+            klist_build_kernel<<<(unsigned)cdiv(pl.n_rb + 2 * pl.n_vt, 8), 256, 0, st>>>(
+                pinfo, row_ptr, row_slots, col_ptr, slot_tile, pl.n_rb, pl.n_vt, sflag_e, sflag_c, de_list, de_cnt,
+                dc_list, dc_cnt);
             CCE_LAUNCH_CHECK();
+            if (a->d_c) {  // dC[vt] = sum over the slots of column vt of G^T E
+                EngineParams p;
+                base_params(&p, V, D, B, op->dtype, 1, 1, status);
+                p.out = a->d_c;
+                p.ldo = D;
+                p.out_dtype = op->dtype;
+                p.accumulate = 0;
+                p.sparse = 2;
+                p.pass_info = pinfo;
+                p.slot_tile = slot_tile;
+                p.col_ptr = col_ptr;
+                p.n_vt = pl.n_vt;
+                p.klist = dc_list;
+                p.kcount = dc_cnt;
+                rc = launch_engine<MODE_GEMM>(tmP_mn, tmE_mn, p, dev->sms, st);
+                if (rc != CCE_OK) return rc;
+            }
+            if (a->d_e) {  // dE[rb] += sum over the slots of row rb (in this pass) of G C
+                EngineParams p;
+                base_params(&p, B, D, V, op->dtype, 0, 1, status);
+                p.out = de32;
+                p.ldo = D;
+                p.out_dtype = CCE_DT_F32;
+                p.accumulate = 2;
+                p.sparse = 1;
+                p.pass_info = pinfo;
+                p.slot_tile = slot_tile;
+                p.row_ptr = row_ptr;
+                p.n_vt = pl.n_vt;
+                p.klist = de_list;
+                p.kcount = de_cnt;
+                rc = launch_engine<MODE_GEMM>(tmP_k, tmC_mn, p, dev->sms, st);
+                if (rc != CCE_OK) return rc;
+            }
+        }
+    } else {
+        uint8_t* flag_e = reinterpret_cast<uint8_t*>(ws + pl.off_flag_e);
+        uint8_t* flag_c = reinterpret_cast<uint8_t*>(ws + pl.off_flag_c);
+        for (int ch = 0; ch < pl.n_chunk; ++ch) {
+            const long long v0 = (long long)ch * pl.Vc;
+            const long long Vw = (V - v0 < pl.Vc) ? (V - v0) : pl.Vc;
+            if (use_flags) CCE_CUDA(cudaMemsetAsync(flag_e, 0, pl.flag_bytes, st));
+
+            // phase 1: G = dLoss/dLogits for columns [v0, v0 + Vw)
+            {
+                EngineParams p = pg;
+                p.N = int(Vw);
+                p.n_nblk = int(cdiv(Vw, BN));
+                p.b_mn_off = int(v0);
+                p.col_off = int(v0);
+                p.ldg = pl.Vc;
+                p.flag_e = flag_e;
+                p.ld_flag_e = pl.ld_flag_e;
+                p.flag_c = flag_c;
+                p.ld_flag_c = pl.ld_flag_c;
+                rc = launch_engine<MODE_PGRAD>(tmE_k, tmC_k, p, dev->sms, st);
+                if (rc != CCE_OK) return rc;
+            }
+
+            // phase 2: dC[v0 : v0 + Vw, :] = G^T E   (M = Vw, N = D, K = B; both operands MN-major)
+            if (a->d_c) {
+                CUtensorMap tmG_mn;
+                rc = make_tmap(&tmG_mn, g_buf, op->dtype, Vw, B, pl.Vc, 64, BK);
+                if (rc != CCE_OK) return rc;
+                EngineParams p;
+                base_params(&p, Vw, D, B, op->dtype, 1, 1, status);
+                p.out = reinterpret_cast<char*>(a->d_c) + (size_t)v0 * D * esz;
+                p.ldo = D;
+                p.out_dtype = op->dtype;
+                p.accumulate = 0;
+                if (a->has_filter && a->filter_c) {
+                    p.kflags = flag_c;
+                    p.ld_kflags = pl.ld_flag_c;
+                }
+                rc = launch_engine<MODE_GEMM>(tmG_mn, tmE_mn, p, dev->sms, st);
+                if (rc != CCE_OK) return rc;
+            }
+
+            // phase 3: dE += G C[v0 : v0 + Vw, :]    (M = B, N = D, K = Vw; A K-major, B MN-major)
+            if (a->d_e) {
+                CUtensorMap tmG_k;
+                rc = make_tmap(&tmG_k, g_buf, op->dtype, Vw, B, pl.Vc, BK, BM);
+                if (rc != CCE_OK) return rc;
+                EngineParams p;
+                base_params(&p, B, D, Vw, op->dtype, 0, 1, status);
+                p.b_k_off = int(v0);
+                p.out = de32;
+                p.ldo = D;
+                p.out_dtype = CCE_DT_F32;
+                p.accumulate = 2;  // fp32 scratch was zeroed above; every chunk adds with vector red
+                if (a->has_filter && a->filter_e) {
+                    p.kflags = flag_e;
+                    p.ld_kflags = pl.ld_flag_e;
+                }
+                rc = launch_engine<MODE_GEMM>(tmG_k, tmC_mn, p, dev->sms, st);
+                if (rc != CCE_OK) return rc;
+            }
+
+            // bias gradient: column sums of G
+            if (a->d_bias) {
+                const int rows_per_block = 512;
+                dim3 grid((unsigned)cdiv(Vw, 256), (unsigned)cdiv(B, rows_per_block));
+                if (op->dtype == CCE_DT_BF16)
+                    colsum_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(g_buf),
+                                                                       pl.Vc, B, int(Vw), rows_per_block,
+                                                                       a->d_bias + v0);
+                else
+                    colsum_kernel<__half><<<grid, 128, 0, st>>>(reinterpret_cast<const __half*>(g_buf), pl.Vc, B,
+                                                                int(Vw), rows_per_block, a->d_bias + v0);
+                CCE_LAUNCH_CHECK();
+            }
         }
     }
 

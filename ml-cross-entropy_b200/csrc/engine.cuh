@@ -52,10 +52,26 @@ struct EngineParams {
     int band_len;       // vocabulary tiles per work item (MODE_LSE)
     float2* partial;    // [n_band][M]  (running max in log2 units, sum)
     float* tile_max;    // null or [n_mblk*4][n_nblk]: max logit (log2 units) of each 32-row x 256-col block
-    // ---- MODE_PGRAD: optional compact list of the tiles to visit (mblk * n_nblk + nblk)
-    const int* tile_list;
-    const int* tile_count;
-    int tile_div;  // tile id = mblk * tile_div + nblk
+    // ---- block-list ("sparse") forms of the backward, used when every product is filtered:
+    // only tiles that can hold a value >= eps are recomputed, each into its own slot of a pool
+    // of 128x256 tiles, and the two products walk per-row / per-column lists of those slots.
+    //   MODE_PGRAD, sparse != 0 : visit the slots of this pass, write G to pool slot (slot - slot_lo)
+    //   MODE_GEMM,  sparse == 1 : dE[rb] += sum over the slots of row rb      (A = pool, B = classifier)
+    //   MODE_GEMM,  sparse == 2 : dC[vt] = sum over the slots of column vt    (A = pool, B = embeddings)
+    int sparse;
+    const int* pass_info;  // device: {vt_lo, vt_hi, slot_lo, slot_hi} of this pass
+    const int* slot_tile;  // [n_slots] tile id rb * n_vt + vt, sorted by vt, then rb
+    const int* row_ptr;    // [n_mblk + 1] CSR over row blocks
+    const int* col_ptr;    // [n_vt + 1]; column vt owns slots [col_ptr[vt], col_ptr[vt + 1])
+    // K-block lists of this pass, built after phase 1 from the slot flags (klist_build_kernel):
+    //   dE, row block rb : klist[4*row_ptr[rb] + i], i < kcount[rb]        = {slot_local*4 + kb, vt}
+    //   dC, (vt, half h) : klist[4*col_ptr[vt] + 2*h*n + i], n = slots of vt, i < kcount[2*vt+h]
+    //                                                                      = {slot_local*2 + kb, rb}
+    const int2* klist;
+    const int* kcount;
+    int n_vt;
+    uint8_t* sflag_e;  // [slot - slot_lo][4]: 64-column group of the tile has a value >= eps
+    uint8_t* sflag_c;  // [slot - slot_lo][4]: (128-column half, 64-row half) has a value >= eps
     // ---- MODE_PGRAD
     const float* lse;          // [M]
     const long long* targets;  // [n_total]
@@ -96,21 +112,39 @@ struct EngineSmem {
     int* acc_empty;  // [2] accumulator holds no product (all K blocks skipped)
 };
 
+struct PassInfo {
+    int vt_lo, vt_hi, slot_lo, slot_hi;
+};
+__device__ __forceinline__ PassInfo load_pass(const EngineParams& p) {
+    PassInfo pi{0, 0, 0, 0};
+    if (p.sparse) {
+        pi.vt_lo = p.pass_info[0];
+        pi.vt_hi = p.pass_info[1];
+        pi.slot_lo = p.pass_info[2];
+        pi.slot_hi = p.pass_info[3];
+    }
+    return pi;
+}
+
 template <int MODE>
 struct TileIter {
     const EngineParams& p;
+    const PassInfo& pass;
     int item, n_items, sub, sub_end;
-    int mblk, nblk, band;
+    int mblk, nblk, band, slot;
     bool first, last;
-    __device__ TileIter(const EngineParams& p_) : p(p_) {
+    __device__ TileIter(const EngineParams& p_, const PassInfo& pass_) : p(p_), pass(pass_) {
         item = int(blockIdx.x) - int(gridDim.x);
         sub = 0;
         sub_end = 0;
+        slot = 0;
         if (MODE == MODE_LSE) {
             const int n_band = (p.n_nblk + p.band_len - 1) / p.band_len;
             n_items = n_band * p.n_mblk;
-        } else if (MODE == MODE_PGRAD && p.tile_list) {
-            n_items = *p.tile_count;
+        } else if (MODE == MODE_PGRAD && p.sparse) {
+            n_items = pass.slot_hi - pass.slot_lo;
+        } else if (MODE == MODE_GEMM && p.sparse == 2) {
+            n_items = (pass.vt_hi - pass.vt_lo) * 2 * p.n_nblk;
         } else {
             n_items = p.n_mblk * p.n_nblk;
         }
@@ -135,14 +169,18 @@ struct TileIter {
             item += gridDim.x;
             if (item >= n_items) return false;
             if (MODE == MODE_PGRAD) {
-                if (p.tile_list) {
-                    const int t = p.tile_list[item];
-                    mblk = t / p.tile_div;
-                    nblk = t % p.tile_div;
+                if (p.sparse) {
+                    const int t = p.slot_tile[pass.slot_lo + item];
+                    mblk = t / p.n_vt;
+                    nblk = t % p.n_vt;
+                    slot = item;
                 } else {
                     nblk = item / p.n_mblk;  // concurrent CTAs share the classifier tile
                     mblk = item % p.n_mblk;
                 }
+            } else if (p.sparse == 2) {
+                mblk = pass.vt_lo * 2 + item / p.n_nblk;
+                nblk = item % p.n_nblk;
             } else {
                 mblk = item / p.n_nblk;
                 nblk = item % p.n_nblk;
@@ -154,12 +192,66 @@ struct TileIter {
     }
 };
 
-// 32-wide activity mask of K blocks [kb0, kb0+32) for the current tile.
-__device__ __forceinline__ uint32_t kblock_mask(const EngineParams& p, int mblk, int kb0, int lane) {
-    const int kb = kb0 + lane;
-    bool act = kb < p.n_kblk;
-    if (act && p.kflags) act = p.kflags[(size_t)mblk * p.ld_kflags + kb] != 0;
-    return __ballot_sync(0xffffffffu, act);
+// The reduction of one output tile is a list of candidate 64-element K blocks; a candidate is
+// either taken (its operands are loaded and multiplied) or skipped.  Dense launches enumerate
+// K blocks 0..n_kblk-1 (skipped where a flag is clear); block-list launches enumerate the
+// (slot, sub-block) pairs of a row or column of the tile pool.
+struct KTile {
+    int n_cand;
+    int e0;  // first list entry (block-list forms)
+    int h;   // dC: which 128-column half of the 256-wide tile
+};
+struct KCoord {
+    int a_mn, a_k, b_mn, b_k;
+};
+
+template <int MODE>
+__device__ __forceinline__ KTile ktile_setup(const EngineParams& p, int mblk) {
+    KTile kt{p.n_kblk, 0, 0};
+    if (MODE == MODE_GEMM) {
+        if (p.sparse == 1) {
+            kt.e0 = 4 * p.row_ptr[mblk];
+            kt.n_cand = p.kcount[mblk];
+        } else if (p.sparse == 2) {
+            const int vt = mblk >> 1;
+            kt.h = mblk & 1;
+            const int c0 = p.col_ptr[vt];
+            kt.e0 = 4 * c0 + 2 * kt.h * (p.col_ptr[vt + 1] - c0);
+            kt.n_cand = p.kcount[mblk];
+        }
+    }
+    return kt;
+}
+
+// Is candidate `cand` of this tile taken, and where are its operands?
+template <int MODE>
+__device__ __forceinline__ bool kcand_eval(const EngineParams& p, const KTile& kt, int mblk, int nblk,
+                                           int cand, KCoord& kc) {
+    if (cand >= kt.n_cand) return false;
+    if (MODE == MODE_GEMM && p.sparse == 1) {  // A = pool tile (K-major), B = classifier rows (MN-major)
+        const int2 ent = p.klist[kt.e0 + cand];
+        const int sl = ent.x >> 2, kb = ent.x & 3;
+        kc.a_mn = sl * BM;
+        kc.a_k = kb * BK;
+        kc.b_mn = nblk * BN;
+        kc.b_k = ent.y * BN + kb * BK;
+        return true;
+    }
+    if (MODE == MODE_GEMM && p.sparse == 2) {  // A = pool tile (MN-major), B = embedding rows (MN-major)
+        const int2 ent = p.klist[kt.e0 + cand];
+        const int sl = ent.x >> 1, kb = ent.x & 1;
+        kc.a_mn = kt.h * 128;
+        kc.a_k = sl * BM + kb * BK;
+        kc.b_mn = nblk * BN;
+        kc.b_k = ent.y * BM + kb * BK;
+        return true;
+    }
+    if (MODE == MODE_GEMM && p.kflags && !p.kflags[(size_t)mblk * p.ld_kflags + cand]) return false;
+    kc.a_mn = p.a_mn_off + mblk * BM;
+    kc.a_k = p.a_k_off + cand * BK;
+    kc.b_mn = p.b_mn_off + nblk * BN;
+    kc.b_k = p.b_k_off + cand * BK;
+    return true;
 }
 
 template <int MODE>
@@ -168,15 +260,21 @@ __device__ void producer_loop(const CUtensorMap* tmA, const CUtensorMap* tmB, co
     const int lane = threadIdx.x & 31;
     int stage = 0;
     uint32_t phase = 0;
-    TileIter<MODE> it(p);
+    const PassInfo pass = load_pass(p);
+    TileIter<MODE> it(p, pass);
     while (it.next()) {
-        for (int kb0 = 0; kb0 < p.n_kblk; kb0 += 32) {
-            uint32_t mask = (MODE == MODE_GEMM) ? kblock_mask(p, it.mblk, kb0, lane)
-                                                : (p.n_kblk - kb0 >= 32 ? 0xffffffffu
-                                                                        : ((1u << (p.n_kblk - kb0)) - 1u));
+        const KTile kt = ktile_setup<MODE>(p, it.mblk);
+        for (int base = 0; base < kt.n_cand; base += 32) {
+            KCoord kc{0, 0, 0, 0};
+            const bool take = kcand_eval<MODE>(p, kt, it.mblk, it.nblk, base + lane, kc);
+            uint32_t mask = __ballot_sync(0xffffffffu, take);
             while (mask) {
-                const int kb = kb0 + __ffs(mask) - 1;
+                const int src = __ffs(mask) - 1;
                 mask &= mask - 1;
+                const int a_mn = __shfl_sync(0xffffffffu, kc.a_mn, src);
+                const int a_k = __shfl_sync(0xffffffffu, kc.a_k, src);
+                const int b_mn = __shfl_sync(0xffffffffu, kc.b_mn, src);
+                const int b_k = __shfl_sync(0xffffffffu, kc.b_k, src);
                 int ok = 1;
                 if (lane == 0) {
                     ok = mbar_wait(smem_u32(&s.empty[stage]), phase ^ 1u, s.abort_flag, p.status,
@@ -187,20 +285,18 @@ __device__ void producer_loop(const CUtensorMap* tmA, const CUtensorMap* tmB, co
                         const uint32_t sb = sa + A_BYTES;
                         mbar_expect_tx(bar, STAGE_BYTES);
                         if (!p.a_mn_major) {
-                            tma_load_2d(sa, tmA, bar, p.a_k_off + kb * BK, p.a_mn_off + it.mblk * BM);
+                            tma_load_2d(sa, tmA, bar, a_k, a_mn);
                         } else {
 #pragma unroll
                             for (int j = 0; j < BM / 64; ++j)
-                                tma_load_2d(sa + j * ATOM_BYTES, tmA, bar,
-                                            p.a_mn_off + it.mblk * BM + j * 64, p.a_k_off + kb * BK);
+                                tma_load_2d(sa + j * ATOM_BYTES, tmA, bar, a_mn + j * 64, a_k);
                         }
                         if (!p.b_mn_major) {
-                            tma_load_2d(sb, tmB, bar, p.b_k_off + kb * BK, p.b_mn_off + it.nblk * BN);
+                            tma_load_2d(sb, tmB, bar, b_k, b_mn);
                         } else {
 #pragma unroll
                             for (int j = 0; j < BN / 64; ++j)
-                                tma_load_2d(sb + j * ATOM_BYTES, tmB, bar,
-                                            p.b_mn_off + it.nblk * BN + j * 64, p.b_k_off + kb * BK);
+                                tma_load_2d(sb + j * ATOM_BYTES, tmB, bar, b_mn + j * 64, b_k);
                         }
                     }
                 }
@@ -226,7 +322,8 @@ __device__ void mma_loop(const EngineParams& p, const EngineSmem& s, uint32_t tm
     const uint32_t a_lbo = p.a_mn_major ? ATOM_BYTES : 16, b_lbo = p.b_mn_major ? ATOM_BYTES : 16;
     const uint32_t a_kstep = p.a_mn_major ? (UMMA_K / 8) * 1024 : UMMA_K * 2;  // bytes per UMMA_K
     const uint32_t b_kstep = p.b_mn_major ? (UMMA_K / 8) * 1024 : UMMA_K * 2;
-    TileIter<MODE> it(p);
+    const PassInfo pass = load_pass(p);
+    TileIter<MODE> it(p, pass);
     while (it.next()) {
         int ok = 1;
         if (lane == 0) {
@@ -238,10 +335,11 @@ __device__ void mma_loop(const EngineParams& p, const EngineSmem& s, uint32_t tm
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         int n_issued = 0;
-        for (int kb0 = 0; kb0 < p.n_kblk; kb0 += 32) {
-            uint32_t mask = (MODE == MODE_GEMM) ? kblock_mask(p, it.mblk, kb0, lane)
-                                                : (p.n_kblk - kb0 >= 32 ? 0xffffffffu
-                                                                        : ((1u << (p.n_kblk - kb0)) - 1u));
+        const KTile kt = ktile_setup<MODE>(p, it.mblk);
+        for (int base = 0; base < kt.n_cand; base += 32) {
+            KCoord kc{0, 0, 0, 0};
+            const bool take = kcand_eval<MODE>(p, kt, it.mblk, it.nblk, base + lane, kc);
+            uint32_t mask = __ballot_sync(0xffffffffu, take);
             while (mask) {
                 mask &= mask - 1;
                 if (lane == 0) {
@@ -319,7 +417,8 @@ __device__ void epilogue_loop(const EngineParams& p, const EngineSmem& s, uint32
     // MODE_LSE running state (log2 units)
     float run_m = -INFINITY, run_s = 0.0f;
 
-    TileIter<MODE> it(p);
+    const PassInfo pass = load_pass(p);
+    TileIter<MODE> it(p, pass);
     while (it.next()) {
         const int row = it.mblk * BM + q * 32 + lane;
         const bool row_ok = row < p.M;
@@ -366,7 +465,8 @@ __device__ void epilogue_loop(const EngineParams& p, const EngineSmem& s, uint32
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
                 const int col0 = it.nblk * BN + c * 32;  // column within this launch
-                if (col0 >= p.N) break;                 // warp-uniform
+                // warp-uniform; a pool slot is written in full (zeros past N) so no stale data stays in it
+                if (col0 >= p.N && !(MODE == MODE_PGRAD && p.sparse)) break;
                 uint32_t r[32];
                 if (!(MODE == MODE_GEMM && acc_is_empty)) {
                     tmem_ld32(taddr + c * 32, r);
@@ -429,7 +529,12 @@ __device__ void epilogue_loop(const EngineParams& p, const EngineSmem& s, uint32
                         }
                         g[j] = row_ok ? d : 0.0f;
                     }
-                    if (row_ok) {
+                    if (p.sparse) {
+                        // pool slot: a dense 128x256 tile; rows past M are written as zeros
+                        char* dst = reinterpret_cast<char*>(p.g_out) +
+                                    (((size_t)it.slot * BM + q * 32 + lane) * BN + c * 32) * 2;
+                        store_g16(dst, g, p.g_is_bf16 != 0);
+                    } else if (row_ok) {
                         char* dst = reinterpret_cast<char*>(p.g_out) + ((size_t)row * p.ldg + col0) * 2;
                         store_g16(dst, g, p.g_is_bf16 != 0);
                     }
@@ -438,9 +543,14 @@ __device__ void epilogue_loop(const EngineParams& p, const EngineSmem& s, uint32
                         // publish at the end of each 64-column group, and at the tile's last chunk
                         if ((c & 1) || (col0 + 32 >= p.N)) {
                             if (flag_bits && lane == 0) {
-                                const int cb64 = it.nblk * (BN / 64) + (c >> 1);
-                                p.flag_e[(size_t)it.mblk * p.ld_flag_e + cb64] = 1;
-                                p.flag_c[(size_t)(cb64 >> 1) * p.ld_flag_c + it.mblk * 2 + (q >> 1)] = 1;
+                                if (p.sparse) {
+                                    p.sflag_e[it.slot * 4 + (c >> 1)] = 1;
+                                    p.sflag_c[it.slot * 4 + (c >> 2) * 2 + (q >> 1)] = 1;
+                                } else {
+                                    const int cb64 = it.nblk * (BN / 64) + (c >> 1);
+                                    p.flag_e[(size_t)it.mblk * p.ld_flag_e + cb64] = 1;
+                                    p.flag_c[(size_t)(cb64 >> 1) * p.ld_flag_c + it.mblk * 2 + (q >> 1)] = 1;
+                                }
                             }
                             flag_bits = 0;
                         }

@@ -137,17 +137,157 @@ __global__ void tile_mark_kernel(const float* __restrict__ tile_max, const float
     }
 }
 
-// Per vocabulary chunk, the compact list of active tiles: id = rb * tiles_per_chunk + tile-in-chunk.
-// Thread index runs vocabulary-tile-major so that neighbours in a list share classifier tiles.
-__global__ void tile_compact_kernel(const uint8_t* __restrict__ act, int n_rb, int n_vt, int tiles_per_chunk,
-                                    int* __restrict__ lists, int* __restrict__ counts) {
-    const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
-    if (i >= (long long)n_rb * n_vt) return;
-    const int vt = int(i / n_rb), rb = int(i % n_rb);
-    if (!act[(size_t)rb * n_vt + vt]) return;
-    const int ch = vt / tiles_per_chunk;
-    const int slot = atomicAdd(counts + ch, 1);
-    lists[(size_t)ch * n_rb * tiles_per_chunk + slot] = rb * tiles_per_chunk + (vt - ch * tiles_per_chunk);
+// Index of the active tiles (one block of 1024 threads; dynamic smem = (max(n_rb, n_vt) + 1) ints).
+// Slots number the active tiles column by column (vt ascending, then rb), so column vt owns the
+// contiguous slots [col_ptr[vt], col_ptr[vt+1]); row_slots lists each row block's slots with vt
+// ascending (CSR).  Passes split the columns greedily so that each pass holds at most `capacity`
+// slots: pass_info[4p..4p+3] = {vt_lo, vt_hi, slot_lo, slot_hi}; unused passes are empty.
+__global__ void tile_index_kernel(const uint8_t* __restrict__ act, int n_rb, int n_vt, int capacity,
+                                  int max_pass, int* __restrict__ col_ptr, int* __restrict__ slot_tile,
+                                  int* __restrict__ slot_of, int* __restrict__ row_ptr,
+                                  int* __restrict__ row_slots, int* __restrict__ pass_info) {
+    extern __shared__ int sm[];
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    const int lane = tid & 31, warp = tid >> 5, nwarp = nthr >> 5;
+    // columns: counts
+    for (int vt = tid; vt < n_vt; vt += nthr) {
+        int cnt = 0;
+        for (int rb = 0; rb < n_rb; ++rb) cnt += act[(size_t)rb * n_vt + vt] != 0;
+        sm[vt] = cnt;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int run = 0, pass = 0, pass_vt0 = 0, pass_s0 = 0;
+        for (int vt = 0; vt < n_vt; ++vt) {
+            const int cnt = sm[vt];
+            if (run - pass_s0 + cnt > capacity && pass + 1 < max_pass) {  // close the pass before this column
+                pass_info[4 * pass + 0] = pass_vt0;
+                pass_info[4 * pass + 1] = vt;
+                pass_info[4 * pass + 2] = pass_s0;
+                pass_info[4 * pass + 3] = run;
+                ++pass;
+                pass_vt0 = vt;
+                pass_s0 = run;
+            }
+            col_ptr[vt] = run;
+            sm[vt] = run;
+            run += cnt;
+        }
+        col_ptr[n_vt] = run;
+        pass_info[4 * pass + 0] = pass_vt0;
+        pass_info[4 * pass + 1] = n_vt;
+        pass_info[4 * pass + 2] = pass_s0;
+        pass_info[4 * pass + 3] = run;
+        for (int q = pass + 1; q < max_pass; ++q) {
+            pass_info[4 * q + 0] = n_vt;
+            pass_info[4 * q + 1] = n_vt;
+            pass_info[4 * q + 2] = run;
+            pass_info[4 * q + 3] = run;
+        }
+    }
+    __syncthreads();
+    // columns: slots
+    for (int vt = tid; vt < n_vt; vt += nthr) {
+        int k = sm[vt];
+        for (int rb = 0; rb < n_rb; ++rb) {
+            if (act[(size_t)rb * n_vt + vt]) {
+                slot_tile[k] = rb * n_vt + vt;
+                slot_of[(size_t)rb * n_vt + vt] = k;
+                ++k;
+            }
+        }
+    }
+    __syncthreads();
+    // rows: counts (one warp per row block)
+    for (int rb = warp; rb < n_rb; rb += nwarp) {
+        int cnt = 0;
+        for (int v0 = 0; v0 < n_vt; v0 += 32) {
+            const int vt = v0 + lane;
+            cnt += __popc(__ballot_sync(0xffffffffu, vt < n_vt && act[(size_t)rb * n_vt + vt]));
+        }
+        if (lane == 0) sm[rb] = cnt;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int run = 0;
+        for (int rb = 0; rb < n_rb; ++rb) {
+            const int cnt = sm[rb];
+            row_ptr[rb] = run;
+            sm[rb] = run;
+            run += cnt;
+        }
+        row_ptr[n_rb] = run;
+    }
+    __syncthreads();
+    // rows: slot lists
+    for (int rb = warp; rb < n_rb; rb += nwarp) {
+        int k = sm[rb];
+        for (int v0 = 0; v0 < n_vt; v0 += 32) {
+            const int vt = v0 + lane;
+            const bool on = vt < n_vt && act[(size_t)rb * n_vt + vt];
+            const uint32_t m = __ballot_sync(0xffffffffu, on);
+            if (on) row_slots[k + __popc(m & ((1u << lane) - 1u))] = slot_of[(size_t)rb * n_vt + vt];
+            k += __popc(m);
+        }
+    }
+}
+
+// After phase 1 of a pass: turn the slot flags into ordered K-block lists for the two products
+// (one warp per list).  Warps 0..n_rb-1 build the dE list of a row block: its slots that belong to
+// the pass, vt ascending, 4 column groups each.  The next 2*n_vt warps build the dC list of a
+// (vt, 128-column half): its slots, rb ascending, 2 row halves each.  Layout: see EngineParams.
+__global__ void klist_build_kernel(const int* __restrict__ pass_info, const int* __restrict__ row_ptr,
+                                   const int* __restrict__ row_slots, const int* __restrict__ col_ptr,
+                                   const int* __restrict__ slot_tile, int n_rb, int n_vt,
+                                   const uint8_t* __restrict__ sflag_e, const uint8_t* __restrict__ sflag_c,
+                                   int2* __restrict__ de_list, int* __restrict__ de_cnt,
+                                   int2* __restrict__ dc_list, int* __restrict__ dc_cnt) {
+    const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    const int vt_lo = pass_info[0], vt_hi = pass_info[1], s_lo = pass_info[2], s_hi = pass_info[3];
+    if (w < n_rb) {
+        const int e0 = row_ptr[w], n = (row_ptr[w + 1] - e0) * 4;
+        int2* out = de_list + 4 * e0;
+        int k = 0;
+        for (int c0 = 0; c0 < n; c0 += 32) {
+            const int c = c0 + lane;
+            bool on = false;
+            int2 ent = make_int2(0, 0);
+            if (c < n) {
+                const int slot = row_slots[e0 + (c >> 2)];
+                if (slot >= s_lo && slot < s_hi) {
+                    const int sl = slot - s_lo, kb = c & 3;
+                    on = sflag_e[sl * 4 + kb] != 0;
+                    ent = make_int2(sl * 4 + kb, slot_tile[slot] % n_vt);
+                }
+            }
+            const uint32_t m = __ballot_sync(0xffffffffu, on);
+            if (on) out[k + __popc(m & ((1u << lane) - 1u))] = ent;
+            k += __popc(m);
+        }
+        if (lane == 0) de_cnt[w] = k;
+    } else if (w < n_rb + 2 * n_vt) {
+        const int id = w - n_rb, vt = id >> 1, h = id & 1;
+        int k = 0;
+        if (vt >= vt_lo && vt < vt_hi) {
+            const int c0s = col_ptr[vt], ns = col_ptr[vt + 1] - c0s, n = ns * 2;
+            int2* out = dc_list + 4 * c0s + 2 * h * ns;
+            for (int c0 = 0; c0 < n; c0 += 32) {
+                const int c = c0 + lane;
+                bool on = false;
+                int2 ent = make_int2(0, 0);
+                if (c < n) {
+                    const int slot = c0s + (c >> 1), sl = slot - s_lo, kb = c & 1;
+                    on = sflag_c[sl * 4 + h * 2 + kb] != 0;
+                    ent = make_int2(sl * 2 + kb, slot_tile[slot] / n_vt);
+                }
+                const uint32_t m = __ballot_sync(0xffffffffu, on);
+                if (on) out[k + __popc(m & ((1u << lane) - 1u))] = ent;
+                k += __popc(m);
+            }
+        }
+        if (lane == 0) dc_cnt[id] = k;
+    }
 }
 
 // dbias[col] += sum_rows G[row][col] for a [n_rows][width] 16-bit block with pitch ldg.
