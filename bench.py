@@ -146,6 +146,12 @@ class ClockSampler:
         return out
 
 
+# DRAM bytes per launch of the forward kernel, as a multiple of its algorithmic bytes
+# 2*(B*D + V*D): measured once with ncu on the small profiling case (165 MB against 160 MB, see
+# profiles/engine_kernels_small-case_ncu_full.md) and scaled by the units a full launch processes.
+FORWARD_DRAM_TRAFFIC_RATIO = 1.031
+
+
 def measured_peak_tflops() -> tuple[float, str]:
     path = ROOT / "MEASURED_PEAKS.json"
     try:
@@ -395,7 +401,9 @@ def main() -> None:
             "loss": float(loss.item()),
             "roofline": {"bound": "tensor", "kernel": names[dom], "achieved": achieved, "peak": peak,
                          "unit": "TFLOP/s", "frac": (achieved / peak) if achieved else None, "peak_source": peak_src,
-                         "avg_launch_ms": avg_ms, "alg_flop_per_launch": alg_per_launch, "traffic": None},
+                         "avg_launch_ms": avg_ms, "alg_flop_per_launch": alg_per_launch,
+                         "traffic": (FORWARD_DRAM_TRAFFIC_RATIO * 2.0 * (n_valid * D + v_local * D)) if dom == 0 else None,
+                         "traffic_note": "bytes per launch, scaled from an ncu capture of a smaller case"},
             "kernels": per_kernel,
             "e2e": e2e,
             "gpu_launches": int(launches),

@@ -7,7 +7,6 @@ all-gather that merges per-rank (lse, correct logit), the fp32 all-reduce of dE,
 
 from __future__ import annotations
 
-import socket
 import sys
 from pathlib import Path
 
@@ -19,10 +18,42 @@ import torch.multiprocessing as mp
 ROOT = Path(__file__).resolve().parent.parent
 
 
-def _free_port() -> int:
-    with socket.socket() as s:
-        s.bind(("127.0.0.1", 0))
-        return s.getsockname()[1]
+def _run_ranks(target, world: int, args: tuple, timeout_s: float = 180.0) -> None:
+    """Start one process per rank, collect one message per rank, and never leave a rank behind:
+    whatever happens, children that are still alive are terminated before returning (a child
+    blocked in a rendezvous would otherwise keep the test process from exiting)."""
+    import queue
+    import tempfile
+    import time
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    with tempfile.TemporaryDirectory() as tmp:
+        init_method = f"file://{tmp}/rendezvous"
+        procs = [ctx.Process(target=target, args=(r, world, init_method, *args, q), daemon=True) for r in range(world)]
+        for p in procs:
+            p.start()
+        results, deadline = [], time.monotonic() + timeout_s
+        try:
+            while len(results) < world and time.monotonic() < deadline:
+                try:
+                    results.append(q.get(timeout=1.0))
+                except queue.Empty:
+                    if any(p.exitcode not in (None, 0) for p in procs):
+                        break  # a rank died without reporting: do not wait for its peers
+        finally:
+            for p in procs:
+                p.join(timeout=10 if len(results) == world else 0.1)
+            for p in procs:
+                if p.is_alive():
+                    p.terminate()
+            for p in procs:
+                p.join(timeout=5)
+                if p.is_alive():
+                    p.kill()
+    assert len(results) == world, f"only {len(results)} of {world} ranks reported: {results}"
+    for rank, msg in sorted(results):
+        assert msg == "ok", f"rank {rank}: {msg}"
 
 
 def _install_cpu_stand_ins():
@@ -75,10 +106,13 @@ def _install_cpu_stand_ins():
     nat.make_operands = None
 
 
-def _worker(rank: int, world: int, port: int, reduce_e_grad: bool, out_q):
+def _worker(rank: int, world: int, init_method: str, reduce_e_grad: bool, out_q):
     for p in (ROOT / "ml-cross-entropy_b200", ROOT, ROOT / "tests"):
         sys.path.insert(0, str(p))
-    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    import datetime
+
+    dist.init_process_group("gloo", init_method=init_method, rank=rank, world_size=world,
+                            timeout=datetime.timedelta(seconds=120))
     try:
         from oracle import cce_oracle as O
 
@@ -135,15 +169,25 @@ def _worker(rank: int, world: int, port: int, reduce_e_grad: bool, out_q):
 
 @pytest.mark.parametrize("reduce_e_grad", [True, False])
 def test_vocab_parallel_two_ranks_gloo(reduce_e_grad):
-    world = 2
-    ctx = mp.get_context("spawn")
-    q = ctx.Queue()
-    port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, reduce_e_grad, q)) for r in range(world)]
-    for p in procs:
-        p.start()
-    results = [q.get(timeout=120) for _ in range(world)]
-    for p in procs:
-        p.join(timeout=60)
-    for rank, msg in sorted(results):
-        assert msg == "ok", f"rank {rank}: {msg}"
+    _run_ranks(_worker, 2, (reduce_e_grad,))
+
+
+def _worker_rank1_dies(rank: int, world: int, init_method: str, q):
+    """Rank 1 exits before the rendezvous; rank 0 would wait for it (up to the group timeout)."""
+    if rank == 1:
+        raise SystemExit(3)
+    import datetime
+
+    dist.init_process_group("gloo", init_method=init_method, rank=rank, world_size=world,
+                            timeout=datetime.timedelta(seconds=120))
+    q.put((rank, "ok"))
+
+
+def test_a_dead_rank_fails_the_test_quickly_and_leaves_no_process_behind():
+    import time
+
+    t0 = time.monotonic()
+    with pytest.raises(AssertionError, match="ranks reported"):
+        _run_ranks(_worker_rank1_dies, 2, ())
+    assert time.monotonic() - t0 < 60
+    assert not [p for p in mp.active_children() if p.is_alive()]
