@@ -363,7 +363,7 @@ BwdPlan plan_bwd(const cce_b200_backward_args* a) {
     const long long total_tiles = (long long)pl.n_rb * pl.n_vt;
     long long cap = gbuf_cap_bytes() / (long long)kSlotBytes;
     if (cap > total_tiles) cap = total_tiles;
-    pl.sparse = wants_sparse(a) && total_tiles > 0 && cap >= 2LL * pl.n_rb && std::max(pl.n_rb, pl.n_vt) < 12000;
+    pl.sparse = wants_sparse(a) && total_tiles > 0 && cap >= 2LL * pl.n_rb && pl.n_rb + pl.n_vt < 12000;
     if (pl.sparse) {
         pl.capacity = int(cap);
         pl.max_pass = int(total_tiles / (cap - pl.n_rb + 1)) + 2;
@@ -636,7 +636,6 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
     int* status = reinterpret_cast<int*>(ws);
     char* g_buf = ws + pl.off_g;
     float* de32 = reinterpret_cast<float*>(ws + pl.off_de32);
-    if (a->d_e) CCE_CUDA(cudaMemsetAsync(de32, 0, (size_t)B * D * 4, st));  // every product adds with red
 
     // operand maps that do not change from chunk to chunk
     CUtensorMap tmE_k, tmC_k, tmE_mn, tmC_mn;
@@ -694,7 +693,7 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
             a->tile_max, minlse, n_groups, pl.n_vt, log2f(a->filter_eps), reinterpret_cast<const long long*>(a->targets),
             op->valids, op->valids_dtype == CCE_IDX_I64, a->shift, a->vocab_start, V, B, act);
         CCE_LAUNCH_CHECK();
-        const size_t sm_bytes = (size_t)(std::max(pl.n_rb, pl.n_vt) + 1) * sizeof(int);
+        const size_t sm_bytes = (size_t)(pl.n_rb + pl.n_vt + 2) * sizeof(int);
         tile_index_kernel<<<1, 1024, sm_bytes, st>>>(act, pl.n_rb, pl.n_vt, pl.capacity, pl.max_pass, col_ptr, slot_tile,
                                                     slot_of, row_ptr, row_slots, pass_info);
         CCE_LAUNCH_CHECK();
@@ -746,7 +745,7 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
                 p.out = de32;
                 p.ldo = D;
                 p.out_dtype = CCE_DT_F32;
-                p.accumulate = 2;
+                p.accumulate = ps == 0 ? 0 : 2;  // the first pass stores every tile, later passes add with red
                 p.sparse = 1;
                 p.pass_info = pinfo;
                 p.slot_tile = slot_tile;
@@ -812,7 +811,7 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
                 p.out = de32;
                 p.ldo = D;
                 p.out_dtype = CCE_DT_F32;
-                p.accumulate = 2;  // fp32 scratch was zeroed above; every chunk adds with vector red
+                p.accumulate = ch == 0 ? 0 : 2;  // the first chunk stores every tile, later chunks add with red
                 if (a->has_filter && a->filter_e) {
                     p.kflags = flag_e;
                     p.ld_kflags = pl.ld_flag_e;

@@ -462,22 +462,22 @@ __device__ void epilogue_loop(const EngineParams& p, const EngineSmem& s, uint32
             // nothing to add
         } else {
             uint32_t flag_bits = 0;  // MODE_PGRAD: activity of the current 64-column group
+            // TMEM -> registers is double-buffered: the load of chunk c+1 is in flight while chunk c
+            // is processed (tcgen05.wait::ld waits for every load issued so far).
+            const bool from_tmem = !(MODE == MODE_GEMM && acc_is_empty);
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
                 const int col0 = it.nblk * BN + c * 32;  // column within this launch
                 // warp-uniform; a pool slot is written in full (zeros past N) so no stale data stays in it
                 if (col0 >= p.N && !(MODE == MODE_PGRAD && p.sparse)) break;
                 uint32_t r[32];
-                if (!(MODE == MODE_GEMM && acc_is_empty)) {
+                if (from_tmem) {
                     tmem_ld32(taddr + c * 32, r);
                     tmem_ld_wait();
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) r[j] = 0u;
                 }
                 float x[32];
 #pragma unroll
-                for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(r[j]);
+                for (int j = 0; j < 32; ++j) x[j] = from_tmem ? __uint_as_float(r[j]) : 0.0f;
 
                 if (MODE == MODE_LSE || MODE == MODE_PGRAD) {
                     if (p.bias) {

@@ -137,7 +137,7 @@ __global__ void tile_mark_kernel(const float* __restrict__ tile_max, const float
     }
 }
 
-// Index of the active tiles (one block of 1024 threads; dynamic smem = (max(n_rb, n_vt) + 1) ints).
+// Index of the active tiles (one block of 1024 threads; dynamic smem = (n_vt + n_rb + 2) ints).
 // Slots number the active tiles column by column (vt ascending, then rb), so column vt owns the
 // contiguous slots [col_ptr[vt], col_ptr[vt+1]); row_slots lists each row block's slots with vt
 // ascending (CSR).  Passes split the columns greedily so that each pass holds at most `capacity`
@@ -147,19 +147,28 @@ __global__ void tile_index_kernel(const uint8_t* __restrict__ act, int n_rb, int
                                   int* __restrict__ slot_of, int* __restrict__ row_ptr,
                                   int* __restrict__ row_slots, int* __restrict__ pass_info) {
     extern __shared__ int sm[];
+    int* col_s = sm;              // [n_vt + 1] column counts, then column starts
+    int* row_s = sm + n_vt + 1;   // [n_rb + 1] row counts, then row starts
     const int tid = threadIdx.x, nthr = blockDim.x;
     const int lane = tid & 31, warp = tid >> 5, nwarp = nthr >> 5;
-    // columns: counts
+    for (int rb = tid; rb < n_rb; rb += nthr) row_s[rb] = 0;
+    __syncthreads();
+    // per-column counts (thread per column; neighbouring threads read neighbouring bytes)
     for (int vt = tid; vt < n_vt; vt += nthr) {
         int cnt = 0;
-        for (int rb = 0; rb < n_rb; ++rb) cnt += act[(size_t)rb * n_vt + vt] != 0;
-        sm[vt] = cnt;
+        for (int rb = 0; rb < n_rb; ++rb) {
+            if (act[(size_t)rb * n_vt + vt]) {
+                ++cnt;
+                atomicAdd(&row_s[rb], 1);
+            }
+        }
+        col_s[vt] = cnt;
     }
     __syncthreads();
-    if (tid == 0) {
+    if (tid == 0) {  // column starts and the pass boundaries
         int run = 0, pass = 0, pass_vt0 = 0, pass_s0 = 0;
         for (int vt = 0; vt < n_vt; ++vt) {
-            const int cnt = sm[vt];
+            const int cnt = col_s[vt];
             if (run - pass_s0 + cnt > capacity && pass + 1 < max_pass) {  // close the pass before this column
                 pass_info[4 * pass + 0] = pass_vt0;
                 pass_info[4 * pass + 1] = vt;
@@ -170,7 +179,7 @@ __global__ void tile_index_kernel(const uint8_t* __restrict__ act, int n_rb, int
                 pass_s0 = run;
             }
             col_ptr[vt] = run;
-            sm[vt] = run;
+            col_s[vt] = run;
             run += cnt;
         }
         col_ptr[n_vt] = run;
@@ -184,11 +193,20 @@ __global__ void tile_index_kernel(const uint8_t* __restrict__ act, int n_rb, int
             pass_info[4 * q + 2] = run;
             pass_info[4 * q + 3] = run;
         }
+    } else if (tid == 32) {  // row starts
+        int run = 0;
+        for (int rb = 0; rb < n_rb; ++rb) {
+            const int cnt = row_s[rb];
+            row_ptr[rb] = run;
+            row_s[rb] = run;
+            run += cnt;
+        }
+        row_ptr[n_rb] = run;
     }
     __syncthreads();
-    // columns: slots
+    // slots, column by column
     for (int vt = tid; vt < n_vt; vt += nthr) {
-        int k = sm[vt];
+        int k = col_s[vt];
         for (int rb = 0; rb < n_rb; ++rb) {
             if (act[(size_t)rb * n_vt + vt]) {
                 slot_tile[k] = rb * n_vt + vt;
@@ -198,36 +216,28 @@ __global__ void tile_index_kernel(const uint8_t* __restrict__ act, int n_rb, int
         }
     }
     __syncthreads();
-    // rows: counts (one warp per row block)
+    // row lists (one warp per row block, 128 columns per step, order kept by an in-warp scan)
     for (int rb = warp; rb < n_rb; rb += nwarp) {
-        int cnt = 0;
-        for (int v0 = 0; v0 < n_vt; v0 += 32) {
-            const int vt = v0 + lane;
-            cnt += __popc(__ballot_sync(0xffffffffu, vt < n_vt && act[(size_t)rb * n_vt + vt]));
-        }
-        if (lane == 0) sm[rb] = cnt;
-    }
-    __syncthreads();
-    if (tid == 0) {
-        int run = 0;
-        for (int rb = 0; rb < n_rb; ++rb) {
-            const int cnt = sm[rb];
-            row_ptr[rb] = run;
-            sm[rb] = run;
-            run += cnt;
-        }
-        row_ptr[n_rb] = run;
-    }
-    __syncthreads();
-    // rows: slot lists
-    for (int rb = warp; rb < n_rb; rb += nwarp) {
-        int k = sm[rb];
-        for (int v0 = 0; v0 < n_vt; v0 += 32) {
-            const int vt = v0 + lane;
-            const bool on = vt < n_vt && act[(size_t)rb * n_vt + vt];
-            const uint32_t m = __ballot_sync(0xffffffffu, on);
-            if (on) row_slots[k + __popc(m & ((1u << lane) - 1u))] = slot_of[(size_t)rb * n_vt + vt];
-            k += __popc(m);
+        int k = row_s[rb];
+        for (int v0 = 0; v0 < n_vt; v0 += 128) {
+            uint32_t bits = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int vt = v0 + lane * 4 + j;
+                if (vt < n_vt && act[(size_t)rb * n_vt + vt]) bits |= 1u << j;
+            }
+            const int c = __popc(bits);
+            int incl = c;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += t;
+            }
+            int pos = k + incl - c;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (bits & (1u << j)) row_slots[pos++] = slot_of[(size_t)rb * n_vt + v0 + lane * 4 + j];
+            k += __shfl_sync(0xffffffffu, incl, 31);
         }
     }
 }
