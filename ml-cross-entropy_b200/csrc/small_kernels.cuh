@@ -156,10 +156,16 @@ __global__ void tile_index_kernel(const uint8_t* __restrict__ act, int n_rb, int
     // per-column counts (thread per column; neighbouring threads read neighbouring bytes)
     for (int vt = tid; vt < n_vt; vt += nthr) {
         int cnt = 0;
-        for (int rb = 0; rb < n_rb; ++rb) {
-            if (act[(size_t)rb * n_vt + vt]) {
-                ++cnt;
-                atomicAdd(&row_s[rb], 1);
+        for (int rb0 = 0; rb0 < n_rb; rb0 += 8) {  // 8 independent loads in flight per step
+            uint8_t v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = (rb0 + j < n_rb) ? act[(size_t)(rb0 + j) * n_vt + vt] : 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (v[j]) {
+                    ++cnt;
+                    atomicAdd(&row_s[rb0 + j], 1);
+                }
             }
         }
         col_s[vt] = cnt;
@@ -207,11 +213,17 @@ __global__ void tile_index_kernel(const uint8_t* __restrict__ act, int n_rb, int
     // slots, column by column
     for (int vt = tid; vt < n_vt; vt += nthr) {
         int k = col_s[vt];
-        for (int rb = 0; rb < n_rb; ++rb) {
-            if (act[(size_t)rb * n_vt + vt]) {
-                slot_tile[k] = rb * n_vt + vt;
-                slot_of[(size_t)rb * n_vt + vt] = k;
-                ++k;
+        for (int rb0 = 0; rb0 < n_rb; rb0 += 8) {
+            uint8_t v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = (rb0 + j < n_rb) ? act[(size_t)(rb0 + j) * n_vt + vt] : 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (v[j]) {
+                    slot_tile[k] = (rb0 + j) * n_vt + vt;
+                    slot_of[(size_t)(rb0 + j) * n_vt + vt] = k;
+                    ++k;
+                }
             }
         }
     }
