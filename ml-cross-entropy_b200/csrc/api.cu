@@ -12,6 +12,7 @@
 #include <vector>
 
 #include "engine.cuh"
+#include "engine_pair.cuh"
 #include "small_kernels.cuh"
 
 using namespace cce;
@@ -71,6 +72,15 @@ EncodeTiledFn get_encode() {
     return fn;
 }
 
+// CCE_B200_LSE_PAIR=1 selects the two-CTA (cta_group::2) forward kernel; read once.
+bool use_cta_pairs() {
+    static const bool on = [] {
+        const char* env = getenv("CCE_B200_LSE_PAIR");
+        return env && env[0] == '1';
+    }();
+    return on;
+}
+
 struct DeviceInfo {
     int sms = 0;
     int cc_major = 0;
@@ -98,6 +108,7 @@ int device_info(DeviceInfo** out) {
                                       ENGINE_SMEM));
         CCE_CUDA(cudaFuncSetAttribute(engine_kernel<MODE_GEMM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       ENGINE_SMEM));
+        CCE_CUDA(cudaFuncSetAttribute(lse_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM));
         d.attr_set = true;
     }
     *out = &d;
@@ -549,8 +560,35 @@ int cce_b200_lse_forward(const cce_b200_operands* op, float* lse, float* tile_ma
     p.band_len = pl.band_len;
     p.partial = reinterpret_cast<float2*>(ws + pl.off_partial);
     p.tile_max = tile_max;
-    rc = launch_engine<MODE_LSE>(tmA, tmB, p, dev->sms, st);
-    if (rc != CCE_OK) return rc;
+    if (use_cta_pairs()) {
+        // two-CTA form: each CTA of a pair stages 128 rows of each operand, the MMA is M = 256
+        rc = make_tmap(&tmB, sg.c, op->dtype, sg.Dk, op->V, sg.ldc, BK, BN / 2);
+        if (rc != CCE_OK) return rc;
+        p.idesc = make_idesc(op->dtype == CCE_DT_BF16 ? 1u : 0u, 0, 0, 2 * BM, BN);
+        const long long items = cdiv(p.n_nblk, p.band_len) * cdiv(p.n_mblk, 2);
+        const long long pairs = std::min<long long>(items, dev->sms / 2);
+        ProfRecord rec{nullptr, nullptr, MODE_LSE};
+        bool prof = false;
+        {
+            std::lock_guard<std::mutex> lock(g_prof_mu);
+            prof = g_prof_on;
+        }
+        if (prof) {
+            CCE_CUDA(cudaEventCreate(&rec.start));
+            CCE_CUDA(cudaEventCreate(&rec.stop));
+            CCE_CUDA(cudaEventRecord(rec.start, st));
+        }
+        lse_pair_kernel<<<(unsigned)(2 * pairs), ENGINE_THREADS, PAIR_SMEM, st>>>(tmA, tmB, p);
+        CCE_LAUNCH_CHECK();
+        if (prof) {
+            CCE_CUDA(cudaEventRecord(rec.stop, st));
+            std::lock_guard<std::mutex> lock(g_prof_mu);
+            g_prof.push_back(rec);
+        }
+    } else {
+        rc = launch_engine<MODE_LSE>(tmA, tmB, p, dev->sms, st);
+        if (rc != CCE_OK) return rc;
+    }
 
     lse_combine_kernel<<<(unsigned)cdiv(op->n_rows, 256), 256, 0, st>>>(p.partial, pl.n_band, op->n_rows, lse);
     CCE_LAUNCH_CHECK();

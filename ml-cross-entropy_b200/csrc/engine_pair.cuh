@@ -1,0 +1,301 @@
+// Forward log-sum-exp on CTA pairs (tcgen05 cta_group::2).
+//
+// A cluster of two CTAs computes one 256-row x 256-column logit tile per step: CTA r of the pair
+// loads rows [128r, 128r+128) of the embedding block and rows [128r, 128r+128) of the classifier
+// tile, the leader (rank 0) issues one M=256 MMA per K step that reads both CTAs' shared memory,
+// and each CTA's TMEM receives the accumulator of its own 128 rows.  Per FLOP a CTA stages a third
+// less operand data than the single-CTA pipeline (32 KB instead of 48 KB per 128x256x64 step).
+// Roles per CTA as in engine.cuh: warp 0 TMA producer, warp 1 MMA issuer (leader only) and TMEM
+// owner, warps 2..5 epilogue.  Same outputs as engine_kernel<MODE_LSE>.
+#pragma once
+#include "engine.cuh"
+#include "ptx_pair.cuh"
+
+namespace cce {
+
+constexpr int P_NSTAGE = 6;
+constexpr int P_A_BYTES = BM * BK * 2;         // 128 rows of E
+constexpr int P_B_BYTES = (BN / 2) * BK * 2;   // 128 of the tile's 256 classifier rows
+constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
+constexpr int PAIR_SMEM = P_NSTAGE * P_STAGE_BYTES + 1024 + 256;
+
+struct PairIter {
+    const EngineParams& p;
+    int item, n_items, stride, sub, sub_end;
+    int rb2, nblk, band;
+    bool first, last;
+    __device__ PairIter(const EngineParams& p_) : p(p_) {
+        stride = int(gridDim.x >> 1);
+        item = int(blockIdx.x >> 1) - stride;
+        sub = sub_end = 0;
+        const int n_band = (p.n_nblk + p.band_len - 1) / p.band_len;
+        n_items = n_band * ((p.n_mblk + 1) >> 1);
+    }
+    __device__ bool next() {
+        if (sub + 1 < sub_end) {
+            ++sub;
+        } else {
+            item += stride;
+            if (item >= n_items) return false;
+            const int n_rb2 = (p.n_mblk + 1) >> 1;
+            band = item / n_rb2;
+            rb2 = item % n_rb2;
+            sub = band * p.band_len;
+            sub_end = min(p.n_nblk, sub + p.band_len);
+        }
+        nblk = sub;
+        first = (sub == band * p.band_len);
+        last = (sub + 1 == sub_end);
+        return true;
+    }
+};
+
+struct PairSmem {
+    uint8_t* stages;
+    uint64_t* full;    // [P_NSTAGE] leader only: both CTAs' TMA bytes -> MMA
+    uint64_t* empty;   // [P_NSTAGE] per CTA: MMA -> this CTA's producer
+    uint64_t* tfull;   // [2] per CTA: MMA -> this CTA's epilogue
+    uint64_t* tempty;  // [2] leader only: both CTAs' epilogues -> MMA
+    uint64_t* tdown;
+    uint32_t* tmem_base;
+    int* abort_flag;
+};
+
+__device__ void pair_producer(const CUtensorMap* tmA, const CUtensorMap* tmB, const EngineParams& p,
+                              const PairSmem& s, uint32_t rank) {
+    const int lane = threadIdx.x & 31;
+    int stage = 0;
+    uint32_t phase = 0;
+    PairIter it(p);
+    while (it.next()) {
+        const int a_row = (it.rb2 * 2 + int(rank)) * BM;
+        const int b_row = it.nblk * BN + int(rank) * (BN / 2);
+        for (int kb = 0; kb < p.n_kblk; ++kb) {
+            int ok = 1;
+            if (lane == 0) {
+                ok = mbar_wait(smem_u32(&s.empty[stage]), phase ^ 1u, s.abort_flag, p.status, ERR_WAIT_SMEM_EMPTY);
+                if (ok) {
+                    const uint32_t bar_local = smem_u32(&s.full[stage]);
+                    const uint32_t bar_leader = map_to_cta(bar_local, 0);
+                    const uint32_t sa = smem_u32(s.stages + stage * P_STAGE_BYTES);
+                    if (rank == 0) mbar_expect_tx(bar_local, 2 * P_STAGE_BYTES);  // bytes of both CTAs
+                    tma_load_2d_pair(sa, tmA, bar_leader, kb * BK, a_row);
+                    tma_load_2d_pair(sa + P_A_BYTES, tmB, bar_leader, kb * BK, b_row);
+                }
+            }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) return;
+            if (++stage == P_NSTAGE) {
+                stage = 0;
+                phase ^= 1u;
+            }
+        }
+    }
+}
+
+// leader CTA only
+__device__ void pair_mma(const EngineParams& p, const PairSmem& s, uint32_t tmem_base) {
+    const int lane = threadIdx.x & 31;
+    int stage = 0;
+    uint32_t phase = 0;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    PairIter it(p);
+    while (it.next()) {
+        int ok = 1;
+        if (lane == 0)
+            ok = mbar_wait(smem_u32(&s.tempty[acc]), acc_phase ^ 1u, s.abort_flag, p.status, ERR_WAIT_TMEM_EMPTY);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) return;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < p.n_kblk; ++kb) {
+            if (lane == 0) {
+                ok = mbar_wait(smem_u32(&s.full[stage]), phase, s.abort_flag, p.status, ERR_WAIT_SMEM_FULL);
+                if (ok) {
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(s.stages + stage * P_STAGE_BYTES);
+                    const uint32_t sb = sa + P_A_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        const uint64_t ad = make_smem_desc(sa + k * UMMA_K * 2, 16, 1024);
+                        const uint64_t bd = make_smem_desc(sb + k * UMMA_K * 2, 16, 1024);
+                        tc_mma_f16_pair(d_tmem, ad, bd, p.idesc, (kb | k) ? 1u : 0u);
+                    }
+                    // the stage is free in both CTAs once these MMAs have read it
+                    const uint32_t eb = smem_u32(&s.empty[stage]);
+                    tc_commit_pair(eb);
+                    tc_commit_pair(map_to_cta(eb, 1));
+                }
+            }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) return;
+            if (++stage == P_NSTAGE) {
+                stage = 0;
+                phase ^= 1u;
+            }
+        }
+        if (lane == 0) {
+            const uint32_t tb = smem_u32(&s.tfull[acc]);
+            tc_commit_pair(tb);
+            tc_commit_pair(map_to_cta(tb, 1));
+        }
+        __syncwarp();
+        if (++acc == 2) {
+            acc = 0;
+            acc_phase ^= 1u;
+        }
+    }
+}
+
+__device__ void pair_epilogue(const EngineParams& p, const PairSmem& s, uint32_t tmem_base, uint32_t rank) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, q = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const float inv_softcap = p.has_softcap ? 1.0f / p.softcap : 0.0f;
+    float run_m = -INFINITY, run_s = 0.0f;
+    PairIter it(p);
+    while (it.next()) {
+        const int mblk = it.rb2 * 2 + int(rank);
+        const int row = mblk * BM + q * 32 + lane;
+        const bool row_ok = row < p.M;
+        if (it.first) {
+            run_m = -INFINITY;
+            run_s = 0.0f;
+        }
+        int ok = mbar_wait(smem_u32(&s.tfull[acc]), acc_phase, s.abort_flag, p.status, ERR_WAIT_TMEM_FULL);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) return;
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + acc * BN + (uint32_t(q * 32) << 16);
+        float tile_rowmax = -INFINITY;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+            const int col0 = it.nblk * BN + c * 32;
+            if (col0 >= p.N) break;
+            uint32_t r[32];
+            tmem_ld32(taddr + c * 32, r);
+            tmem_ld_wait();
+            float x[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(r[j]);
+            if (p.bias) {
+                const float* bp = p.bias + col0;
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (col0 + j < p.N) x[j] += __ldg(bp + j);
+            }
+            if (p.has_softcap) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) x[j] = apply_softcap(x[j], p.softcap, inv_softcap);
+            }
+            float cmax = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                x[j] = (col0 + j < p.N) ? x[j] * kLog2e : -INFINITY;
+                cmax = fmaxf(cmax, x[j]);
+            }
+            tile_rowmax = fmaxf(tile_rowmax, cmax);
+            if (cmax > run_m) {
+                run_s *= ex2f(run_m - cmax);
+                run_m = cmax;
+            }
+            if (run_m > -INFINITY) {
+                float acc_s = 0.0f;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) acc_s += ex2f(x[j] - run_m);
+                run_s += acc_s;
+            }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&s.tempty[acc]), 0));
+        if (p.tile_max && mblk < p.n_mblk) {
+            float m = row_ok ? tile_rowmax : -INFINITY;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+            if (lane == 0) p.tile_max[(size_t)(mblk * 4 + q) * p.n_nblk + it.nblk] = m;
+        }
+        if (++acc == 2) {
+            acc = 0;
+            acc_phase ^= 1u;
+        }
+        if (it.last && row_ok) p.partial[(size_t)it.band * p.M + row] = make_float2(run_m, run_s);
+    }
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(ENGINE_THREADS, 1)
+lse_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                const EngineParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    PairSmem s;
+    s.stages = base;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(base + P_NSTAGE * P_STAGE_BYTES);
+    s.full = bars;
+    s.empty = bars + P_NSTAGE;
+    s.tfull = bars + 2 * P_NSTAGE;
+    s.tempty = bars + 2 * P_NSTAGE + 2;
+    s.tdown = bars + 2 * P_NSTAGE + 4;
+    s.tmem_base = reinterpret_cast<uint32_t*>(bars + 2 * P_NSTAGE + 5);
+    s.abort_flag = reinterpret_cast<int*>(s.tmem_base + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < P_NSTAGE; ++i) {
+            mbar_init(smem_u32(&s.full[i]), 1);
+            mbar_init(smem_u32(&s.empty[i]), 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(smem_u32(&s.tfull[i]), 1);
+            mbar_init(smem_u32(&s.tempty[i]), 8);  // four epilogue warps in each CTA of the pair
+        }
+        mbar_init(smem_u32(s.tdown), 1);
+        *s.abort_flag = 0;
+        fence_barrier_init();
+        fence_proxy_async();
+        tma_prefetch_desc(&tmA);
+        tma_prefetch_desc(&tmB);
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(smem_u32(s.tmem_base), TMEM_COLS);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    __syncthreads();
+    // both CTAs' barriers exist before either one signals the other
+    cluster_arrive();
+    cluster_wait();
+    tc_fence_after();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(s.tmem_base);
+
+    if (warp == 0) {
+        pair_producer(&tmA, &tmB, p, s, rank);
+    } else if (warp == 1) {
+        if (rank == 0) pair_mma(p, s, tmem_base);
+    } else {
+        pair_epilogue(p, s, tmem_base, rank);
+    }
+
+    // tear-down: the leader waits (bounded) for its MMAs; neither CTA leaves, or frees TMEM, while
+    // the other may still read its shared memory or signal its barriers
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1 && rank == 0) {
+        if (lane == 0) {
+            tc_commit_pair(smem_u32(s.tdown));
+            mbar_wait(smem_u32(s.tdown), 0, s.abort_flag, p.status, ERR_WAIT_TEARDOWN);
+        }
+        __syncwarp();
+    }
+    cluster_arrive();
+    cluster_wait();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    }
+}
+
+}  // namespace cce

@@ -172,3 +172,37 @@ def test_workspace_too_small_and_bad_arguments_are_reported():
     assert rc == -1
     with pytest.raises(_native.NativeError):
         _native.check(rc, "lse")
+
+
+def test_two_cta_forward_kernel_matches_the_default_one():
+    """CCE_B200_LSE_PAIR=1 selects the cta_group::2 forward kernel (a cluster of two CTAs per
+    256x256 tile).  The switch is read once per process, so the comparison runs in a child."""
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parent.parent
+    code = (
+        "import sys, torch\n"
+        f"sys.path[:0] = [r'{root / 'ml-cross-entropy_b200'}', r'{root / 'tests'}', r'{root}']\n"
+        "from conftest import planted_inputs\n"
+        "from cut_cross_entropy.cce_lse_forward import cce_lse_forward_kernel\n"
+        "out = []\n"
+        "for n, v, d, sc in ((1000, 5000, 256, None), (255, 507, 123, 20.0), (385, 1300, 512, None)):\n"
+        "    e, c, b, _ = planted_inputs(n, v, d, torch.bfloat16, 'cuda', seed=n, bias=True)\n"
+        "    lse, tm = cce_lse_forward_kernel(e, c, b.float(), softcap=sc, return_tile_max=True)\n"
+        "    out += [lse.cpu(), tm.cpu()]\n"
+        "torch.save(out, sys.argv[1])\n"
+    )
+    import tempfile
+
+    with tempfile.TemporaryDirectory() as tmp:
+        results = []
+        for flag in ("0", "1"):
+            path = os.path.join(tmp, f"lse_{flag}.pt")
+            env = dict(os.environ, CCE_B200_LSE_PAIR=flag, CCE_B200_DEBUG="1")
+            subprocess.run([sys.executable, "-c", code, path], check=True, env=env, timeout=300)
+            results.append(torch.load(path))
+    for a, b in zip(*results):
+        torch.testing.assert_close(a, b, rtol=0, atol=1e-5)
