@@ -48,7 +48,8 @@ enum {
     CCE_ERR_CUDA = -4,       /* a CUDA runtime/driver call failed (see cce_b200_last_cuda_error) */
     CCE_ERR_DEVICE = -5,     /* not an sm_100 device */
     CCE_ERR_KERNEL_WAIT = -6, /* status word non-zero: a kernel abandoned a bounded wait */
-    CCE_ERR_TOO_LARGE = -7    /* problem needs more scratch than the fixed buffer of cce_b200_lse_forward_static */
+    CCE_ERR_TOO_LARGE = -7,   /* problem needs more scratch than the fixed buffer of cce_b200_lse_forward_static */
+    CCE_ERR_UNSUPPORTED = -8  /* feature not compiled into this build (wait tracing needs -DCCE_TRACE=1) */
 };
 
 /* Shape and operand description shared by the three entry points.
@@ -170,6 +171,16 @@ int cce_b200_read_status(const void* workspace, void* stream, int32_t* word /* h
  * kernel mode (index 0: forward log-sum-exp, 1: logit-gradient recompute, 2: dE/dC products)
  * into host arrays of 3 entries each, and forgets the records. */
 int cce_b200_profile_enable(int on);
+/* Tracing of the pipeline's internal waits.  Give a zeroed device array of 24 uint64 (3 kernel
+ * modes x 8); until it is reset to NULL every launch of the pipeline kernel adds, into the 8 words
+ * of its mode: [0] cycles the TMA producer waited for a free stage, [1] cycles the MMA issuer
+ * waited for a filled stage, [2] cycles it waited for a free accumulator, [3] cycles an epilogue
+ * warp waited for a finished accumulator, [4] CTA lifetimes, [5] number of CTAs; all summed over
+ * CTAs.  The array belongs to the caller and must outlive the launches.  The counters cost the
+ * forward kernel several per cent even when unused, so they exist only in a library built with
+ * -DCCE_TRACE=1 (python -m cut_cross_entropy._build --trace -> libcce_b200_trace.so, loaded with
+ * CCE_B200_LIB); the default build answers CCE_ERR_UNSUPPORTED to a non-NULL array. */
+int cce_b200_profile_wait_counters(void* device_counters /* uint64[24] or NULL */);
 int cce_b200_profile_read(double* ms /* host [3] */, int64_t* launches /* host [3] */);
 
 /* Counters since library load (host side): kernels launched by this library. */

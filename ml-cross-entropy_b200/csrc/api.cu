@@ -50,6 +50,7 @@ struct ProfRecord {
 std::mutex g_prof_mu;
 bool g_prof_on = false;
 std::vector<ProfRecord> g_prof;
+unsigned long long* g_wait_counters = nullptr;  // device memory of the caller, [3 modes][8]; null = off
 
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 inline long long cdiv(long long a, long long b) { return (a + b - 1) / b; }
@@ -266,16 +267,18 @@ int launch_engine(const CUtensorMap& a, const CUtensorMap& b, const EngineParams
     const unsigned grid = (unsigned)(items < sms ? items : sms);
     ProfRecord rec{nullptr, nullptr, MODE};
     bool prof = false;
+    EngineParams pp = p;
     {
         std::lock_guard<std::mutex> lock(g_prof_mu);
         prof = g_prof_on;
+        if (g_wait_counters) pp.wait_cycles = g_wait_counters + 8 * MODE;
     }
     if (prof) {
         CCE_CUDA(cudaEventCreate(&rec.start));
         CCE_CUDA(cudaEventCreate(&rec.stop));
         CCE_CUDA(cudaEventRecord(rec.start, st));
     }
-    engine_kernel<MODE><<<grid, ENGINE_THREADS, ENGINE_SMEM, st>>>(a, b, p);
+    engine_kernel<MODE><<<grid, ENGINE_THREADS, ENGINE_SMEM, st>>>(a, b, pp);
     CCE_LAUNCH_CHECK();
     if (prof) {
         CCE_CUDA(cudaEventRecord(rec.stop, st));
@@ -466,6 +469,7 @@ const char* cce_b200_strerror(int code) {
         case CCE_ERR_CUDA: return "CUDA call failed (see cce_b200_last_cuda_error)";
         case CCE_ERR_DEVICE: return "device is not sm_100";
         case CCE_ERR_KERNEL_WAIT: return "a kernel abandoned a bounded wait (status word non-zero)";
+        case CCE_ERR_UNSUPPORTED: return "not available in this build of the library";
         case CCE_ERR_TOO_LARGE:
             return "problem needs more scratch than the fixed buffer of cce_b200_lse_forward_static";
         default: return "unknown error";
@@ -484,6 +488,13 @@ int cce_b200_read_status(const void* workspace, void* stream, int32_t* word) {
 int cce_b200_profile_enable(int on) {
     std::lock_guard<std::mutex> lock(g_prof_mu);
     g_prof_on = on != 0;
+    return CCE_OK;
+}
+
+int cce_b200_profile_wait_counters(void* device_counters) {
+    if (device_counters && !kTrace) return CCE_ERR_UNSUPPORTED;  // this build has no tracing code
+    std::lock_guard<std::mutex> lock(g_prof_mu);
+    g_wait_counters = reinterpret_cast<unsigned long long*>(device_counters);
     return CCE_OK;
 }
 
@@ -577,6 +588,10 @@ int cce_b200_lse_forward(const cce_b200_operands* op, float* lse, float* tile_ma
             CCE_CUDA(cudaEventCreate(&rec.start));
             CCE_CUDA(cudaEventCreate(&rec.stop));
             CCE_CUDA(cudaEventRecord(rec.start, st));
+        }
+        {
+            std::lock_guard<std::mutex> lock(g_prof_mu);
+            if (g_wait_counters) p.wait_cycles = g_wait_counters;
         }
         lse_pair_kernel<<<(unsigned)(2 * pairs), ENGINE_THREADS, PAIR_SMEM, st>>>(tmA, tmB, p);
         CCE_LAUNCH_CHECK();

@@ -30,6 +30,13 @@ constexpr int ENGINE_SMEM = NSTAGE * STAGE_BYTES + 1024 /*align slack*/ + 256 /*
 
 enum { MODE_LSE = 0, MODE_PGRAD = 1, MODE_GEMM = 2 };
 
+// Wait-cycle tracing (EngineParams::wait_cycles) is compiled in only with -DCCE_TRACE=1: even
+// switched off at run time its clock reads cost the forward kernel ~8 %.
+#ifndef CCE_TRACE
+#define CCE_TRACE 0
+#endif
+constexpr bool kTrace = CCE_TRACE != 0;
+
 struct EngineParams {
     // extents of this launch
     int M;       // valid rows on the A side (TMEM lanes direction)
@@ -43,6 +50,10 @@ struct EngineParams {
     int a_mn_major, b_mn_major;  // 0: K contiguous in memory, 1: M/N contiguous in memory
     uint32_t idesc;
     int* status;
+    // optional tracing: cycles each role spent waiting, summed over CTAs (null = off)
+    //   [0] producer on a free stage, [1] MMA on a filled stage, [2] MMA on a free accumulator,
+    //   [3] epilogue on a finished accumulator (sum over its 4 warps / 4), [4] CTA lifetime, [5] CTAs
+    unsigned long long* wait_cycles;
 
     // ---- MODE_LSE / MODE_PGRAD
     const float* bias;  // fp32 [>= col_off + N] or null
@@ -260,8 +271,46 @@ __device__ void producer_loop(const CUtensorMap* tmA, const CUtensorMap* tmB, co
     const int lane = threadIdx.x & 31;
     int stage = 0;
     uint32_t phase = 0;
+    long long waited = 0;
     const PassInfo pass = load_pass(p);
     TileIter<MODE> it(p, pass);
+    const bool plain = (MODE != MODE_GEMM) || (!p.sparse && !p.kflags);  // every K block of every tile
+    if (plain) {
+        // One lane runs the whole loop: no ballots or shuffles on the per-K-block path.
+        if (lane == 0) {
+            while (it.next()) {
+                const int a_mn = p.a_mn_off + it.mblk * BM, b_mn = p.b_mn_off + it.nblk * BN;
+                for (int kb = 0; kb < p.n_kblk; ++kb) {
+                    if (!mbar_wait(smem_u32(&s.empty[stage]), phase ^ 1u, s.abort_flag, p.status,
+                                   ERR_WAIT_SMEM_EMPTY))
+                        return;
+                    const uint32_t bar = smem_u32(&s.full[stage]);
+                    const uint32_t sa = smem_u32(s.stages + stage * STAGE_BYTES);
+                    const uint32_t sb = sa + A_BYTES;
+                    const int a_k = p.a_k_off + kb * BK, b_k = p.b_k_off + kb * BK;
+                    mbar_expect_tx(bar, STAGE_BYTES);
+                    if (!p.a_mn_major) {
+                        tma_load_2d(sa, tmA, bar, a_k, a_mn);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * ATOM_BYTES, tmA, bar, a_mn + j * 64, a_k);
+                    }
+                    if (!p.b_mn_major) {
+                        tma_load_2d(sb, tmB, bar, b_k, b_mn);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * ATOM_BYTES, tmB, bar, b_mn + j * 64, b_k);
+                    }
+                    if (++stage == NSTAGE) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+        return;
+    }
+    if constexpr (MODE == MODE_GEMM) {  // only the products have sparse or flagged reductions
     while (it.next()) {
         const KTile kt = ktile_setup<MODE>(p, it.mblk);
         for (int base = 0; base < kt.n_cand; base += 32) {
@@ -277,8 +326,10 @@ __device__ void producer_loop(const CUtensorMap* tmA, const CUtensorMap* tmB, co
                 const int b_k = __shfl_sync(0xffffffffu, kc.b_k, src);
                 int ok = 1;
                 if (lane == 0) {
+                    const long long t0 = (kTrace && p.wait_cycles) ? clock64() : 0;
                     ok = mbar_wait(smem_u32(&s.empty[stage]), phase ^ 1u, s.abort_flag, p.status,
                                    ERR_WAIT_SMEM_EMPTY);
+                    if (kTrace && p.wait_cycles) waited += clock64() - t0;
                     if (ok) {
                         const uint32_t bar = smem_u32(&s.full[stage]);
                         const uint32_t sa = smem_u32(s.stages + stage * STAGE_BYTES);
@@ -309,6 +360,8 @@ __device__ void producer_loop(const CUtensorMap* tmA, const CUtensorMap* tmB, co
             }
         }
     }
+    }
+    if (kTrace && p.wait_cycles && lane == 0) atomicAdd(p.wait_cycles + 0, (unsigned long long)waited);
 }
 
 template <int MODE>
@@ -322,13 +375,67 @@ __device__ void mma_loop(const EngineParams& p, const EngineSmem& s, uint32_t tm
     const uint32_t a_lbo = p.a_mn_major ? ATOM_BYTES : 16, b_lbo = p.b_mn_major ? ATOM_BYTES : 16;
     const uint32_t a_kstep = p.a_mn_major ? (UMMA_K / 8) * 1024 : UMMA_K * 2;  // bytes per UMMA_K
     const uint32_t b_kstep = p.b_mn_major ? (UMMA_K / 8) * 1024 : UMMA_K * 2;
+    long long waited_full = 0, waited_acc = 0;
     const PassInfo pass = load_pass(p);
     TileIter<MODE> it(p, pass);
+    const bool plain = (MODE != MODE_GEMM) || (!p.sparse && !p.kflags);  // every K block of every tile
+    if (plain && p.n_kblk > 0) {
+        if (lane == 0) {
+            // descriptors of the four ring stages, built once; a K step adds to the address field
+            uint64_t adesc[NSTAGE], bdesc[NSTAGE];
+#pragma unroll
+            for (int i = 0; i < NSTAGE; ++i) {
+                const uint32_t sa = smem_u32(s.stages + i * STAGE_BYTES);
+                adesc[i] = make_smem_desc(sa, a_lbo, 1024);
+                bdesc[i] = make_smem_desc(sa + A_BYTES, b_lbo, 1024);
+            }
+            const uint64_t a_inc = a_kstep >> 4, b_inc = b_kstep >> 4;
+            while (it.next()) {
+                if (!mbar_wait(smem_u32(&s.tempty[acc]), acc_phase ^ 1u, s.abort_flag, p.status,
+                               ERR_WAIT_TMEM_EMPTY))
+                    return;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = 0; kb < p.n_kblk; ++kb) {
+                    if (!mbar_wait(smem_u32(&s.full[stage]), phase, s.abort_flag, p.status, ERR_WAIT_SMEM_FULL))
+                        return;
+                    tc_fence_after();
+                    uint64_t ad = 0, bd = 0;
+#pragma unroll
+                    for (int i = 0; i < NSTAGE; ++i) {  // select without dynamic register indexing
+                        if (i == stage) {
+                            ad = adesc[i];
+                            bd = bdesc[i];
+                        }
+                    }
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        tc_mma_f16(d_tmem, ad + k * a_inc, bd + k * b_inc, p.idesc, (kb | k) ? 1u : 0u);
+                    tc_commit(smem_u32(&s.empty[stage]));
+                    if (++stage == NSTAGE) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                s.acc_empty[acc] = 0;
+                __threadfence_block();
+                tc_commit(smem_u32(&s.tfull[acc]));
+                if (++acc == 2) {
+                    acc = 0;
+                    acc_phase ^= 1u;
+                }
+            }
+        }
+        return;
+    }
+    if constexpr (MODE == MODE_GEMM) {  // only the products have sparse or flagged reductions
     while (it.next()) {
         int ok = 1;
         if (lane == 0) {
+            const long long t0 = (kTrace && p.wait_cycles) ? clock64() : 0;
             ok = mbar_wait(smem_u32(&s.tempty[acc]), acc_phase ^ 1u, s.abort_flag, p.status,
                            ERR_WAIT_TMEM_EMPTY);
+            if (kTrace && p.wait_cycles) waited_acc += clock64() - t0;
         }
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) return;
@@ -343,8 +450,10 @@ __device__ void mma_loop(const EngineParams& p, const EngineSmem& s, uint32_t tm
             while (mask) {
                 mask &= mask - 1;
                 if (lane == 0) {
+                    const long long t0 = (kTrace && p.wait_cycles) ? clock64() : 0;
                     ok = mbar_wait(smem_u32(&s.full[stage]), phase, s.abort_flag, p.status,
                                    ERR_WAIT_SMEM_FULL);
+                    if (kTrace && p.wait_cycles) waited_full += clock64() - t0;
                     if (ok) {
                         tc_fence_after();
                         const uint32_t sa = smem_u32(s.stages + stage * STAGE_BYTES);
@@ -381,6 +490,11 @@ __device__ void mma_loop(const EngineParams& p, const EngineSmem& s, uint32_t tm
             acc_phase ^= 1u;
         }
     }
+    }
+    if (kTrace && p.wait_cycles && lane == 0) {
+        atomicAdd(p.wait_cycles + 1, (unsigned long long)waited_full);
+        atomicAdd(p.wait_cycles + 2, (unsigned long long)waited_acc);
+    }
 }
 
 __device__ __forceinline__ float apply_softcap(float x, float softcap, float inv_softcap) {
@@ -416,6 +530,7 @@ __device__ void epilogue_loop(const EngineParams& p, const EngineSmem& s, uint32
 
     // MODE_LSE running state (log2 units)
     float run_m = -INFINITY, run_s = 0.0f;
+    long long waited_epi = 0;
 
     const PassInfo pass = load_pass(p);
     TileIter<MODE> it(p, pass);
@@ -448,8 +563,10 @@ __device__ void epilogue_loop(const EngineParams& p, const EngineSmem& s, uint32
         }
 
         // every epilogue thread observes the barrier itself before touching TMEM
+        const long long t0w = (kTrace && p.wait_cycles) ? clock64() : 0;
         int ok = mbar_wait(smem_u32(&s.tfull[acc]), acc_phase, s.abort_flag, p.status,
                            ERR_WAIT_TMEM_FULL);
+        if (kTrace && p.wait_cycles) waited_epi += clock64() - t0w;
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) return;
         tc_fence_after();
@@ -624,6 +741,7 @@ __device__ void epilogue_loop(const EngineParams& p, const EngineSmem& s, uint32
             if (it.last && row_ok) p.partial[(size_t)it.band * p.M + row] = make_float2(run_m, run_s);
         }
     }
+    if (kTrace && p.wait_cycles && lane == 0) atomicAdd(p.wait_cycles + 3, (unsigned long long)(waited_epi / 4));
 }
 
 template <int MODE>
@@ -646,6 +764,7 @@ engine_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    const long long t_start = (kTrace && p.wait_cycles) ? clock64() : 0;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < NSTAGE; ++i) {
@@ -693,6 +812,10 @@ engine_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
         __syncwarp();
         tc_fence_after();
         tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+    if (kTrace && p.wait_cycles && threadIdx.x == 0) {
+        atomicAdd(p.wait_cycles + 4, (unsigned long long)(clock64() - t_start));
+        atomicAdd(p.wait_cycles + 5, 1ull);
     }
 }
 

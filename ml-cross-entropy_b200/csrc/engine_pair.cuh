@@ -63,88 +63,103 @@ struct PairSmem {
 
 __device__ void pair_producer(const CUtensorMap* tmA, const CUtensorMap* tmB, const EngineParams& p,
                               const PairSmem& s, uint32_t rank) {
-    const int lane = threadIdx.x & 31;
+    if ((threadIdx.x & 31) != 0) return;  // one lane runs the whole loop
     int stage = 0;
     uint32_t phase = 0;
+    long long waited = 0;
     PairIter it(p);
     while (it.next()) {
         const int a_row = (it.rb2 * 2 + int(rank)) * BM;
         const int b_row = it.nblk * BN + int(rank) * (BN / 2);
         for (int kb = 0; kb < p.n_kblk; ++kb) {
-            int ok = 1;
-            if (lane == 0) {
-                ok = mbar_wait(smem_u32(&s.empty[stage]), phase ^ 1u, s.abort_flag, p.status, ERR_WAIT_SMEM_EMPTY);
-                if (ok) {
-                    const uint32_t bar_local = smem_u32(&s.full[stage]);
-                    const uint32_t bar_leader = map_to_cta(bar_local, 0);
-                    const uint32_t sa = smem_u32(s.stages + stage * P_STAGE_BYTES);
-                    if (rank == 0) mbar_expect_tx(bar_local, 2 * P_STAGE_BYTES);  // bytes of both CTAs
-                    tma_load_2d_pair(sa, tmA, bar_leader, kb * BK, a_row);
-                    tma_load_2d_pair(sa + P_A_BYTES, tmB, bar_leader, kb * BK, b_row);
-                }
-            }
-            ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (!ok) return;
+            const long long t0 = (kTrace && p.wait_cycles) ? clock64() : 0;
+            if (!mbar_wait(smem_u32(&s.empty[stage]), phase ^ 1u, s.abort_flag, p.status, ERR_WAIT_SMEM_EMPTY)) return;
+            if (kTrace && p.wait_cycles) waited += clock64() - t0;
+            const uint32_t bar_local = smem_u32(&s.full[stage]);
+            const uint32_t bar_leader = map_to_cta(bar_local, 0);
+            const uint32_t sa = smem_u32(s.stages + stage * P_STAGE_BYTES);
+            if (rank == 0) mbar_expect_tx(bar_local, 2 * P_STAGE_BYTES);  // bytes of both CTAs
+            tma_load_2d_pair(sa, tmA, bar_leader, kb * BK, a_row);
+            tma_load_2d_pair(sa + P_A_BYTES, tmB, bar_leader, kb * BK, b_row);
             if (++stage == P_NSTAGE) {
                 stage = 0;
                 phase ^= 1u;
             }
         }
     }
+    if (kTrace && p.wait_cycles) atomicAdd(p.wait_cycles + 0, (unsigned long long)waited);
 }
 
-// leader CTA only
+// leader CTA only; one lane runs the whole loop
 __device__ void pair_mma(const EngineParams& p, const PairSmem& s, uint32_t tmem_base) {
-    const int lane = threadIdx.x & 31;
+    if ((threadIdx.x & 31) != 0) return;
     int stage = 0;
     uint32_t phase = 0;
     int acc = 0;
     uint32_t acc_phase = 0;
+    long long waited_full = 0, waited_acc = 0;
+    // per-stage descriptors and barrier addresses (own CTA and peer), built once
+    uint64_t adesc[P_NSTAGE], bdesc[P_NSTAGE];
+    uint32_t full_bar[P_NSTAGE], empty_bar[P_NSTAGE], empty_peer[P_NSTAGE];
+#pragma unroll
+    for (int i = 0; i < P_NSTAGE; ++i) {
+        const uint32_t sa = smem_u32(s.stages + i * P_STAGE_BYTES);
+        adesc[i] = make_smem_desc(sa, 16, 1024);
+        bdesc[i] = make_smem_desc(sa + P_A_BYTES, 16, 1024);
+        full_bar[i] = smem_u32(&s.full[i]);
+        empty_bar[i] = smem_u32(&s.empty[i]);
+        empty_peer[i] = map_to_cta(empty_bar[i], 1);
+    }
+    const uint32_t tfull_bar[2] = {smem_u32(&s.tfull[0]), smem_u32(&s.tfull[1])};
+    const uint32_t tfull_peer[2] = {map_to_cta(tfull_bar[0], 1), map_to_cta(tfull_bar[1], 1)};
     PairIter it(p);
     while (it.next()) {
-        int ok = 1;
-        if (lane == 0)
-            ok = mbar_wait(smem_u32(&s.tempty[acc]), acc_phase ^ 1u, s.abort_flag, p.status, ERR_WAIT_TMEM_EMPTY);
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) return;
+        {
+            const long long t0 = (kTrace && p.wait_cycles) ? clock64() : 0;
+            if (!mbar_wait(smem_u32(&s.tempty[acc]), acc_phase ^ 1u, s.abort_flag, p.status, ERR_WAIT_TMEM_EMPTY))
+                return;
+            if (kTrace && p.wait_cycles) waited_acc += clock64() - t0;
+        }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < p.n_kblk; ++kb) {
-            if (lane == 0) {
-                ok = mbar_wait(smem_u32(&s.full[stage]), phase, s.abort_flag, p.status, ERR_WAIT_SMEM_FULL);
-                if (ok) {
-                    tc_fence_after();
-                    const uint32_t sa = smem_u32(s.stages + stage * P_STAGE_BYTES);
-                    const uint32_t sb = sa + P_A_BYTES;
+            uint64_t ad = 0, bd = 0;
+            uint32_t fb = 0, eb = 0, ep = 0;
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k) {
-                        const uint64_t ad = make_smem_desc(sa + k * UMMA_K * 2, 16, 1024);
-                        const uint64_t bd = make_smem_desc(sb + k * UMMA_K * 2, 16, 1024);
-                        tc_mma_f16_pair(d_tmem, ad, bd, p.idesc, (kb | k) ? 1u : 0u);
-                    }
-                    // the stage is free in both CTAs once these MMAs have read it
-                    const uint32_t eb = smem_u32(&s.empty[stage]);
-                    tc_commit_pair(eb);
-                    tc_commit_pair(map_to_cta(eb, 1));
+            for (int i = 0; i < P_NSTAGE; ++i) {  // select without dynamic register indexing
+                if (i == stage) {
+                    ad = adesc[i];
+                    bd = bdesc[i];
+                    fb = full_bar[i];
+                    eb = empty_bar[i];
+                    ep = empty_peer[i];
                 }
             }
-            ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (!ok) return;
+            const long long t0 = (kTrace && p.wait_cycles) ? clock64() : 0;
+            if (!mbar_wait(fb, phase, s.abort_flag, p.status, ERR_WAIT_SMEM_FULL)) return;
+            if (kTrace && p.wait_cycles) waited_full += clock64() - t0;
+            tc_fence_after();
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k)
+                tc_mma_f16_pair(d_tmem, ad + k * 2, bd + k * 2, p.idesc, (kb | k) ? 1u : 0u);  // +32 B per K step
+            // the stage is free in both CTAs once these MMAs have read it
+            tc_commit_pair(eb);
+            tc_commit_pair(ep);
             if (++stage == P_NSTAGE) {
                 stage = 0;
                 phase ^= 1u;
             }
         }
-        if (lane == 0) {
-            const uint32_t tb = smem_u32(&s.tfull[acc]);
-            tc_commit_pair(tb);
-            tc_commit_pair(map_to_cta(tb, 1));
-        }
-        __syncwarp();
+        tc_commit_pair(acc ? tfull_bar[1] : tfull_bar[0]);
+        tc_commit_pair(acc ? tfull_peer[1] : tfull_peer[0]);
         if (++acc == 2) {
             acc = 0;
             acc_phase ^= 1u;
         }
+    }
+    if (kTrace && p.wait_cycles) {
+        atomicAdd(p.wait_cycles + 1, (unsigned long long)waited_full);
+        atomicAdd(p.wait_cycles + 2, (unsigned long long)waited_acc);
     }
 }
 
@@ -154,6 +169,7 @@ __device__ void pair_epilogue(const EngineParams& p, const PairSmem& s, uint32_t
     uint32_t acc_phase = 0;
     const float inv_softcap = p.has_softcap ? 1.0f / p.softcap : 0.0f;
     float run_m = -INFINITY, run_s = 0.0f;
+    long long waited_epi = 0;
     PairIter it(p);
     while (it.next()) {
         const int mblk = it.rb2 * 2 + int(rank);
@@ -163,7 +179,9 @@ __device__ void pair_epilogue(const EngineParams& p, const PairSmem& s, uint32_t
             run_m = -INFINITY;
             run_s = 0.0f;
         }
+        const long long t0w = (kTrace && p.wait_cycles) ? clock64() : 0;
         int ok = mbar_wait(smem_u32(&s.tfull[acc]), acc_phase, s.abort_flag, p.status, ERR_WAIT_TMEM_FULL);
+        if (kTrace && p.wait_cycles) waited_epi += clock64() - t0w;
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) return;
         tc_fence_after();
@@ -222,6 +240,7 @@ __device__ void pair_epilogue(const EngineParams& p, const PairSmem& s, uint32_t
         }
         if (it.last && row_ok) p.partial[(size_t)it.band * p.M + row] = make_float2(run_m, run_s);
     }
+    if (kTrace && p.wait_cycles && lane == 0) atomicAdd(p.wait_cycles + 3, (unsigned long long)(waited_epi / 4));
 }
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(ENGINE_THREADS, 1)
@@ -242,6 +261,7 @@ lse_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
+    const long long t_start = (kTrace && p.wait_cycles) ? clock64() : 0;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < P_NSTAGE; ++i) {
@@ -295,6 +315,10 @@ lse_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    }
+    if (kTrace && p.wait_cycles && threadIdx.x == 0) {
+        atomicAdd(p.wait_cycles + 4, (unsigned long long)(clock64() - t_start));
+        atomicAdd(p.wait_cycles + 5, 1ull);
     }
 }
 

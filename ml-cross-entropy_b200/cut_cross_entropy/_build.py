@@ -41,18 +41,31 @@ def is_stale() -> bool:
     return any((CSRC_DIR / f).resolve().stat().st_mtime > built for f in SOURCES + HEADERS)
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile the library if it is missing or older than its sources."""
+TRACE_LIB_PATH = PKG_DIR / "libcce_b200_trace.so"
+
+
+def build(force: bool = False, verbose: bool = False, trace: bool = False) -> Path:
+    """Compile the library if it is missing or older than its sources.
+
+    ``trace=True`` builds ``libcce_b200_trace.so`` instead, with the pipeline's wait-cycle counters
+    compiled in (select it at run time with ``CCE_B200_LIB``).
+    """
+    if trace:
+        return _compile(TRACE_LIB_PATH, ["-DCCE_TRACE=1"], verbose)
     if not force and not is_stale():
         return LIB_PATH
+    return _compile(LIB_PATH, [], verbose)
+
+
+def _compile(out: Path, defines: list[str], verbose: bool) -> Path:
     cmd = [
         _nvcc(),
         "-gencode", "arch=compute_100a,code=sm_100a",
         "-lineinfo", "-O3", "-std=c++17",
         *(["-Xptxas", "-v"] if verbose else []),
         *_host_compiler(),
-        "-shared", "-Xcompiler", "-fPIC",
-        "-o", str(LIB_PATH),
+        "-shared", "-Xcompiler", "-fPIC", *defines,
+        "-o", str(out),
         *[str(CSRC_DIR / s) for s in SOURCES],
     ]  # fmt: skip
     proc = subprocess.run(cmd, capture_output=True, text=True)
@@ -60,8 +73,8 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         raise RuntimeError(f"nvcc failed ({proc.returncode}):\n{proc.stdout}\n{proc.stderr}")
     if verbose:
         print(proc.stderr, file=sys.stderr)
-    return LIB_PATH
+    return out
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, trace="--trace" in sys.argv))

@@ -33,6 +33,7 @@ EXPORTS = (
     "cce_b200_read_status",
     "cce_b200_launch_count",
     "cce_b200_profile_enable",
+    "cce_b200_profile_wait_counters",
     "cce_b200_profile_read",
     "cce_b200_strerror",
     "cce_b200_last_cuda_error",
@@ -125,6 +126,8 @@ def lib() -> ctypes.CDLL:
     L.cce_b200_read_status.argtypes = [c_void_p, c_void_p, POINTER(c_int32)]
     L.cce_b200_profile_enable.restype = c_int32
     L.cce_b200_profile_enable.argtypes = [c_int32]
+    L.cce_b200_profile_wait_counters.restype = c_int32
+    L.cce_b200_profile_wait_counters.argtypes = [c_void_p]
     L.cce_b200_profile_read.restype = c_int32
     L.cce_b200_profile_read.argtypes = [POINTER(ctypes.c_double), POINTER(c_int64)]
     L.cce_b200_launch_count.restype = c_int64
