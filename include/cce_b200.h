@@ -65,7 +65,8 @@ typedef struct cce_b200_operands {
     int64_t V;            /* classifier rows held by this rank */
     int64_t D;            /* hidden size */
     int64_t lde, ldc;     /* row strides in elements */
-    int32_t dtype;        /* CCE_DT_F16 or CCE_DT_BF16: type of e and c */
+    int32_t dtype;        /* type of e and c: CCE_DT_BF16, CCE_DT_F16, or CCE_DT_F32 (computed as a
+                             three-term bf16 split, ~2^-16 relative error per product, 3x the work) */
     int32_t bias_dtype;   /* CCE_DT_* of bias */
     int32_t valids_dtype; /* CCE_IDX_* */
     int32_t has_softcap;  /* 0/1 */
@@ -134,9 +135,9 @@ typedef struct cce_b200_backward_args {
     float filter_eps;
     int32_t filter_e;        /* apply the filter to the dE product */
     int32_t filter_c;        /* apply the filter to the dC product */
-    void* d_e;               /* [n_total, D], row stride D, or NULL; fully written (zeros at rows not in valids) */
+    void* d_e;               /* [n_total, D] in op.dtype, row stride D, or NULL; fully written (zeros at rows not in valids) */
     int32_t d_e_f32;         /* element type of d_e: 0 = op.dtype, 1 = fp32 (for a caller that reduces dE across ranks in fp32) */
-    void* d_c;               /* [V, D] in op.dtype, row stride D, or NULL */
+    void* d_c;               /* [V, D] in op.dtype (fp32 for fp32 operands), row stride D, or NULL */
     float* d_bias;           /* [V] fp32 or NULL */
     const float* tile_max;   /* by-product of cce_b200_lse_forward for the same operands, or NULL */
 } cce_b200_backward_args;

@@ -146,7 +146,7 @@ int check_operands(const cce_b200_operands* op) {
     if (op->n_total < 0 || op->n_rows < 0 || op->V <= 0 || op->D <= 0) return CCE_ERR_ARG;
     if (op->n_rows > op->n_total) return CCE_ERR_ARG;
     if (!op->valids && op->n_rows != 0 && op->n_rows != op->n_total) return CCE_ERR_ARG;
-    if (op->dtype != CCE_DT_F16 && op->dtype != CCE_DT_BF16) return CCE_ERR_ARG;
+    if (op->dtype != CCE_DT_F16 && op->dtype != CCE_DT_BF16 && op->dtype != CCE_DT_F32) return CCE_ERR_ARG;
     if (op->bias && (op->bias_dtype < 0 || op->bias_dtype > 2)) return CCE_ERR_ARG;
     if (op->valids && op->valids_dtype != CCE_IDX_I32 && op->valids_dtype != CCE_IDX_I64) return CCE_ERR_ARG;
     if (op->lde < op->D || op->ldc < op->D) return CCE_ERR_ARG;
@@ -157,9 +157,14 @@ int check_operands(const cce_b200_operands* op) {
 
 // Where the operands the tensor-core kernels read come from: the caller's buffers when TMA
 // can address them, else packed/padded copies in the workspace.
+// fp32 operands are staged as three-term bf16 splits (split_rows_kernel) and then follow the bf16 path.
+inline bool is_split(const cce_b200_operands* op) { return op->dtype == CCE_DT_F32; }
+inline int compute_dtype(const cce_b200_operands* op) { return is_split(op) ? CCE_DT_BF16 : op->dtype; }
+
 struct OperandPlan {
-    bool pack_e, pad_c, bias32;
-    long long Dp;  // row length (elements) of the copies, multiple of 8
+    bool pack_e, pad_c, bias32, split;
+    long long Dp;    // length (elements) of one padded block of columns, multiple of 8
+    long long Drow;  // row length of the staged copies: Dp, or 3*Dp for split fp32 operands
     size_t off_e, off_c, off_bias, end;
 };
 
@@ -170,11 +175,14 @@ OperandPlan plan_operands(const cce_b200_operands* op, size_t start) {
     pl.pack_e = op->valids || !d_ok || (op->lde % 8) || (reinterpret_cast<uintptr_t>(op->e) & 15);
     pl.pad_c = !d_ok || (op->ldc % 8) || (reinterpret_cast<uintptr_t>(op->c) & 15);
     pl.bias32 = op->bias && op->bias_dtype != CCE_DT_F32;
+    pl.split = is_split(op);
+    if (pl.split) pl.pack_e = pl.pad_c = true;
+    pl.Drow = pl.split ? 3 * pl.Dp : pl.Dp;
     size_t off = align_up(start, 256);
     pl.off_e = off;
-    if (pl.pack_e) off = align_up(off + (size_t)op->n_rows * pl.Dp * 2, 256);
+    if (pl.pack_e) off = align_up(off + (size_t)op->n_rows * pl.Drow * 2, 256);
     pl.off_c = off;
-    if (pl.pad_c) off = align_up(off + (size_t)op->V * pl.Dp * 2, 256);
+    if (pl.pad_c) off = align_up(off + (size_t)op->V * pl.Drow * 2, 256);
     pl.off_bias = off;
     if (pl.bias32) off = align_up(off + (size_t)op->V * 4, 256);
     pl.end = off;
@@ -187,12 +195,31 @@ struct Staged {
     const void* c;
     long long ldc;
     const float* bias;
-    long long Dk;  // reduction extent visible to TMA (D, or the padded length of the copies)
+    long long Dk;   // reduction extent of E.C^T visible to TMA: D, or 3*Dp for split fp32 operands
+    long long Dmn;  // extent of the column dimension when the operand is read column-major (MN-major)
+    long long blk;  // distance between the column blocks of a split row (Dp), 0 otherwise
 };
 
 int stage_operands(const cce_b200_operands* op, const OperandPlan& pl, char* ws, cudaStream_t st, Staged* out) {
-    out->Dk = op->D;
-    if (pl.pack_e) {
+    out->Dk = out->Dmn = op->D;
+    out->blk = 0;
+    if (pl.split) {
+        out->Dk = out->Dmn = pl.Drow;
+        out->blk = pl.Dp;
+        if (op->n_rows > 0) {
+            split_rows_kernel<<<(unsigned)op->n_rows, 128, 0, st>>>(
+                reinterpret_cast<const float*>(op->e), op->lde, op->valids, op->valids_dtype == CCE_IDX_I64,
+                reinterpret_cast<__nv_bfloat16*>(ws + pl.off_e), pl.Dp, op->D, op->n_rows, 0);
+            CCE_LAUNCH_CHECK();
+        }
+        split_rows_kernel<<<(unsigned)op->V, 128, 0, st>>>(reinterpret_cast<const float*>(op->c), op->ldc, nullptr, 0,
+                                                          reinterpret_cast<__nv_bfloat16*>(ws + pl.off_c), pl.Dp,
+                                                          op->D, op->V, 1);
+        CCE_LAUNCH_CHECK();
+        out->e = ws + pl.off_e;
+        out->c = ws + pl.off_c;
+        out->lde = out->ldc = pl.Drow;
+    } else if (pl.pack_e) {
         if (op->n_rows > 0) {
             pack_rows_kernel<<<(unsigned)op->n_rows, 128, 0, st>>>(
                 reinterpret_cast<const uint16_t*>(op->e), op->lde, op->valids, op->valids_dtype == CCE_IDX_I64,
@@ -205,7 +232,9 @@ int stage_operands(const cce_b200_operands* op, const OperandPlan& pl, char* ws,
         out->e = op->e;
         out->lde = op->lde;
     }
-    if (pl.pad_c) {
+    if (pl.split) {
+        // staged above
+    } else if (pl.pad_c) {
         pack_rows_kernel<<<(unsigned)op->V, 128, 0, st>>>(reinterpret_cast<const uint16_t*>(op->c), op->ldc, nullptr, 0,
                                                          reinterpret_cast<uint16_t*>(ws + pl.off_c), pl.Dp, op->D,
                                                          op->V);
@@ -557,14 +586,15 @@ int cce_b200_lse_forward(const cce_b200_operands* op, float* lse, float* tile_ma
     rc = stage_operands(op, pl.ops, ws, st, &sg);
     if (rc != CCE_OK) return rc;
 
+    const int cdt = compute_dtype(op);
     CUtensorMap tmA, tmB;
-    rc = make_tmap(&tmA, sg.e, op->dtype, sg.Dk, op->n_rows, sg.lde, BK, BM);
+    rc = make_tmap(&tmA, sg.e, cdt, sg.Dk, op->n_rows, sg.lde, BK, BM);
     if (rc != CCE_OK) return rc;
-    rc = make_tmap(&tmB, sg.c, op->dtype, sg.Dk, op->V, sg.ldc, BK, BN);
+    rc = make_tmap(&tmB, sg.c, cdt, sg.Dk, op->V, sg.ldc, BK, BN);
     if (rc != CCE_OK) return rc;
 
     EngineParams p;
-    base_params(&p, op->n_rows, op->V, sg.Dk, op->dtype, 0, 0, reinterpret_cast<int*>(ws));
+    base_params(&p, op->n_rows, op->V, sg.Dk, cdt, 0, 0, reinterpret_cast<int*>(ws));
     p.bias = sg.bias;
     p.has_softcap = op->has_softcap;
     p.softcap = op->softcap;
@@ -573,9 +603,9 @@ int cce_b200_lse_forward(const cce_b200_operands* op, float* lse, float* tile_ma
     p.tile_max = tile_max;
     if (use_cta_pairs()) {
         // two-CTA form: each CTA of a pair stages 128 rows of each operand, the MMA is M = 256
-        rc = make_tmap(&tmB, sg.c, op->dtype, sg.Dk, op->V, sg.ldc, BK, BN / 2);
+        rc = make_tmap(&tmB, sg.c, cdt, sg.Dk, op->V, sg.ldc, BK, BN / 2);
         if (rc != CCE_OK) return rc;
-        p.idesc = make_idesc(op->dtype == CCE_DT_BF16 ? 1u : 0u, 0, 0, 2 * BM, BN);
+        p.idesc = make_idesc(cdt == CCE_DT_BF16 ? 1u : 0u, 0, 0, 2 * BM, BN);
         const long long items = cdiv(p.n_nblk, p.band_len) * cdiv(p.n_mblk, 2);
         const long long pairs = std::min<long long>(items, dev->sms / 2);
         ProfRecord rec{nullptr, nullptr, MODE_LSE};
@@ -629,7 +659,12 @@ int cce_b200_indexed_neg_dot(const cce_b200_operands* op, const int64_t* targets
     if (op->n_rows == 0) return CCE_OK;
     cudaStream_t st = (cudaStream_t)stream;
     const unsigned blocks = (unsigned)cdiv(op->n_rows, 8);  // 8 warps per block
-    if (op->dtype == CCE_DT_BF16) {
+    if (op->dtype == CCE_DT_F32) {
+        indexed_neg_dot_kernel<float><<<blocks, 256, 0, st>>>(
+            reinterpret_cast<const float*>(op->e), op->lde, reinterpret_cast<const float*>(op->c), op->ldc, op->bias,
+            op->bias_dtype, op->valids, op->valids_dtype == CCE_IDX_I64, reinterpret_cast<const long long*>(targets),
+            shift, vocab_start, op->V, op->D, op->n_rows, op->has_softcap, op->softcap, out);
+    } else if (op->dtype == CCE_DT_BF16) {
         indexed_neg_dot_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(
             reinterpret_cast<const __nv_bfloat16*>(op->e), op->lde, reinterpret_cast<const __nv_bfloat16*>(op->c),
             op->ldc, op->bias, op->bias_dtype, op->valids, op->valids_dtype == CCE_IDX_I64,
@@ -670,10 +705,12 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
     cudaStream_t st = (cudaStream_t)stream;
     char* ws = reinterpret_cast<char*>(workspace);
     const long long D = op->D, V = op->V, B = op->n_rows;
-    const size_t esz = 2;
+    const int cdt = compute_dtype(op);      // type the tensor cores see (fp32 operands are split into bf16)
+    const bool split = is_split(op);
+    const size_t esz = split ? 4 : 2;       // element size of the caller's e, c, d_c (and d_e unless d_e_f32)
 
     CCE_CUDA(cudaMemsetAsync(ws, 0, kStatusBytes, st));
-    const size_t de_esz = a->d_e_f32 ? 4 : esz;
+    const size_t de_esz = (a->d_e_f32 || split) ? 4 : esz;
     if (a->d_e && (op->valids || B == 0)) CCE_CUDA(cudaMemsetAsync(a->d_e, 0, (size_t)op->n_total * D * de_esz, st));
     if (a->d_bias) CCE_CUDA(cudaMemsetAsync(a->d_bias, 0, (size_t)V * 4, st));
     if (B == 0) {
@@ -692,18 +729,36 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
 
     // operand maps that do not change from chunk to chunk
     CUtensorMap tmE_k, tmC_k, tmE_mn, tmC_mn;
-    rc = make_tmap(&tmE_k, sg.e, op->dtype, sg.Dk, B, sg.lde, BK, BM);
+    rc = make_tmap(&tmE_k, sg.e, cdt, sg.Dk, B, sg.lde, BK, BM);
     if (rc != CCE_OK) return rc;
-    rc = make_tmap(&tmC_k, sg.c, op->dtype, sg.Dk, V, sg.ldc, BK, BN);
+    rc = make_tmap(&tmC_k, sg.c, cdt, sg.Dk, V, sg.ldc, BK, BN);
     if (rc != CCE_OK) return rc;
-    rc = make_tmap(&tmE_mn, sg.e, op->dtype, D, B, sg.lde, 64, BK);
+    rc = make_tmap(&tmE_mn, sg.e, cdt, sg.Dmn, B, sg.lde, 64, BK);
     if (rc != CCE_OK) return rc;
-    rc = make_tmap(&tmC_mn, sg.c, op->dtype, D, V, sg.ldc, 64, BK);
+    rc = make_tmap(&tmC_mn, sg.c, cdt, sg.Dmn, V, sg.ldc, 64, BK);
     if (rc != CCE_OK) return rc;
+
+    // The two products.  With split fp32 operands the staged rows hold three column blocks
+    // ([hi|hi|lo] for e, [hi|lo|hi] for c): dC = G^T e_hi + G^T e_lo and dE = G c_hi + G c_lo, i.e. the
+    // same launch run twice on different column blocks of the B operand, the second adding in fp32.
+    auto run_dc = [&](EngineParams p, const CUtensorMap& tmA) -> int {
+        int r = launch_engine<MODE_GEMM>(tmA, tmE_mn, p, dev->sms, st);
+        if (r != CCE_OK || !split) return r;
+        p.b_mn_off = int(2 * sg.blk);
+        p.accumulate = 2;
+        return launch_engine<MODE_GEMM>(tmA, tmE_mn, p, dev->sms, st);
+    };
+    auto run_de = [&](EngineParams p, const CUtensorMap& tmA) -> int {
+        int r = launch_engine<MODE_GEMM>(tmA, tmC_mn, p, dev->sms, st);
+        if (r != CCE_OK || !split) return r;
+        p.b_mn_off = int(sg.blk);
+        p.accumulate = 2;
+        return launch_engine<MODE_GEMM>(tmA, tmC_mn, p, dev->sms, st);
+    };
 
     // phase-1 parameters shared by both shapes
     EngineParams pg;
-    base_params(&pg, B, V, sg.Dk, op->dtype, 0, 0, status);
+    base_params(&pg, B, V, sg.Dk, cdt, 0, 0, status);
     pg.bias = sg.bias;
     pg.has_softcap = op->has_softcap;
     pg.softcap = op->softcap;
@@ -719,7 +774,7 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
     pg.grad_scale = a->grad_scale;
     pg.filter_eps = use_flags ? a->filter_eps : -1.0f;
     pg.g_out = g_buf;
-    pg.g_is_bf16 = op->dtype == CCE_DT_BF16;
+    pg.g_is_bf16 = cdt == CCE_DT_BF16;
 
     if (pl.sparse) {
         // ---- index of the tiles worth recomputing
@@ -752,9 +807,9 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
         CCE_LAUNCH_CHECK();
 
         CUtensorMap tmP_k, tmP_mn;  // the pool seen as a [capacity*128][256] matrix
-        rc = make_tmap(&tmP_k, g_buf, op->dtype, BN, (long long)pl.capacity * BM, BN, BK, BM);
+        rc = make_tmap(&tmP_k, g_buf, cdt, BN, (long long)pl.capacity * BM, BN, BK, BM);
         if (rc != CCE_OK) return rc;
-        rc = make_tmap(&tmP_mn, g_buf, op->dtype, BN, (long long)pl.capacity * BM, BN, 64, BK);
+        rc = make_tmap(&tmP_mn, g_buf, cdt, BN, (long long)pl.capacity * BM, BN, 64, BK);
         if (rc != CCE_OK) return rc;
 
         for (int ps = 0; ps < pl.max_pass; ++ps) {
@@ -777,10 +832,10 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
             CCE_LAUNCH_CHECK();
             if (a->d_c) {  // dC[vt] = sum over the slots of column vt of G^T E
                 EngineParams p;
-                base_params(&p, V, D, B, op->dtype, 1, 1, status);
+                base_params(&p, V, D, B, cdt, 1, 1, status);
                 p.out = a->d_c;
                 p.ldo = D;
-                p.out_dtype = op->dtype;
+                p.out_dtype = split ? CCE_DT_F32 : op->dtype;
                 p.accumulate = 0;
                 p.sparse = 2;
                 p.pass_info = pinfo;
@@ -789,12 +844,12 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
                 p.n_vt = pl.n_vt;
                 p.klist = dc_list;
                 p.kcount = dc_cnt;
-                rc = launch_engine<MODE_GEMM>(tmP_mn, tmE_mn, p, dev->sms, st);
+                rc = run_dc(p, tmP_mn);
                 if (rc != CCE_OK) return rc;
             }
             if (a->d_e) {  // dE[rb] += sum over the slots of row rb (in this pass) of G C
                 EngineParams p;
-                base_params(&p, B, D, V, op->dtype, 0, 1, status);
+                base_params(&p, B, D, V, cdt, 0, 1, status);
                 p.out = de32;
                 p.ldo = D;
                 p.out_dtype = CCE_DT_F32;
@@ -806,7 +861,7 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
                 p.n_vt = pl.n_vt;
                 p.klist = de_list;
                 p.kcount = de_cnt;
-                rc = launch_engine<MODE_GEMM>(tmP_k, tmC_mn, p, dev->sms, st);
+                rc = run_de(p, tmP_k);
                 if (rc != CCE_OK) return rc;
             }
         }
@@ -837,29 +892,29 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
             // phase 2: dC[v0 : v0 + Vw, :] = G^T E   (M = Vw, N = D, K = B; both operands MN-major)
             if (a->d_c) {
                 CUtensorMap tmG_mn;
-                rc = make_tmap(&tmG_mn, g_buf, op->dtype, Vw, B, pl.Vc, 64, BK);
+                rc = make_tmap(&tmG_mn, g_buf, cdt, Vw, B, pl.Vc, 64, BK);
                 if (rc != CCE_OK) return rc;
                 EngineParams p;
-                base_params(&p, Vw, D, B, op->dtype, 1, 1, status);
+                base_params(&p, Vw, D, B, cdt, 1, 1, status);
                 p.out = reinterpret_cast<char*>(a->d_c) + (size_t)v0 * D * esz;
                 p.ldo = D;
-                p.out_dtype = op->dtype;
+                p.out_dtype = split ? CCE_DT_F32 : op->dtype;
                 p.accumulate = 0;
                 if (a->has_filter && a->filter_c) {
                     p.kflags = flag_c;
                     p.ld_kflags = pl.ld_flag_c;
                 }
-                rc = launch_engine<MODE_GEMM>(tmG_mn, tmE_mn, p, dev->sms, st);
+                rc = run_dc(p, tmG_mn);
                 if (rc != CCE_OK) return rc;
             }
 
             // phase 3: dE += G C[v0 : v0 + Vw, :]    (M = B, N = D, K = Vw; A K-major, B MN-major)
             if (a->d_e) {
                 CUtensorMap tmG_k;
-                rc = make_tmap(&tmG_k, g_buf, op->dtype, Vw, B, pl.Vc, BK, BM);
+                rc = make_tmap(&tmG_k, g_buf, cdt, Vw, B, pl.Vc, BK, BM);
                 if (rc != CCE_OK) return rc;
                 EngineParams p;
-                base_params(&p, B, D, Vw, op->dtype, 0, 1, status);
+                base_params(&p, B, D, Vw, cdt, 0, 1, status);
                 p.b_k_off = int(v0);
                 p.out = de32;
                 p.ldo = D;
@@ -869,7 +924,7 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
                     p.kflags = flag_e;
                     p.ld_kflags = pl.ld_flag_e;
                 }
-                rc = launch_engine<MODE_GEMM>(tmG_k, tmC_mn, p, dev->sms, st);
+                rc = run_de(p, tmG_k);
                 if (rc != CCE_OK) return rc;
             }
 
@@ -877,7 +932,7 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
             if (a->d_bias) {
                 const int rows_per_block = 512;
                 dim3 grid((unsigned)cdiv(Vw, 256), (unsigned)cdiv(B, rows_per_block));
-                if (op->dtype == CCE_DT_BF16)
+                if (cdt == CCE_DT_BF16)
                     colsum_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(g_buf),
                                                                        pl.Vc, B, int(Vw), rows_per_block,
                                                                        a->d_bias + v0);
@@ -890,10 +945,10 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
     }
 
     if (a->d_e) {
-        if (a->d_e_f32)
+        if (a->d_e_f32 || split)
             scatter_cast_kernel<float><<<(unsigned)B, 128, 0, st>>>(
                 de32, D, op->valids, op->valids_dtype == CCE_IDX_I64, reinterpret_cast<float*>(a->d_e), D, D, B);
-        else if (op->dtype == CCE_DT_BF16)
+        else if (cdt == CCE_DT_BF16)
             scatter_cast_kernel<__nv_bfloat16><<<(unsigned)B, 128, 0, st>>>(
                 de32, D, op->valids, op->valids_dtype == CCE_IDX_I64, reinterpret_cast<__nv_bfloat16*>(a->d_e), D, D, B);
         else

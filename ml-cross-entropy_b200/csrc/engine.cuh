@@ -244,7 +244,7 @@ __device__ __forceinline__ bool kcand_eval(const EngineParams& p, const KTile& k
         const int sl = ent.x >> 2, kb = ent.x & 3;
         kc.a_mn = sl * BM;
         kc.a_k = kb * BK;
-        kc.b_mn = nblk * BN;
+        kc.b_mn = p.b_mn_off + nblk * BN;
         kc.b_k = ent.y * BN + kb * BK;
         return true;
     }
@@ -253,7 +253,7 @@ __device__ __forceinline__ bool kcand_eval(const EngineParams& p, const KTile& k
         const int sl = ent.x >> 1, kb = ent.x & 1;
         kc.a_mn = kt.h * 128;
         kc.a_k = sl * BM + kb * BK;
-        kc.b_mn = nblk * BN;
+        kc.b_mn = p.b_mn_off + nblk * BN;
         kc.b_k = ent.y * BM + kb * BK;
         return true;
     }

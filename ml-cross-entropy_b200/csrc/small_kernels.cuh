@@ -37,6 +37,29 @@ __global__ void pack_rows_kernel(const uint16_t* __restrict__ src, long long ld_
     for (long long j = D + threadIdx.x; j < Dp; j += blockDim.x) d[j] = 0;
 }
 
+// fp32 operands run on the bf16 tensor path as a three-term split: x = hi + lo with hi = bf16(x),
+// lo = bf16(x - hi), and  e.c ~= e_hi.c_hi + e_hi.c_lo + e_lo.c_hi  (error ~2^-16 relative).
+// This kernel writes one staged row of 3*Dp bf16: pattern 0 (embeddings) = [hi | hi | lo],
+// pattern 1 (classifier) = [hi | lo | hi], each block zero-padded from D to Dp columns, so that
+// one K = 3*Dp contraction of the staged rows gives the three-term sum.  One block per row.
+__global__ void split_rows_kernel(const float* __restrict__ src, long long ld_src, const void* __restrict__ rows,
+                                  int rows_i64, __nv_bfloat16* __restrict__ dst, long long Dp, long long D,
+                                  long long n_rows, int pattern) {
+    const long long i = blockIdx.x;
+    if (i >= n_rows) return;
+    const long long r = rows ? load_index(rows, rows_i64, i) : i;
+    const float* s = src + r * ld_src;
+    __nv_bfloat16* d = dst + i * 3 * Dp;
+    for (long long j = threadIdx.x; j < Dp; j += blockDim.x) {
+        const float x = j < D ? s[j] : 0.0f;
+        const __nv_bfloat16 hi = __float2bfloat16_rn(x);
+        const __nv_bfloat16 lo = __float2bfloat16_rn(x - __bfloat162float(hi));
+        d[j] = hi;
+        d[Dp + j] = pattern == 0 ? hi : lo;
+        d[2 * Dp + j] = pattern == 0 ? lo : hi;
+    }
+}
+
 __global__ void to_f32_kernel(const void* __restrict__ src, int dtype, float* __restrict__ dst, long long n) {
     const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
     if (i < n) dst[i] = load_as_float(src, dtype, i);
@@ -79,17 +102,18 @@ __global__ void indexed_neg_dot_kernel(const T* __restrict__ e, long long lde, c
     const T* ep = e + r * lde;
     const T* cp = c + t * ldc;
     float acc = 0.0f;
-    const bool vec = (D % 8 == 0) && ((reinterpret_cast<uintptr_t>(ep) & 15) == 0) &&
+    constexpr int VE = 16 / int(sizeof(T));  // elements per 16-byte load
+    const bool vec = (D % VE == 0) && ((reinterpret_cast<uintptr_t>(ep) & 15) == 0) &&
                      ((reinterpret_cast<uintptr_t>(cp) & 15) == 0);
     if (vec) {
         const uint4* e4 = reinterpret_cast<const uint4*>(ep);
         const uint4* c4 = reinterpret_cast<const uint4*>(cp);
-        for (long long j = lane; j < D / 8; j += 32) {
+        for (long long j = lane; j < D / VE; j += 32) {
             const uint4 a = __ldg(e4 + j), b = __ldg(c4 + j);
             const T* ah = reinterpret_cast<const T*>(&a);
             const T* bh = reinterpret_cast<const T*>(&b);
 #pragma unroll
-            for (int k = 0; k < 8; ++k) acc = fmaf(float(ah[k]), float(bh[k]), acc);
+            for (int k = 0; k < VE; ++k) acc = fmaf(float(ah[k]), float(bh[k]), acc);
         }
     } else {
         for (long long j = lane; j < D; j += 32) acc = fmaf(float(ep[j]), float(cp[j]), acc);

@@ -170,8 +170,8 @@ def make_operands(
     """Describe ``e`` [n_total, D], ``c`` [V, D], ``bias`` and the valid-row list for the C ABI."""
     if not e.is_cuda:
         raise RuntimeError("cut_cross_entropy (B200 backend) needs CUDA tensors; it has no CPU path")
-    if e.dtype not in (torch.float16, torch.bfloat16):
-        raise NotImplementedError(f"e/c of dtype {e.dtype} are not supported by this backend (bf16 and fp16 are)")
+    if e.dtype not in (torch.float16, torch.bfloat16, torch.float32):
+        raise NotImplementedError(f"e/c of dtype {e.dtype} are not supported by this backend (bf16, fp16, fp32 are)")
     assert e.dim() == 2 and c.dim() == 2 and e.dtype == c.dtype
     assert e.stride(1) == 1 and c.stride(1) == 1
     if valids is not None:

@@ -62,8 +62,8 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
         c_info = TensorInfo(c.dtype, c.requires_grad)
         bias_info = TensorInfo(bias.dtype, bias.requires_grad) if bias is not None else None
 
-        if torch.is_autocast_enabled():
-            amp_dtype = torch.get_autocast_gpu_dtype()
+        if torch.is_autocast_enabled("cuda"):
+            amp_dtype = torch.get_autocast_dtype("cuda")
             e, c = e.to(dtype=amp_dtype), c.to(dtype=amp_dtype)
             if bias is not None:
                 bias = bias.to(dtype=amp_dtype)
@@ -216,7 +216,7 @@ def cce_linear_cross_entropy(
     e = e.flatten(0, -2)
     targets = targets.flatten()
 
-    amp_dtype = torch.get_autocast_gpu_dtype() if torch.is_autocast_enabled() else e.dtype
+    amp_dtype = torch.get_autocast_dtype("cuda") if torch.is_autocast_enabled("cuda") else e.dtype
     params = CCEParams(
         targets=targets,
         valids=valids,

@@ -90,7 +90,7 @@ def _logits(e, c, bias, softcap):
     return x
 
 
-@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("softcap", [None, 20.0])
 @pytest.mark.parametrize("has_bias", [False, True])
 @pytest.mark.parametrize("shape", SHAPES)
@@ -100,8 +100,12 @@ def test_lse_kernel(dtype, softcap, has_bias, shape):
     torch.backends.cuda.matmul.allow_tf32 = False
     N, V, D = shape
     e, c, bias, _ = planted_inputs(N, V, D, dtype, DEV, bias=has_bias)
-    gt = torch.logsumexp(_logits(e.float(), c.float(), None if bias is None else bias.float(), softcap), -1)
+    gt = torch.logsumexp(_logits(e.double(), c.double(), None if bias is None else bias.double(), softcap), -1).float()
+    # yardstick: the same PyTorch code in the input dtype (for fp32: with TF32 matmuls, which is what
+    # the reference's kernels use under float32_matmul_precision("high"), tests/test_cce_lse.py:44)
+    torch.backends.cuda.matmul.allow_tf32 = dtype == torch.float32
     ref = torch.logsumexp(_logits(e, c, bias, softcap).float(), -1)
+    torch.backends.cuda.matmul.allow_tf32 = False
     lse = cce_lse_forward_kernel(e, c, bias, softcap=softcap)
     assert lse.dtype == torch.float32 and lse.shape == (N,)
     assert ((gt - lse).abs() <= (gt - ref).abs() + 1e-5).all(), (gt - lse).abs().max()
@@ -112,7 +116,7 @@ def test_lse_kernel(dtype, softcap, has_bias, shape):
         torch.testing.assert_close(lse_v, lse[valids], rtol=0, atol=1e-6)
 
 
-@pytest.mark.parametrize("dtype,tol", [(torch.float16, 1e-3), (torch.bfloat16, 1e-2)])
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-6), (torch.float16, 1e-3), (torch.bfloat16, 1e-2)])
 @pytest.mark.parametrize("softcap", [None, 20.0])
 @pytest.mark.parametrize("has_bias", [False, True])
 @pytest.mark.parametrize("shape", SHAPES)
@@ -122,8 +126,10 @@ def test_indexed_dot_kernel(dtype, tol, softcap, has_bias, shape):
     N, V, D = shape
     e, c, bias, t = planted_inputs(N, V, D, dtype, DEV, bias=has_bias)
     fb = None if bias is None else bias.float()
-    gt = -_logits(e.float(), c.float(), fb, softcap)[torch.arange(N), t]
+    gt = -_logits(e.double(), c.double(), None if bias is None else bias.double(), softcap)[torch.arange(N), t].float()
+    torch.backends.cuda.matmul.allow_tf32 = dtype == torch.float32  # fp32 yardstick: TF32, as in the reference's tests
     ref = -_logits(e, c, bias, softcap).float()[torch.arange(N), t]
+    torch.backends.cuda.matmul.allow_tf32 = False
     out = indexed_neg_dot_forward_kernel(e, c, t, bias, softcap=softcap, out_dtype=torch.float32)
     assert ((gt - out).abs() <= (gt - ref).abs() + tol).all()
     # the kernel accumulates in fp32: it should in fact be close to the float32 answer
@@ -166,7 +172,7 @@ def test_workspace_too_small_and_bad_arguments_are_reported():
     assert need > 256
     rc = L.cce_b200_lse_forward(op, lse.data_ptr(), None, ws.data_ptr(), 256, torch.cuda.current_stream().cuda_stream)
     assert rc == -3 and b"workspace" in L.cce_b200_strerror(rc)
-    op.dtype = _native.DT_F32
+    op.dtype = 7  # no such element type
     assert L.cce_b200_lse_workspace_bytes(op) == 0
     rc = L.cce_b200_lse_forward(op, lse.data_ptr(), None, ws.data_ptr(), 256, torch.cuda.current_stream().cuda_stream)
     assert rc == -1

@@ -72,7 +72,7 @@ def _make(shape, dtype, has_bias, invalids, seed=0):
     return e, c, bias, t.view(4, -1)
 
 
-@pytest.mark.parametrize("dtype,tol", [(torch.float16, 1e-3), (torch.bfloat16, 1e-2)])
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.float16, 1e-3), (torch.bfloat16, 1e-2)])
 @pytest.mark.parametrize("softcap", [None, 20.0])
 @pytest.mark.parametrize("has_bias", [False, True])
 @pytest.mark.parametrize("shift", [0, 2])
@@ -85,7 +85,9 @@ def test_loss_forward(dtype, tol, softcap, has_bias, shift, invalids, shape):
     e, c, bias, targets = _make(shape, dtype, has_bias, invalids)
     with torch.no_grad():
         gt, gt_lse = _ref_loss(e, c, bias, targets, softcap, shift, "none", fp32=True)
+        torch.backends.cuda.matmul.allow_tf32 = dtype == torch.float32  # the yardstick for fp32 is TF32
         ref, _ = _ref_loss(e, c, bias, targets, softcap, shift, "none", fp32=False)
+        torch.backends.cuda.matmul.allow_tf32 = False
         loss, lse = linear_cross_entropy(e, c, targets, bias=bias, softcap=softcap, shift=shift,
                                          reduction="none", return_lse=True)  # fmt: skip
     assert loss.shape == gt.shape and lse.shape == gt.shape and loss.dtype == torch.float32
@@ -126,6 +128,19 @@ def test_loss_backward_fp16(impl, softcap, has_bias, shift, reduction, shape):
     _backward_case(torch.float16, 1e-3, impl, softcap, has_bias, shift, True, reduction, True, shape)
 
 
+@pytest.mark.parametrize("impl", ["cce", "cce_exact", "cce_kahan_full_c"])
+@pytest.mark.parametrize("softcap", [None, 20.0])
+@pytest.mark.parametrize("has_bias", [False, True])
+@pytest.mark.parametrize("shift", [False, True])
+@pytest.mark.parametrize("reduction", ["none", "mean", "sum"])
+@pytest.mark.parametrize("z_loss", [True, False])
+@pytest.mark.parametrize("shape", [(256, 512, 128), (252, 507, 123)])
+def test_loss_backward_fp32(impl, softcap, has_bias, shift, reduction, z_loss, shape):
+    """fp32 tensors (three-term bf16 split on the tensor cores); tolerance of the reference's fp32
+    cases, tests/test_cce_loss_backward.py:81."""
+    _backward_case(torch.float32, 5e-4, impl, softcap, has_bias, shift, True, reduction, z_loss, shape)
+
+
 def _backward_case(dtype, tol, impl, softcap, has_bias, shift, invalids, reduction, z_loss, shape):
     from cut_cross_entropy import linear_cross_entropy
 
@@ -144,7 +159,9 @@ def _backward_case(dtype, tol, impl, softcap, has_bias, shift, invalids, reducti
         return _objective(loss, lse, targets, shift, reduction, z_loss)
 
     gt = _grads(lambda: torch_fn(True), e, c, bias)
+    torch.backends.cuda.matmul.allow_tf32 = dtype == torch.float32  # the yardstick for fp32 is TF32
     ref = _grads(lambda: torch_fn(False), e, c, bias)
+    torch.backends.cuda.matmul.allow_tf32 = False
     got = _grads(ours, e, c, bias)
     for name, g, r, o in zip(("de", "dc", "dbias"), gt, ref, got):
         assert o.dtype == g.dtype and o.shape == g.shape
@@ -298,7 +315,7 @@ def test_error_behaviour_matches_reference():
     with pytest.raises(AssertionError):
         linear_cross_entropy(e, c[:, :16], t)
     with pytest.raises(NotImplementedError):
-        linear_cross_entropy(e.float(), c.float(), t)
+        linear_cross_entropy(e.double(), c.double(), t)
 
 
 @pytest.mark.parametrize("softcap", [None, 30.0])
