@@ -34,7 +34,7 @@ import torch  # noqa: E402
 METRIC = "linear-CE fwd+bwd tokens/s"
 UNIT = "tokens/s"
 
-# name -> (e shape, V, sigma_c, ignored fraction, options)     [SURVEY section 8(d) recipe]
+# name -> e shape, V, std of the classifier entries, ignored-label fraction, options of the call
 CONFIGS = {
     "gemma2-2b-head": dict(idx=1, e_shape=(8192, 2304), V=256000, sigma=0.02, ignored=0.05, kw=dict(impl="cce")),
     "llama3-8b-head-shift": dict(idx=2, e_shape=(4, 4096, 4096), V=128256, sigma=0.015, ignored=0.02,
