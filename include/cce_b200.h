@@ -11,6 +11,9 @@
  *                                (indexed_neg_dot_forward_kernel)
  *   cce_b200_backward         <- cut_cross_entropy/cce_backward.py:346-521
  *                                (cce_backward_kernel)
+ *   cce_b200_valid_rows       <- cut_cross_entropy/utils.py:28-49
+ *                                (_build_flat_valids, the list of rows the three
+ *                                launchers above take as `valids`)
  *
  * Conventions
  *   - every pointer is a DEVICE pointer unless stated otherwise; the library
@@ -120,6 +123,21 @@ int cce_b200_lse_forward_static(const cce_b200_operands* op, float* lse /* [n_ro
 int cce_b200_indexed_neg_dot(const cce_b200_operands* op, const int64_t* targets /* [n_total] */,
                              int64_t shift, int64_t vocab_start, float* out /* [n_rows] */,
                              void* stream);
+
+/* The rows of the flattened embedding matrix that enter the loss, in ascending order:
+ * row r (0 <= r < n_total) is paired with label targets[r + shift] and is listed when that label
+ * lies in the same sequence (r % seq_len < seq_len - shift) and differs from ignore_index.
+ * rows_out (int32 or int64 by rows_dtype, room for n_total entries) receives the list and
+ * count_out[0] (a device int64) its length; the caller reads the count back (the one host
+ * synchronisation of the forward pass) and passes rows_out/count on as `valids`/`n_rows`.
+ * n_total must be a multiple of seq_len.  Two small launches, no atomics: the list is
+ * deterministic; its workspace carries no status word (these kernels never wait).  Replaces
+ * (cut_cross_entropy/utils.py:28-49), which the reference evaluates with
+ * torch.nonzero / boolean indexing. */
+size_t cce_b200_valid_rows_workspace_bytes(int64_t n_total);
+int cce_b200_valid_rows(const int64_t* targets /* [n_total] */, int64_t n_total, int64_t seq_len,
+                        int64_t shift, int64_t ignore_index, void* rows_out, int rows_dtype,
+                        int64_t* count_out, void* workspace, size_t workspace_bytes, void* stream);
 
 typedef struct cce_b200_backward_args {
     cce_b200_operands op;

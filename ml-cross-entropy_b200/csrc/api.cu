@@ -683,6 +683,38 @@ int cce_b200_indexed_neg_dot(const cce_b200_operands* op, const int64_t* targets
     return CCE_OK;
 }
 
+size_t cce_b200_valid_rows_workspace_bytes(int64_t n_total) {
+    if (n_total < 0) return 0;
+    return align_up((size_t)cdiv(std::max<long long>(n_total, 1), VR_BLOCK) * sizeof(int), 256);
+}
+
+int cce_b200_valid_rows(const int64_t* targets, int64_t n_total, int64_t seq_len, int64_t shift,
+                        int64_t ignore_index, void* rows_out, int rows_dtype, int64_t* count_out, void* workspace,
+                        size_t workspace_bytes, void* stream) {
+    if (!count_out || n_total < 0 || shift < 0 || seq_len <= 0 || n_total % seq_len != 0) return CCE_ERR_ARG;
+    if (rows_dtype != CCE_IDX_I32 && rows_dtype != CCE_IDX_I64) return CCE_ERR_ARG;
+    if (rows_dtype == CCE_IDX_I32 && n_total > 0x7fffffffLL) return CCE_ERR_TOO_LARGE;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (n_total == 0 || shift >= seq_len) {
+        CCE_CUDA(cudaMemsetAsync(count_out, 0, sizeof(int64_t), st));
+        return CCE_OK;
+    }
+    if (!targets || !rows_out || !workspace) return CCE_ERR_ARG;
+    if (workspace_bytes < cce_b200_valid_rows_workspace_bytes(n_total)) return CCE_ERR_WORKSPACE;
+    const long long blocks = cdiv(n_total, VR_BLOCK);
+    if (blocks > 0x7fffffffLL) return CCE_ERR_TOO_LARGE;
+    int* block_counts = reinterpret_cast<int*>(workspace);
+    const long long* t = reinterpret_cast<const long long*>(targets);
+    valid_rows_count_kernel<<<(unsigned)blocks, VR_THREADS, 0, st>>>(t, n_total, seq_len, shift, ignore_index,
+                                                                      block_counts);
+    CCE_LAUNCH_CHECK();
+    valid_rows_write_kernel<<<(unsigned)blocks, VR_THREADS, 0, st>>>(
+        t, n_total, seq_len, shift, ignore_index, block_counts, rows_out, rows_dtype == CCE_IDX_I64,
+        reinterpret_cast<long long*>(count_out));
+    CCE_LAUNCH_CHECK();
+    return CCE_OK;
+}
+
 size_t cce_b200_backward_workspace_bytes(const cce_b200_backward_args* a) {
     if (!a || check_operands(&a->op) != CCE_OK) return 0;
     return plan_bwd(a).total;

@@ -156,6 +156,8 @@ struct TileIter {
             n_items = pass.slot_hi - pass.slot_lo;
         } else if (MODE == MODE_GEMM && p.sparse == 2) {
             n_items = (pass.vt_hi - pass.vt_lo) * 2 * p.n_nblk;
+        } else if (MODE == MODE_GEMM && p.sparse == 1 && p.accumulate == 2 && pass.slot_lo == pass.slot_hi) {
+            n_items = 0;  // an adding launch over an empty pass has nothing to add anywhere
         } else {
             n_items = p.n_mblk * p.n_nblk;
         }
@@ -765,6 +767,13 @@ engine_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const long long t_start = (kTrace && p.wait_cycles) ? clock64() : 0;
+
+    {   // a CTA without a first item (a small problem, or an empty pass of the block-list backward)
+        // leaves before it sets up barriers or tensor memory; the test is uniform over the CTA
+        const PassInfo pass = load_pass(p);
+        const TileIter<MODE> probe(p, pass);
+        if (int(blockIdx.x) >= probe.n_items) return;
+    }
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < NSTAGE; ++i) {

@@ -195,33 +195,70 @@ __global__ void tile_index_kernel(const uint8_t* __restrict__ act, int n_rb, int
         col_s[vt] = cnt;
     }
     __syncthreads();
-    if (tid == 0) {  // column starts and the pass boundaries
-        int run = 0, pass = 0, pass_vt0 = 0, pass_s0 = 0;
-        for (int vt = 0; vt < n_vt; ++vt) {
-            const int cnt = col_s[vt];
-            if (run - pass_s0 + cnt > capacity && pass + 1 < max_pass) {  // close the pass before this column
-                pass_info[4 * pass + 0] = pass_vt0;
-                pass_info[4 * pass + 1] = vt;
-                pass_info[4 * pass + 2] = pass_s0;
-                pass_info[4 * pass + 3] = run;
-                ++pass;
-                pass_vt0 = vt;
-                pass_s0 = run;
+    {   // column starts: exclusive scan of the counts, a contiguous run of columns per thread
+        __shared__ int warp_sum[32];
+        const int per = (n_vt + nthr - 1) / nthr;
+        const int beg = min(tid * per, n_vt), end = min(beg + per, n_vt);
+        int local = 0;
+        for (int vt = beg; vt < end; ++vt) local += col_s[vt];
+        int incl = local;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += t;
+        }
+        if (lane == 31) warp_sum[warp] = incl;
+        __syncthreads();
+        if (warp == 0) {
+            int v = lane < nwarp ? warp_sum[lane] : 0;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_up_sync(0xffffffffu, v, o);
+                if (lane >= o) v += t;
             }
-            col_ptr[vt] = run;
+            warp_sum[lane] = v;
+        }
+        __syncthreads();
+        int run = incl - local + (warp > 0 ? warp_sum[warp - 1] : 0);
+        for (int vt = beg; vt < end; ++vt) {
+            const int cnt = col_s[vt];
             col_s[vt] = run;
+            col_ptr[vt] = run;
             run += cnt;
         }
-        col_ptr[n_vt] = run;
-        pass_info[4 * pass + 0] = pass_vt0;
-        pass_info[4 * pass + 1] = n_vt;
-        pass_info[4 * pass + 2] = pass_s0;
-        pass_info[4 * pass + 3] = run;
+        if (tid == nthr - 1) {
+            col_s[n_vt] = warp_sum[nwarp - 1];
+            col_ptr[n_vt] = warp_sum[nwarp - 1];
+        }
+    }
+    __syncthreads();
+    if (tid == 0) {  // pass boundaries: each pass takes whole columns while it holds <= capacity slots
+        const int total = col_s[n_vt];
+        int pass = 0, vt0 = 0;
+        while (true) {
+            const int s0 = col_s[vt0];
+            int vt_end = n_vt;
+            if (pass + 1 < max_pass && total - s0 > capacity) {
+                int lo = vt0 + 1, hi = n_vt;  // largest v in [lo, hi] with col_s[v] - s0 <= capacity
+                while (lo < hi) {
+                    const int mid = (lo + hi + 1) >> 1;
+                    if (col_s[mid] - s0 <= capacity) lo = mid; else hi = mid - 1;
+                }
+                vt_end = lo;
+            }
+            pass_info[4 * pass + 0] = vt0;
+            pass_info[4 * pass + 1] = vt_end;
+            pass_info[4 * pass + 2] = s0;
+            pass_info[4 * pass + 3] = col_s[vt_end];
+            if (vt_end == n_vt) break;
+            ++pass;
+            vt0 = vt_end;
+        }
         for (int q = pass + 1; q < max_pass; ++q) {
             pass_info[4 * q + 0] = n_vt;
             pass_info[4 * q + 1] = n_vt;
-            pass_info[4 * q + 2] = run;
-            pass_info[4 * q + 3] = run;
+            pass_info[4 * q + 2] = total;
+            pass_info[4 * q + 3] = total;
         }
     } else if (tid == 32) {  // row starts
         int run = 0;
@@ -291,6 +328,11 @@ __global__ void klist_build_kernel(const int* __restrict__ pass_info, const int*
     const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     const int vt_lo = pass_info[0], vt_hi = pass_info[1], s_lo = pass_info[2], s_hi = pass_info[3];
+    if (s_lo == s_hi) {  // an empty pass: every list is empty
+        if (lane == 0 && w < n_rb) de_cnt[w] = 0;
+        if (lane == 0 && w >= n_rb && w < n_rb + 2 * n_vt) dc_cnt[w - n_rb] = 0;
+        return;
+    }
     if (w < n_rb) {
         const int e0 = row_ptr[w], n = (row_ptr[w + 1] - e0) * 4;
         int2* out = de_list + 4 * e0;
@@ -372,6 +414,85 @@ __global__ void scatter_cast_kernel(const float* __restrict__ src, long long ld_
     const float* s = src + i * ld_src;
     T* d = dst + r * ld_dst;
     for (long long j = threadIdx.x; j < D; j += blockDim.x) d[j] = T(s[j]);
+}
+
+// ---- rows that enter the loss (ordered stream compaction in two launches)
+// Row r of the flattened embeddings is paired with label targets[r + shift]; it is valid when the
+// label lies in the same sequence (r % seq_len < seq_len - shift) and differs from ignore_index.
+constexpr int VR_THREADS = 256;
+constexpr int VR_PER_THREAD = 8;
+constexpr int VR_BLOCK = VR_THREADS * VR_PER_THREAD;
+
+__device__ __forceinline__ uint32_t valid_row_bits(const long long* __restrict__ targets, long long n_total,
+                                                   long long seq_len, long long shift, long long ignore_index,
+                                                   long long r0) {
+    uint32_t bits = 0;
+#pragma unroll
+    for (int j = 0; j < VR_PER_THREAD; ++j) {
+        const long long r = r0 + j;
+        if (r < n_total && (shift == 0 || r % seq_len < seq_len - shift) && targets[r + shift] != ignore_index)
+            bits |= 1u << j;
+    }
+    return bits;
+}
+
+// Sum over the block of one int per thread (VR_THREADS threads); every thread gets the total and
+// its own exclusive prefix.
+__device__ __forceinline__ int block_scan_256(int v, int* total) {
+    __shared__ int warp_tot[VR_THREADS / 32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int incl = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += t;
+    }
+    __syncthreads();  // the previous use of warp_tot is over
+    if (lane == 31) warp_tot[warp] = incl;
+    __syncthreads();
+    int before = 0, all = 0;
+#pragma unroll
+    for (int w = 0; w < VR_THREADS / 32; ++w) {
+        const int t = warp_tot[w];
+        if (w < warp) before += t;
+        all += t;
+    }
+    *total = all;
+    return before + incl - v;
+}
+
+// block_counts[b] = valid rows among rows [b * VR_BLOCK, (b + 1) * VR_BLOCK)
+__global__ void __launch_bounds__(VR_THREADS)
+valid_rows_count_kernel(const long long* __restrict__ targets, long long n_total, long long seq_len,
+                        long long shift, long long ignore_index, int* __restrict__ block_counts) {
+    const long long r0 = (long long)blockIdx.x * VR_BLOCK + threadIdx.x * VR_PER_THREAD;
+    int total;
+    block_scan_256(__popc(valid_row_bits(targets, n_total, seq_len, shift, ignore_index, r0)), &total);
+    if (threadIdx.x == 0) block_counts[blockIdx.x] = total;
+}
+
+// rows_out[k] = k-th valid row (ascending), as int32 or int64; count_out[0] = number of valid rows
+__global__ void __launch_bounds__(VR_THREADS)
+valid_rows_write_kernel(const long long* __restrict__ targets, long long n_total, long long seq_len,
+                        long long shift, long long ignore_index, const int* __restrict__ block_counts,
+                        void* __restrict__ rows_out, int rows_i64, long long* __restrict__ count_out) {
+    int before = 0;  // valid rows of the blocks before this one
+    for (int b = threadIdx.x; b < (int)blockIdx.x; b += VR_THREADS) before += block_counts[b];
+    int base;
+    block_scan_256(before, &base);
+    const long long r0 = (long long)blockIdx.x * VR_BLOCK + threadIdx.x * VR_PER_THREAD;
+    const uint32_t bits = valid_row_bits(targets, n_total, seq_len, shift, ignore_index, r0);
+    int total;
+    long long k = (long long)base + block_scan_256(__popc(bits), &total);
+#pragma unroll
+    for (int j = 0; j < VR_PER_THREAD; ++j) {
+        if (bits & (1u << j)) {
+            if (rows_i64) reinterpret_cast<long long*>(rows_out)[k] = r0 + j;
+            else reinterpret_cast<int*>(rows_out)[k] = int(r0 + j);
+            ++k;
+        }
+    }
+    if (blockIdx.x == gridDim.x - 1 && threadIdx.x == 0) count_out[0] = (long long)base + total;
 }
 
 }  // namespace cce

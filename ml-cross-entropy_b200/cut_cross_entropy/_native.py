@@ -27,6 +27,8 @@ EXPORTS = (
     "cce_b200_tile_max_elems",
     "cce_b200_lse_forward_static",
     "cce_b200_indexed_neg_dot",
+    "cce_b200_valid_rows_workspace_bytes",
+    "cce_b200_valid_rows",
     "cce_b200_backward_workspace_bytes",
     "cce_b200_backward",
     "cce_b200_gemm",
@@ -113,6 +115,12 @@ def lib() -> ctypes.CDLL:
     L.cce_b200_lse_forward_static.argtypes = [POINTER(Operands), c_void_p, c_void_p]
     L.cce_b200_indexed_neg_dot.restype = c_int32
     L.cce_b200_indexed_neg_dot.argtypes = [POINTER(Operands), c_void_p, c_int64, c_int64, c_void_p, c_void_p]
+    L.cce_b200_valid_rows_workspace_bytes.restype = c_size_t
+    L.cce_b200_valid_rows_workspace_bytes.argtypes = [c_int64]
+    L.cce_b200_valid_rows.restype = c_int32
+    L.cce_b200_valid_rows.argtypes = [
+        c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p, c_int32, c_void_p, c_void_p, c_size_t, c_void_p,
+    ]  # fmt: skip
     L.cce_b200_backward_workspace_bytes.restype = c_size_t
     L.cce_b200_backward_workspace_bytes.argtypes = [POINTER(BackwardArgs)]
     L.cce_b200_backward.restype = c_int32

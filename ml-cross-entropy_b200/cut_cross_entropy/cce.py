@@ -17,7 +17,7 @@ from .cce_backward import cce_backward_kernel
 from .cce_lse_forward import cce_lse_forward_kernel
 from .constants import IGNORE_INDEX
 from .indexed_dot import indexed_neg_dot_forward_kernel
-from .utils import TensorInfo, _build_flat_valids, _handle_eps, handle_reduction_none
+from .utils import PendingValidRows, TensorInfo, _handle_eps, handle_reduction_none, launch_flat_valids
 from .vocab_parallel.utils import VocabParallelOptions, vp_merge_forward
 
 
@@ -36,6 +36,8 @@ class CCEParams:
     filter_c_grad: bool
     vocab_parallel_options: VocabParallelOptions | None
     return_lse: bool
+    # the valid-row list while the GPU is still writing it; forward() turns it into `valids`
+    pending_valids: PendingValidRows | None = None
 
 
 def _reduce_loss(nll: torch.Tensor, params: CCEParams) -> torch.Tensor:
@@ -70,6 +72,10 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
 
         vp = params.vocab_parallel_options
         vocab_start = vp.start if vp is not None else 0
+
+        if params.pending_valids is not None:  # everything above ran while the list was being built
+            params.valids = params.pending_valids.resolve()
+            params.pending_valids = None
 
         # The filtered backward can skip recomputing logit tiles that provably hold nothing above the
         # threshold if the forward records each tile's largest logit; worth it only when every
@@ -211,7 +217,7 @@ def cce_linear_cross_entropy(
     e = e.contiguous()
     targets = targets.contiguous()
     shift = int(shift)
-    valids = _build_flat_valids(targets, ignore_index, shift)
+    pending = launch_flat_valids(targets, ignore_index, shift)
 
     e = e.flatten(0, -2)
     targets = targets.flatten()
@@ -219,7 +225,7 @@ def cce_linear_cross_entropy(
     amp_dtype = torch.get_autocast_dtype("cuda") if torch.is_autocast_enabled("cuda") else e.dtype
     params = CCEParams(
         targets=targets,
-        valids=valids,
+        valids=None,
         softcap=softcap,
         reduction=reduction,
         filter_eps=_handle_eps(filter_eps, amp_dtype),
@@ -231,5 +237,6 @@ def cce_linear_cross_entropy(
         filter_c_grad=filter_c_grad and filter_eps is not None,
         vocab_parallel_options=vocab_parallel_options,
         return_lse=return_lse,
+        pending_valids=pending,
     )
     return linear_cross_entropy_apply(e, c, bias, params)

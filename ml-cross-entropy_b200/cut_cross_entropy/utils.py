@@ -34,15 +34,59 @@ def _handle_eps(filter_eps: float | str | None, dtype: torch.dtype) -> float | N
     raise RuntimeError(f"Unknown eps {filter_eps=}")
 
 
+class PendingValidRows:
+    """A list of valid rows that the GPU is still writing: the kernels are enqueued, the length
+    of the list has not been read back.  :meth:`resolve` reads it (the one host synchronisation of
+    the forward pass) and returns what ``_build_flat_valids`` returns."""
+
+    def __init__(self, rows: torch.Tensor, count: torch.Tensor, n_total: int, shift: int):
+        self.rows, self.count, self.n_total, self.shift = rows, count, n_total, shift
+
+    def resolve(self) -> torch.Tensor | None:
+        n = int(self.count.item())
+        if self.shift == 0 and n == self.n_total:
+            return None
+        return self.rows[:n]
+
+
+def launch_flat_valids(targets: torch.Tensor, ignore_index: int, shift: int) -> PendingValidRows:
+    """Enqueue ``cce_b200_valid_rows`` on the current stream for CUDA ``targets`` of shape
+    ``[..., seq_len]``; host work that does not need the list can follow before ``resolve()``."""
+    from . import _native
+
+    flat = targets.reshape(-1)
+    if flat.dtype != torch.int64:
+        flat = flat.long()
+    flat = flat.contiguous()
+    n_total = flat.numel()
+    seq = targets.size(-1) if targets.dim() > 0 else 1
+    L = _native.lib()
+    rows = torch.empty((n_total,), dtype=torch.int32 if shift == 0 else torch.int64, device=targets.device)
+    count = torch.empty((1,), dtype=torch.int64, device=targets.device)
+    ws = _native.workspace(L.cce_b200_valid_rows_workspace_bytes(n_total), targets.device)
+    with torch.cuda.device(targets.device):
+        rc = L.cce_b200_valid_rows(
+            flat.data_ptr(), n_total, max(seq, 1), shift, ignore_index, rows.data_ptr(),
+            _native.IDX_I32 if shift == 0 else _native.IDX_I64, count.data_ptr(), ws.data_ptr(), ws.numel(),
+            _native.stream_ptr(targets.device),
+        )  # fmt: skip
+    _native.check(rc, "cce_b200_valid_rows")
+    return PendingValidRows(rows, count, n_total, shift)
+
+
 def _build_flat_valids(targets: torch.Tensor, ignore_index: int, shift: int) -> torch.Tensor | None:
     """Rows of the flattened ``e`` that enter the loss (reference utils.py:28-49).
 
     Row ``r`` of ``e`` is paired with label ``targets.flatten()[r + shift]``.
     Without a shift the result is ``None`` when no label is ignored, else int32
     row numbers; with a shift it is always an int64 tensor (rows whose label
-    would fall past the end of their sequence are never listed).  The
-    ``nonzero`` inside synchronises the stream, as it does in the reference.
+    would fall past the end of their sequence are never listed).  Reading the
+    length of the list synchronises the stream, as the ``nonzero`` of the
+    reference does.  CUDA labels go through ``cce_b200_valid_rows``; the
+    PyTorch expressions below serve labels in host memory.
     """
+    if targets.is_cuda:
+        return launch_flat_valids(targets, ignore_index, shift).resolve()
     if shift == 0:
         keep = (targets.reshape(-1) != ignore_index).nonzero().squeeze(1)
         if keep.numel() == targets.numel():

@@ -212,3 +212,53 @@ def test_two_cta_forward_kernel_matches_the_default_one():
             results.append(torch.load(path))
     for a, b in zip(*results):
         torch.testing.assert_close(a, b, rtol=0, atol=1e-5)
+
+
+@pytest.mark.parametrize("shape", [(4, 32), (1, 1), (3, 2047), (7, 3001), (64, 1024), (2, 3, 500)])
+@pytest.mark.parametrize("shift", [0, 1, 3])
+@pytest.mark.parametrize("ignored", [0.0, 0.3, 1.0])
+def test_valid_rows_kernel_matches_the_reference_expressions(shape, shift, ignored):
+    """cce_b200_valid_rows against the reference's own formulation (utils.py:28-49: nonzero
+    without a shift, boolean indexing of an arange with one), bit-exact, dtype included."""
+    from cut_cross_entropy.utils import _build_flat_valids
+
+    g = torch.Generator().manual_seed(sum(shape) + shift)
+    t = torch.randint(0, 1000, shape, generator=g)
+    if ignored:
+        t[torch.rand(shape, generator=g) < ignored] = -100
+    want = _build_flat_valids(t, -100, shift)  # labels in host memory: the PyTorch expressions
+    for dtype in (torch.int64, torch.int32):
+        got = _build_flat_valids(t.to(DEV, dtype), -100, shift)
+        if want is None:
+            assert got is None
+            continue
+        assert got is not None and got.dtype == want.dtype and got.is_cuda
+        assert torch.equal(got.cpu(), want)
+    # another ignore_index
+    want = _build_flat_valids(t, 7, shift)
+    got = _build_flat_valids(t.to(DEV), 7, shift)
+    assert (want is None and got is None) or torch.equal(got.cpu(), want)
+
+
+def test_valid_rows_entry_point_rejects_bad_arguments():
+    from cut_cross_entropy import _native
+
+    L = _native.lib()
+    t = torch.zeros(64, dtype=torch.int64, device=DEV)
+    rows = torch.empty(64, dtype=torch.int32, device=DEV)
+    cnt = torch.empty(1, dtype=torch.int64, device=DEV)
+    ws = _native.workspace(L.cce_b200_valid_rows_workspace_bytes(64), DEV)
+    st = torch.cuda.current_stream().cuda_stream
+    args = (t.data_ptr(), 64, 16, 0, -100, rows.data_ptr(), _native.IDX_I32, cnt.data_ptr(), ws.data_ptr())
+    assert L.cce_b200_valid_rows(*args, ws.numel(), st) == 0
+    assert int(cnt.item()) == 64
+    assert L.cce_b200_valid_rows(*args, 0, st) == -3  # workspace too small
+    bad = list(args)
+    bad[2] = 24  # n_total is not a multiple of seq_len
+    assert L.cce_b200_valid_rows(*bad, ws.numel(), st) == -1
+    bad = list(args)
+    bad[6] = 5  # no such index type
+    assert L.cce_b200_valid_rows(*bad, ws.numel(), st) == -1
+    bad = list(args)
+    bad[7] = None  # nowhere to put the count
+    assert L.cce_b200_valid_rows(*bad, ws.numel(), st) == -1
