@@ -516,9 +516,65 @@ __device__ __forceinline__ void store_g16(void* dst, const float (&v)[32], bool 
             w[j] = *reinterpret_cast<uint32_t*>(&h);
         }
     }
-    uint4* d = reinterpret_cast<uint4*>(dst);
+    if ((reinterpret_cast<uintptr_t>(dst) & 31) == 0) {  // two full 32-byte sectors
+        st_global_v8(dst, w);
+        st_global_v8(reinterpret_cast<char*>(dst) + 32, w + 8);
+    } else {
+        uint4* d = reinterpret_cast<uint4*>(dst);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) d[j] = o[j];
+        for (int j = 0; j < 4; ++j) d[j] = o[j];
+    }
+}
+
+// One row's 32 consecutive columns of a product tile (fp32 accumulator bits in r) to the output:
+// store, read-add-store (accumulate == 1) or red.add (accumulate == 2); fp32 or 16-bit output.
+__device__ __forceinline__ void gemm_store_chunk(const EngineParams& p, int row, int col0, const uint32_t (&r)[32]) {
+    float x[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(r[j]);
+    const int ncol = min(32, p.N - col0);
+    if (p.out_dtype == 2) {
+        float* dst = reinterpret_cast<float*>(p.out) + (size_t)row * p.ldo + col0;
+        const bool vec = (ncol == 32) && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
+        if (vec && p.accumulate == 2) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) red_add_v4(dst + 4 * j, x[4 * j], x[4 * j + 1], x[4 * j + 2], x[4 * j + 3]);
+        } else if (vec && !p.accumulate && (reinterpret_cast<uintptr_t>(dst) & 31) == 0) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) st_global_v8(dst + 8 * j, r + 8 * j);
+        } else if (vec) {
+            float4* d4 = reinterpret_cast<float4*>(dst);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                float4 v = make_float4(x[4 * j], x[4 * j + 1], x[4 * j + 2], x[4 * j + 3]);
+                if (p.accumulate) {
+                    const float4 o = d4[j];
+                    v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                }
+                d4[j] = v;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (j < ncol) dst[j] = p.accumulate ? dst[j] + x[j] : x[j];
+        }
+    } else {
+        char* dst = reinterpret_cast<char*>(p.out) + ((size_t)row * p.ldo + col0) * 2;
+        const bool vec = (ncol == 32) && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
+        if (vec) {
+            store_g16(dst, x, p.out_dtype == 1);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                if (j < ncol) {
+                    if (p.out_dtype == 1)
+                        reinterpret_cast<__nv_bfloat16*>(dst)[j] = __float2bfloat16_rn(x[j]);
+                    else
+                        reinterpret_cast<__half*>(dst)[j] = __float2half_rn(x[j]);
+                }
+            }
+        }
+    }
 }
 
 template <int MODE>
@@ -579,11 +635,32 @@ __device__ void epilogue_loop(const EngineParams& p, const EngineSmem& s, uint32
         float tile_rowmax = -INFINITY;  // MODE_LSE: max logit (log2 units) of this row within the tile
         if (MODE == MODE_GEMM && acc_is_empty && p.accumulate) {
             // nothing to add
+        } else if constexpr (MODE == MODE_GEMM) {
+            // Store-only epilogue: two 32-column loads from TMEM are in flight per wait, so half of
+            // the load latency is exposed compared with one load per wait.
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; c += 2) {
+                const int col0 = it.nblk * BN + c * 32;
+                if (col0 >= p.N) break;  // warp-uniform
+                uint32_t r0[32], r1[32];
+                if (!acc_is_empty) {
+                    tmem_ld32(taddr + c * 32, r0);
+                    tmem_ld32(taddr + c * 32 + 32, r1);
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) r0[j] = r1[j] = 0u;
+                }
+                if (row_ok) {
+                    gemm_store_chunk(p, row, col0, r0);
+                    if (col0 + 32 < p.N) gemm_store_chunk(p, row, col0 + 32, r1);
+                }
+            }
         } else {
             uint32_t flag_bits = 0;  // MODE_PGRAD: activity of the current 64-column group
-            // TMEM -> registers is double-buffered: the load of chunk c+1 is in flight while chunk c
-            // is processed (tcgen05.wait::ld waits for every load issued so far).
-            const bool from_tmem = !(MODE == MODE_GEMM && acc_is_empty);
+            // one 32-column load from TMEM per step; the math of a step hides little of the next
+            // load's latency, yet deeper buffering measured slower here (register pressure)
+            const bool from_tmem = true;
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
                 const int col0 = it.nblk * BN + c * 32;  // column within this launch
@@ -672,50 +749,6 @@ __device__ void epilogue_loop(const EngineParams& p, const EngineSmem& s, uint32
                                 }
                             }
                             flag_bits = 0;
-                        }
-                    }
-                } else {  // MODE_GEMM
-                    if (row_ok) {
-                        const int ncol = min(32, p.N - col0);
-                        if (p.out_dtype == 2) {
-                            float* dst = reinterpret_cast<float*>(p.out) + (size_t)row * p.ldo + col0;
-                            const bool vec = (ncol == 32) && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
-                            if (vec && p.accumulate == 2) {
-#pragma unroll
-                                for (int j = 0; j < 8; ++j)
-                                    red_add_v4(dst + 4 * j, x[4 * j], x[4 * j + 1], x[4 * j + 2], x[4 * j + 3]);
-                            } else if (vec) {
-                                float4* d4 = reinterpret_cast<float4*>(dst);
-#pragma unroll
-                                for (int j = 0; j < 8; ++j) {
-                                    float4 v = make_float4(x[4 * j], x[4 * j + 1], x[4 * j + 2], x[4 * j + 3]);
-                                    if (p.accumulate) {
-                                        const float4 o = d4[j];
-                                        v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
-                                    }
-                                    d4[j] = v;
-                                }
-                            } else {
-#pragma unroll
-                                for (int j = 0; j < 32; ++j)
-                                    if (j < ncol) dst[j] = p.accumulate ? dst[j] + x[j] : x[j];
-                            }
-                        } else {
-                            char* dst = reinterpret_cast<char*>(p.out) + ((size_t)row * p.ldo + col0) * 2;
-                            const bool vec = (ncol == 32) && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
-                            if (vec) {
-                                store_g16(dst, x, p.out_dtype == 1);
-                            } else {
-#pragma unroll
-                                for (int j = 0; j < 32; ++j) {
-                                    if (j < ncol) {
-                                        if (p.out_dtype == 1)
-                                            reinterpret_cast<__nv_bfloat16*>(dst)[j] = __float2bfloat16_rn(x[j]);
-                                        else
-                                            reinterpret_cast<__half*>(dst)[j] = __float2half_rn(x[j]);
-                                    }
-                                }
-                            }
                         }
                     }
                 }
