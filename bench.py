@@ -372,7 +372,7 @@ def main() -> None:
             s_main.wait_stream(s_out)
             s_main.wait_stream(s_in)
 
-        e2e_steps = max(4, min(args.steps, 12))
+        e2e_steps = max(4, min(args.steps, 50))
         e2e_run(2)
         barrier()
         ev0.record()

@@ -128,8 +128,11 @@ int cce_b200_indexed_neg_dot(const cce_b200_operands* op, const int64_t* targets
  * row r (0 <= r < n_total) is paired with label targets[r + shift] and is listed when that label
  * lies in the same sequence (r % seq_len < seq_len - shift) and differs from ignore_index.
  * rows_out (int32 or int64 by rows_dtype, room for n_total entries) receives the list and
- * count_out[0] (a device int64) its length; the caller reads the count back (the one host
- * synchronisation of the forward pass) and passes rows_out/count on as `valids`/`n_rows`.
+ * count_out[0] (an int64 the device can write: device memory, or pinned host memory, which kernels
+ * reach through unified addressing and which spares the read-back a copy-engine transfer that
+ * could queue behind a bulk download) its length; the caller waits for the stream, reads the
+ * count (the one host synchronisation of the forward pass) and passes rows_out/count on as
+ * `valids`/`n_rows`.
  * n_total must be a multiple of seq_len.  Two small launches, no atomics: the list is
  * deterministic; its workspace carries no status word (these kernels never wait).  Replaces
  * (cut_cross_entropy/utils.py:28-49), which the reference evaluates with

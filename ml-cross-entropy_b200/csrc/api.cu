@@ -696,7 +696,8 @@ int cce_b200_valid_rows(const int64_t* targets, int64_t n_total, int64_t seq_len
     if (rows_dtype == CCE_IDX_I32 && n_total > 0x7fffffffLL) return CCE_ERR_TOO_LARGE;
     cudaStream_t st = (cudaStream_t)stream;
     if (n_total == 0 || shift >= seq_len) {
-        CCE_CUDA(cudaMemsetAsync(count_out, 0, sizeof(int64_t), st));
+        set_count_kernel<<<1, 1, 0, st>>>(reinterpret_cast<long long*>(count_out), 0);  // count_out may be host-mapped
+        CCE_LAUNCH_CHECK();
         return CCE_OK;
     }
     if (!targets || !rows_out || !workspace) return CCE_ERR_ARG;

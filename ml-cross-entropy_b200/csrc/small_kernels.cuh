@@ -461,6 +461,8 @@ __device__ __forceinline__ int block_scan_256(int v, int* total) {
     return before + incl - v;
 }
 
+__global__ void set_count_kernel(long long* __restrict__ count_out, long long v) { count_out[0] = v; }
+
 // block_counts[b] = valid rows among rows [b * VR_BLOCK, (b + 1) * VR_BLOCK)
 __global__ void __launch_bounds__(VR_THREADS)
 valid_rows_count_kernel(const long long* __restrict__ targets, long long n_total, long long seq_len,

@@ -39,11 +39,14 @@ class PendingValidRows:
     of the list has not been read back.  :meth:`resolve` reads it (the one host synchronisation of
     the forward pass) and returns what ``_build_flat_valids`` returns."""
 
-    def __init__(self, rows: torch.Tensor, count: torch.Tensor, n_total: int, shift: int):
-        self.rows, self.count, self.n_total, self.shift = rows, count, n_total, shift
+    def __init__(self, rows: torch.Tensor, count: torch.Tensor, done: torch.cuda.Event, n_total: int, shift: int):
+        self.rows, self.count, self.done, self.n_total, self.shift = rows, count, done, n_total, shift
 
     def resolve(self) -> torch.Tensor | None:
-        n = int(self.count.item())
+        # The kernel wrote the length straight into pinned host memory: waiting for the event is
+        # all it takes, no device-to-host copy that could queue behind someone's bulk download.
+        self.done.synchronize()
+        n = int(self.count[0])
         if self.shift == 0 and n == self.n_total:
             return None
         return self.rows[:n]
@@ -62,7 +65,7 @@ def launch_flat_valids(targets: torch.Tensor, ignore_index: int, shift: int) -> 
     seq = targets.size(-1) if targets.dim() > 0 else 1
     L = _native.lib()
     rows = torch.empty((n_total,), dtype=torch.int32 if shift == 0 else torch.int64, device=targets.device)
-    count = torch.empty((1,), dtype=torch.int64, device=targets.device)
+    count = torch.empty((1,), dtype=torch.int64, pin_memory=True)  # device-writable through unified addressing
     ws = _native.workspace(L.cce_b200_valid_rows_workspace_bytes(n_total), targets.device)
     with torch.cuda.device(targets.device):
         rc = L.cce_b200_valid_rows(
@@ -71,7 +74,9 @@ def launch_flat_valids(targets: torch.Tensor, ignore_index: int, shift: int) -> 
             _native.stream_ptr(targets.device),
         )  # fmt: skip
     _native.check(rc, "cce_b200_valid_rows")
-    return PendingValidRows(rows, count, n_total, shift)
+    done = torch.cuda.Event()
+    done.record(torch.cuda.current_stream(targets.device))
+    return PendingValidRows(rows, count, done, n_total, shift)
 
 
 def _build_flat_valids(targets: torch.Tensor, ignore_index: int, shift: int) -> torch.Tensor | None:
