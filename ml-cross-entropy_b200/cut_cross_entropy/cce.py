@@ -73,9 +73,8 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
         vp = params.vocab_parallel_options
         vocab_start = vp.start if vp is not None else 0
 
-        if params.pending_valids is not None:  # everything above ran while the list was being built
-            params.valids = params.pending_valids.resolve()
-            params.pending_valids = None
+        pending = params.pending_valids
+        params.pending_valids = None
 
         # The filtered backward can skip recomputing logit tiles that provably hold nothing above the
         # threshold if the forward records each tile's largest logit; worth it only when every
@@ -88,9 +87,17 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
             and (params.filter_c_grad or not c_info.requires_grad)
             and not (bias_info is not None and bias_info.requires_grad)
         )
+        # a pending row list is waited for inside the launcher, after everything that does not need it
         ret = cce_lse_forward_kernel(
-            e=e, c=c, bias=bias, valids=params.valids, softcap=params.softcap, return_tile_max=want_tile_max
+            e=e,
+            c=c,
+            bias=bias,
+            valids=pending if pending is not None else params.valids,
+            softcap=params.softcap,
+            return_tile_max=want_tile_max,
         )
+        if pending is not None:
+            params.valids = pending.resolve()
         lse, tile_max = ret if want_tile_max else (ret, None)
         assert isinstance(lse, torch.Tensor)
         # labels this rank does not own give 0, so the same call serves the vocab-parallel case

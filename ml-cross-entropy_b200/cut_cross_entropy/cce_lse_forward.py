@@ -10,13 +10,14 @@ from __future__ import annotations
 import torch
 
 from . import _native
+from .utils import PendingValidRows
 
 
 def cce_lse_forward_kernel(
     e: torch.Tensor,
     c: torch.Tensor,
     bias: torch.Tensor | None = None,
-    valids: torch.Tensor | None = None,
+    valids: torch.Tensor | PendingValidRows | None = None,
     softcap: float | None = None,
     return_logit_avg: bool = False,
     return_tile_max: bool = False,
@@ -27,6 +28,10 @@ def cce_lse_forward_kernel(
     per-column mean logit only to reorder the vocabulary before filtering
     (``cce.py:171-174``); this backend filters in natural vocabulary order, so the
     second return value is always ``None``.
+
+    ``valids`` may be a :class:`~cut_cross_entropy.utils.PendingValidRows` (a row list the GPU is
+    still writing): buffers are then sized for all rows and the operand description is prepared
+    before the list's length is waited for, so the launch follows the wait at once.
 
     ``return_tile_max`` asks for this backend's own by-product instead: the largest logit (in
     log2 units) of every (32-row group, 256-column tile) block, which lets the filtered
@@ -39,6 +44,9 @@ def cce_lse_forward_kernel(
         bias = bias.contiguous()
     if c.stride(1) != 1:
         c = c.contiguous()
+    pending = valids if isinstance(valids, PendingValidRows) else None
+    if pending is not None:
+        valids = pending.rows  # the whole buffer: an upper bound of the list, for sizing
     if valids is not None:
         assert valids.ndim == 1
         valids = valids.contiguous()
@@ -50,9 +58,20 @@ def cce_lse_forward_kernel(
     if return_tile_max:
         tile_max = torch.empty((L.cce_b200_tile_max_elems(op),), dtype=torch.float32, device=e.device)
     ws = _native.workspace(L.cce_b200_lse_workspace_bytes(op), e.device)
+    stream = _native.stream_ptr(e.device)
+    if pending is not None:  # now wait for the list and shrink everything to its true length
+        rows = pending.resolve()
+        op.n_rows = e.size(0) if rows is None else rows.numel()
+        op.valids = _native._ptr(rows)
+        lse = lse[: op.n_rows]
+        if tile_max is not None:
+            tile_max = tile_max[: L.cce_b200_tile_max_elems(op)]
+        need = L.cce_b200_lse_workspace_bytes(op)  # not monotonic in n_rows (the band split changes)
+        if need > ws.numel():
+            ws = _native.workspace(need, e.device)
     with torch.cuda.device(e.device):
         rc = L.cce_b200_lse_forward(
-            op, lse.data_ptr(), _native._ptr(tile_max), ws.data_ptr(), ws.numel(), _native.stream_ptr(e.device)
+            op, lse.data_ptr(), _native._ptr(tile_max), ws.data_ptr(), ws.numel(), stream
         )
     _native.check(rc, "cce_b200_lse_forward")
     _native.finish(ws, "cce_b200_lse_forward")

@@ -34,6 +34,9 @@ def _handle_eps(filter_eps: float | str | None, dtype: torch.dtype) -> float | N
     raise RuntimeError(f"Unknown eps {filter_eps=}")
 
 
+_UNRESOLVED = object()
+
+
 class PendingValidRows:
     """A list of valid rows that the GPU is still writing: the kernels are enqueued, the length
     of the list has not been read back.  :meth:`resolve` reads it (the one host synchronisation of
@@ -41,15 +44,16 @@ class PendingValidRows:
 
     def __init__(self, rows: torch.Tensor, count: torch.Tensor, done: torch.cuda.Event, n_total: int, shift: int):
         self.rows, self.count, self.done, self.n_total, self.shift = rows, count, done, n_total, shift
+        self._resolved: torch.Tensor | None | object = _UNRESOLVED
 
     def resolve(self) -> torch.Tensor | None:
-        # The kernel wrote the length straight into pinned host memory: waiting for the event is
-        # all it takes, no device-to-host copy that could queue behind someone's bulk download.
-        self.done.synchronize()
-        n = int(self.count[0])
-        if self.shift == 0 and n == self.n_total:
-            return None
-        return self.rows[:n]
+        if self._resolved is _UNRESOLVED:
+            # The kernel wrote the length straight into pinned host memory: waiting for the event
+            # is all it takes, no device-to-host copy that could queue behind a bulk download.
+            self.done.synchronize()
+            n = int(self.count[0])
+            self._resolved = None if (self.shift == 0 and n == self.n_total) else self.rows[:n]
+        return self._resolved
 
 
 def launch_flat_valids(targets: torch.Tensor, ignore_index: int, shift: int) -> PendingValidRows:
