@@ -409,9 +409,10 @@ BwdPlan plan_bwd(const cce_b200_backward_args* a) {
     pl.sparse = wants_sparse(a) && total_tiles > 0 && cap >= 2LL * pl.n_rb && pl.n_rb + pl.n_vt < 12000;
     if (pl.sparse) {
         pl.capacity = int(cap);
-        // a pass that cannot take the next column holds more than cap - n_rb slots, which bounds the
-        // number of passes; a pool that holds every tile needs exactly one
-        pl.max_pass = cap >= total_tiles ? 1 : int(total_tiles / (cap - pl.n_rb + 1)) + 2;
+        // Every pass but the last was closed because the next column (at most n_rb tiles) did not
+        // fit, so it holds at least x = cap - n_rb + 1 slots: P passes give (P - 1) * x < total, i.e.
+        // P <= ceil(total / x).  A pool that holds every tile needs exactly one pass.
+        pl.max_pass = cap >= total_tiles ? 1 : int(cdiv(total_tiles, cap - pl.n_rb + 1));
         pl.off_minlse = off;
         off = align_up(off + (size_t)pl.n_rb * 4 * sizeof(float), 256);
         pl.off_act = off;

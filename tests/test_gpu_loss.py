@@ -361,6 +361,39 @@ def test_recompute_skipping_changes_nothing(softcap, shape):
     assert (dc1.float() - dc2.float()).abs().max() <= 1e-2 * dc2.float().abs().max()
 
 
+@pytest.mark.parametrize("pool_mb", [1, 2, 5])
+def test_block_list_backward_with_every_tile_active_and_a_tiny_pool(pool_mb):
+    """Worst case for the number of passes over the tile pool: a threshold so small that every
+    tile is active, and a pool of 16, 32 or 80 tiles for the 11 x 40 = 440 tiles of the problem (16
+    is below the two columns the block list needs, so that case takes the chunked form; 32 makes
+    the number of passes equal to its bound).  dC
+    sums its row blocks in the same order as the unfiltered backward; dE differs by the order of
+    its fp32 partial sums only."""
+    import os
+
+    from cut_cross_entropy.cce_backward import cce_backward_kernel
+    from cut_cross_entropy.cce_lse_forward import cce_lse_forward_kernel
+    from cut_cross_entropy.utils import TensorInfo
+
+    N, V, D = 1300, 10100, 192
+    g = torch.Generator().manual_seed(11)
+    e = torch.randn(N, D, generator=g).bfloat16().to(DEV)
+    c = (torch.randn(V, D, generator=g) * 0.05).bfloat16().to(DEV)
+    t = torch.randint(0, V, (N,), generator=g).to(DEV)
+    lse, tile_max = cce_lse_forward_kernel(e, c, return_tile_max=True)
+    info = TensorInfo(torch.bfloat16, True)
+    kw = dict(do=torch.ones((), device=DEV), dlse=None, e=e, e_info=info, c=c, c_info=info, bias=None,
+              bias_info=None, lse=lse, valids=None, softcap=None, targets=t, grad_scale=1.0 / N)
+    de0, dc0, _ = cce_backward_kernel(**kw, filter_eps=None)
+    os.environ["CCE_B200_GBUF_MB"] = str(pool_mb)
+    try:
+        de1, dc1, _ = cce_backward_kernel(**kw, filter_eps=1e-30, tile_max=tile_max)
+    finally:
+        del os.environ["CCE_B200_GBUF_MB"]
+    torch.testing.assert_close(dc1, dc0, rtol=0, atol=0)
+    assert (de1.float() - de0.float()).abs().max() <= 1e-2 * de0.float().abs().max()  # one bf16 ulp of the largest
+
+
 @pytest.mark.parametrize("world", [2, 3])
 @pytest.mark.parametrize("impl_filter", [None, 2.0**-12])
 def test_vocabulary_shards_on_one_gpu(world, impl_filter):
