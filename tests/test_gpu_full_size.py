@@ -227,3 +227,54 @@ def test_full_size_properties():
         del os.environ["CCE_B200_GBUF_MB"]
     torch.testing.assert_close(dc_b, dc_a, rtol=0, atol=0)
     _check_grad(de_b, de_a, "dE with a small tile pool")
+
+
+@pytest.mark.parametrize("world", [4, 8])
+def test_full_size_vocabulary_shards_on_one_gpu(world):
+    """The per-rank work of `bench.py --gpus N` at the Gemma-2-2B head shape, shard after shard on
+    one GPU, with the block-list backward each rank runs (per-shard tile maxima, global lse):
+    the shards' log-sum-exps merge to the unsharded one, each shard's dC is the matching slice of
+    the unsharded dC bit for bit (the same tiles, the same order of row blocks), and the fp32 dE
+    partial sums add up to the unsharded dE within its bf16 rounding."""
+    from cut_cross_entropy.cce_backward import cce_backward_kernel
+    from cut_cross_entropy.cce_lse_forward import cce_lse_forward_kernel
+    from cut_cross_entropy.utils import TensorInfo, _build_flat_valids
+    from cut_cross_entropy.vocab_parallel import partition_n_into_range
+
+    cfg = bench.CONFIGS["gemma2-2b-head"]
+    e, c, _, targets = bench.make_inputs(cfg, DEV)
+    t = targets.flatten()
+    valids = _build_flat_valids(targets, IGNORE, 0)
+    B, V = valids.numel(), c.size(0)
+    info = TensorInfo(torch.bfloat16, True)
+    do = torch.ones((), device=DEV)
+    eps = 2.0**-12
+
+    def bwd(cs, lse, tile_max, start):
+        return cce_backward_kernel(do=do, dlse=None, e=e, e_info=info, c=cs, c_info=info, bias=None, bias_info=None,
+                                   lse=lse, valids=valids, softcap=None, filter_eps=eps, targets=t,
+                                   grad_scale=1.0 / B, vocab_start=start, reduce_e_grad=False,
+                                   tile_max=tile_max)  # fmt: skip
+
+    lse_full, tm_full = cce_lse_forward_kernel(e, c, None, valids, return_tile_max=True)
+    de_full, dc_full, _ = bwd(c, lse_full, tm_full, 0)
+
+    parts = []
+    for r in range(world):
+        s0, s1 = partition_n_into_range(V, r, world)
+        cs = c[s0:s1].contiguous()
+        lse_r, tm_r = cce_lse_forward_kernel(e, cs, None, valids, return_tile_max=True)
+        parts.append((s0, s1, cs, lse_r, tm_r))
+    lse = torch.logsumexp(torch.stack([p[3] for p in parts]), 0)
+    torch.testing.assert_close(lse, lse_full, rtol=0, atol=1e-5)
+
+    de_sum = torch.zeros(de_full.shape, dtype=torch.float32, device=DEV)
+    for s0, s1, cs, _, tm_r in parts:
+        de, dc, _ = bwd(cs, lse_full, tm_r, s0)
+        if s0 % 256 == 0:  # the shard's 256-column tiles are tiles of the unsharded problem
+            torch.testing.assert_close(dc, dc_full[s0:s1], rtol=0, atol=0)
+        else:
+            _check_grad(dc, dc_full[s0:s1], f"dC of shard [{s0}, {s1})")
+        de_sum += de.float()
+        del de, dc
+    _check_grad(de_sum, de_full, "sum of the shards' dE")
