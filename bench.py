@@ -161,7 +161,7 @@ def measured_peak_tflops() -> tuple[float, str]:
         return 1400.0, "fallback (sustained figure of an earlier measurement on this pool)"
 
 
-def cpu_baseline(cfg: dict, sample_rows: int = 1024, iters: int = 2) -> dict:
+def cpu_baseline(cfg: dict, sample_rows: int = 1024, iters: int = 8) -> dict:
     """The reference's CPU path (oracle/cpu_reference.py) on a bounded sample: the first
     ``sample_rows`` rows of the workload against the full classifier, all host threads."""
     from oracle import cpu_reference
@@ -191,9 +191,10 @@ def run_reference(args, cfg_name: str, cfg: dict, rank: int) -> None:
     e2 = e.reshape(-1, e.size(-1))[:sample_rows].contiguous()
     t2 = targets.reshape(-1)[:sample_rows].contiguous()
     softcap = cfg["kw"].get("softcap")
-    for _ in range(min(args.warmup, 1)):
+    warmup = min(args.warmup, 5)
+    for _ in range(warmup):
         cpu_reference.torch_compile_path_step(e2, c, t2, bias, softcap)
-    steps = min(args.steps, 3)
+    steps = min(args.steps, 200)  # ~1 s per step at the default workload
     t0 = time.perf_counter()
     for _ in range(steps):
         cpu_reference.torch_compile_path_step(e2, c, t2, bias, softcap)
@@ -201,7 +202,7 @@ def run_reference(args, cfg_name: str, cfg: dict, rank: int) -> None:
     value = sample_rows / sec
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
-        "warmup": min(args.warmup, 1), "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong",
+        "warmup": warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": cfg_name, "rows": cfg["e_shape"][:-1], "D": cfg["e_shape"][-1], "V": cfg["V"]},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
