@@ -126,3 +126,114 @@ def test_partition():
     for n, w in ((10, 3), (262144, 8), (5, 8)):
         for r in range(w):
             assert partition_n_into_range(n, r, w) == O.partition_n_into_range(n, r, w)
+
+
+def _operands(n_total, n_rows, V, D, dtype=1, valids=False):
+    """A description with dummy (never dereferenced) 256-byte aligned addresses: the planning
+    functions of the C ABI are host arithmetic on shapes, strides and alignments."""
+    from cut_cross_entropy import _native
+
+    op = _native.Operands()
+    op.e, op.c = 0x10000, 0x20000
+    op.valids = 0x30000 if valids else None
+    op.n_total, op.n_rows, op.V, op.D = n_total, n_rows, V, D
+    op.lde = op.ldc = D
+    op.dtype, op.bias_dtype, op.valids_dtype = dtype, 2, 0
+    return op
+
+
+def test_workspace_planning_is_host_arithmetic_with_the_documented_sizes():
+    from cut_cross_entropy import _native
+
+    L = _native.lib()
+    # Gemma-2-2B head, dense aligned bf16 operands, no row list: only the status block and the
+    # per-band partial sums -> "about 4 MiB", as the header says of the no-allocation entry point
+    op = _operands(8192, 8192, 256000, 2304)
+    need = L.cce_b200_lse_workspace_bytes(op)
+    assert 3 << 20 < need < 5 << 20
+    assert L.cce_b200_tile_max_elems(op) == (8192 // 128) * 4 * 1000
+    # a row list adds the packed copy of the listed rows; fp32 operands add three-term bf16 splits
+    # of both matrices (3 x 2 bytes per element)
+    with_rows = L.cce_b200_lse_workspace_bytes(_operands(8192, 7783, 256000, 2304, valids=True))
+    assert 0 < with_rows - need < 7783 * 2304 * 2 + (1 << 20)
+    split = L.cce_b200_lse_workspace_bytes(_operands(8192, 8192, 256000, 2304, dtype=2))
+    assert split - need >= (8192 + 256000) * 2304 * 6
+    # an odd hidden size is padded to a multiple of 8 elements in staged copies of both operands
+    odd = L.cce_b200_lse_workspace_bytes(_operands(256, 256, 512, 123))
+    assert odd >= (256 + 512) * 128 * 2
+    # nonsense is refused with size 0
+    assert L.cce_b200_lse_workspace_bytes(_operands(8, 9, 512, 64)) == 0  # more listed rows than rows
+    assert L.cce_b200_lse_workspace_bytes(_operands(8, 8, 0, 64)) == 0
+    assert L.cce_b200_lse_workspace_bytes(_operands(8, 8, 512, 64, dtype=7)) == 0
+    # the row-list builder: one int per block of 2048 labels, rounded up to 256 bytes
+    assert L.cce_b200_valid_rows_workspace_bytes(1) == 256
+    assert L.cce_b200_valid_rows_workspace_bytes(2048 * 64) == 256
+    assert L.cce_b200_valid_rows_workspace_bytes(2048 * 64 + 1) == 512
+    assert L.cce_b200_valid_rows_workspace_bytes(-1) == 0
+
+
+def test_backward_planning_respects_the_logit_gradient_buffer_cap(monkeypatch):
+    """The backward never holds more than the cap (512 MiB unless CCE_B200_GBUF_MB says otherwise)
+    of recomputed logit gradients, whatever the problem size; everything else in its workspace is
+    the fp32 dE scratch, staged operands and index arrays."""
+    from cut_cross_entropy import _native
+
+    L = _native.lib()
+
+    def need(n, V, D, tile_max, mb=None, **kw):
+        if mb is None:
+            monkeypatch.delenv("CCE_B200_GBUF_MB", raising=False)
+        else:
+            monkeypatch.setenv("CCE_B200_GBUF_MB", str(mb))
+        a = _native.BackwardArgs()
+        a.op = _operands(n, n, V, D)
+        a.lse, a.targets, a.d_out, a.d_e, a.d_c = 0x40000, 0x50000, 0x60000, 0x70000, 0x80000
+        a.d_out_numel, a.grad_scale = 1, 1.0
+        a.has_filter, a.filter_eps, a.filter_e, a.filter_c = 1, 2.0**-12, 1, 1
+        a.tile_max = 0x90000 if tile_max else None
+        for k, v in kw.items():
+            setattr(a, k, v)
+        return L.cce_b200_backward_workspace_bytes(a)
+
+    de32 = 8192 * 2304 * 4
+    for tile_max in (False, True):  # chunked form / block-list form
+        total = need(8192, 256000, 2304, tile_max)
+        assert (512 << 20) * 0.5 < total - de32 < (512 << 20) + (16 << 20), (tile_max, total)
+    # a tenth of the cap: a tenth of the buffer
+    small = need(8192, 256000, 2304, True, mb=52)
+    assert small - de32 < (52 << 20) + (16 << 20)
+    # a problem whose every tile fits the pool asks for exactly its tiles, not for the cap
+    tiny = need(256, 1024, 128, True)
+    assert tiny < 2 << 20
+    # without a gradient for e there is no fp32 dE scratch
+    assert need(8192, 256000, 2304, True) - need(8192, 256000, 2304, True, d_e=None) >= de32
+    # refused descriptions
+    assert L.cce_b200_backward_workspace_bytes(None) == 0
+
+
+def test_entry_points_reject_bad_arguments_before_touching_the_gpu():
+    from cut_cross_entropy import _native
+
+    L = _native.lib()
+    op = _operands(128, 128, 512, 64)
+    # missing outputs, workspaces and label arrays
+    assert L.cce_b200_lse_forward(op, None, None, None, 0, None) == -1
+    assert L.cce_b200_lse_forward(op, 0x1000, None, 0x1001, 1 << 30, None) == -2  # workspace not 256-byte aligned
+    assert L.cce_b200_lse_forward(op, 0x1000, None, 0x1000, 16, None) == -3  # workspace too small
+    assert L.cce_b200_indexed_neg_dot(op, None, 0, 0, 0x1000, None) == -1
+    assert L.cce_b200_indexed_neg_dot(op, 0x1000, -1, 0, 0x1000, None) == -1  # negative shift
+    # the fixed scratch of the no-allocation entry point is 8 MiB: a packed copy of 65536 x 4096
+    # rows cannot fit, and is refused before anything is looked up on a device
+    big = _operands(65536, 65536, 262144, 4096, valids=True)
+    assert L.cce_b200_lse_forward_static(big, 0x1000, None) == -7
+    # the row-list builder
+    args = (0x1000, 64, 16, 0, -100, 0x2000, _native.IDX_I32, 0x3000, 0x4000)
+    assert L.cce_b200_valid_rows(*args[:7], None, args[8], 256, None) == -1  # nowhere to put the count
+    assert L.cce_b200_valid_rows(0x1000, 64, 24, 0, -100, 0x2000, 0, 0x3000, 0x4000, 256, None) == -1  # 64 % 24
+    assert L.cce_b200_valid_rows(0x1000, 64, 16, -1, -100, 0x2000, 0, 0x3000, 0x4000, 256, None) == -1
+    assert L.cce_b200_valid_rows(0x1000, 64, 16, 0, -100, 0x2000, 9, 0x3000, 0x4000, 256, None) == -1  # index type
+    assert L.cce_b200_valid_rows(0x1000, 64, 16, 0, -100, 0x2000, 0, 0x3000, 0x4000, 0, None) == -3  # workspace
+    assert L.cce_b200_valid_rows(0x1000, 1 << 31, 1, 0, -100, 0x2000, 0, 0x3000, 0x4000, 1 << 30, None) == -7  # int32 rows
+    for code in range(0, -9, -1):
+        assert L.cce_b200_strerror(code) != b"unknown error"
+    assert L.cce_b200_strerror(-99) == b"unknown error"
