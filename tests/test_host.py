@@ -237,3 +237,26 @@ def test_entry_points_reject_bad_arguments_before_touching_the_gpu():
     for code in range(0, -9, -1):
         assert L.cce_b200_strerror(code) != b"unknown error"
     assert L.cce_b200_strerror(-99) == b"unknown error"
+
+
+def test_pending_row_list_resolution_rules():
+    """What `resolve()` hands on once the length is known (the reference's conventions,
+    utils.py:28-49): `None` without a shift when every row is listed, else the first `count`
+    entries of the buffer; the wait happens once."""
+    from cut_cross_entropy.utils import PendingValidRows
+
+    class Done:
+        waits = 0
+
+        def synchronize(self):
+            Done.waits += 1
+
+    rows = torch.arange(10, dtype=torch.int32)
+    p = PendingValidRows(rows, torch.tensor([10]), Done(), n_total=10, shift=0)
+    assert p.resolve() is None and p.resolve() is None and Done.waits == 1
+    p = PendingValidRows(rows, torch.tensor([7]), Done(), n_total=10, shift=0)
+    assert torch.equal(p.resolve(), rows[:7]) and p.resolve().data_ptr() == rows.data_ptr()
+    p = PendingValidRows(rows.long(), torch.tensor([10]), Done(), n_total=10, shift=1)
+    assert p.resolve().numel() == 10  # with a shift the list is always returned
+    p = PendingValidRows(rows, torch.tensor([0]), Done(), n_total=10, shift=0)
+    assert p.resolve().numel() == 0
