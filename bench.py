@@ -194,7 +194,7 @@ def run_reference(args, cfg_name: str, cfg: dict, rank: int) -> None:
     warmup = min(args.warmup, 5)
     for _ in range(warmup):
         cpu_reference.torch_compile_path_step(e2, c, t2, bias, softcap)
-    steps = min(args.steps, 200)  # ~1 s per step at the default workload
+    steps = min(args.steps, 100)  # ~1 s per step at the default workload: the arm ends within two minutes
     t0 = time.perf_counter()
     for _ in range(steps):
         cpu_reference.torch_compile_path_step(e2, c, t2, bias, softcap)
