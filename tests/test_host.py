@@ -260,3 +260,26 @@ def test_pending_row_list_resolution_rules():
     assert p.resolve().numel() == 10  # with a shift the list is always returned
     p = PendingValidRows(rows, torch.tensor([0]), Done(), n_total=10, shift=0)
     assert p.resolve().numel() == 0
+
+
+def test_reference_arm_of_the_benchmark_prints_the_contract_line():
+    """`bench.py --impl reference` needs no GPU: it times the CPU port on a bounded sample and
+    prints one JSON line with the metric, the config and the keys of the GPU arm's line."""
+    import json
+    import subprocess
+    import sys
+
+    out = subprocess.run(
+        [sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--config", "gemma2-2b-head-small",
+         "--steps", "3", "--warmup", "3"],
+        check=True, capture_output=True, text=True, timeout=600, cwd=ROOT,
+    )  # fmt: skip
+    line = json.loads(out.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and line["metric"] == "linear-CE fwd+bwd tokens/s"
+    assert line["unit"] == "tokens/s" and line["higher_is_better"] is True and line["n_gpus"] == 1
+    assert line["steps"] == 3 and line["warmup"] == 3 and line["ms_per_step"] > 0 and line["value"] > 0
+    assert line["config"]["workload"] == "gemma2-2b-head-small" and line["vs_baseline"] is None
+    cb = line["cpu_baseline"]
+    assert cb["kind"] == "port" and cb["cores"] >= 1 and cb["value"] == line["value"] and "1024 rows" in cb["sample"]
+    assert line["e2e"] == {"value": line["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+    assert line["gpu_launches"] == 0
