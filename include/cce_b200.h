@@ -124,6 +124,25 @@ int cce_b200_indexed_neg_dot(const cce_b200_operands* op, const int64_t* targets
                              int64_t shift, int64_t vocab_start, float* out /* [n_rows] */,
                              void* stream);
 
+/* Tail of the forward pass, one launch: merge the per-rank statistics, form the negative
+ * log-likelihood of every row, and reduce or scatter it.
+ *   stats [world][2][n_rows] fp32: for each vocabulary shard (rank) the log-sum-exp of every row over
+ *   that shard (what cce_b200_lse_forward wrote) and minus the correct-token logit (what
+ *   cce_b200_indexed_neg_dot wrote; 0 on ranks that do not own the label).  world = 1 without
+ *   vocab parallelism; with it, the block is what an all-gather of the ranks' [2][n_rows] blocks gives.
+ *   lse_i = logsumexp_r stats[r][0][i];  nll_i = lse_i + sum_r stats[r][1][i].
+ *   reduction 0 (mean) / 1 (sum): loss_out[0] = mean / sum over rows of nll, summed in a fixed order;
+ *   reduction 2 (none): loss_out [n_total] receives nll_i at position rows[i] + shift (i when rows is
+ *   NULL) and 0 elsewhere.  lse_rows (optional, [n_rows]) receives lse_i (the vector the backward
+ *   takes); lse_scatter (optional, [n_total]) receives lse_i at the same positions as the loss, 0 elsewhere.
+ *   status_workspace (optional): the workspace of the cce_b200_lse_forward call that produced the
+ *   statistics; if its status word is non-zero (a kernel abandoned a wait) every output is NaN.
+ * Replaces, in cut_cross_entropy/cce.py:139-160 and utils.py:52-61, the element-wise add, the
+ * mean/sum and the index-put of handle_reduction_none, and vocab_parallel/utils.py:47-65's merges. */
+int cce_b200_loss_tail(const float* stats, int32_t world, int64_t n_rows, const void* rows, int32_t rows_dtype,
+                       int64_t shift, int64_t n_total, int32_t reduction, float* lse_rows, float* loss_out,
+                       float* lse_scatter, const void* status_workspace, void* stream);
+
 /* The rows of the flattened embedding matrix that enter the loss, in ascending order:
  * row r (0 <= r < n_total) is paired with label targets[r + shift] and is listed when that label
  * lies in the same sequence (r % seq_len < seq_len - shift) and differs from ignore_index.
@@ -184,8 +203,19 @@ int cce_b200_gemm(const void* A, const void* B, void* out, int64_t M, int64_t N,
                   int32_t a_mn, int32_t b_mn, int32_t accumulate, const uint8_t* kflags,
                   int32_t* status, void* stream);
 
-/* Synchronises `stream` and returns CCE_OK or CCE_ERR_KERNEL_WAIT; the raw word goes to *word. */
+/* Synchronises `stream` and returns CCE_OK or CCE_ERR_KERNEL_WAIT; the raw word goes to *word.
+ * Without this read an abandoned wait still shows: the log-sum-exp (hence the loss) and dE of that
+ * call come back as NaN. */
 int cce_b200_read_status(const void* workspace, void* stream, int32_t* word /* host, may be NULL */);
+/* The same for the fixed scratch of cce_b200_lse_forward_static on the current device. */
+int cce_b200_lse_forward_static_status(void* stream, int32_t* word /* host, may be NULL */);
+
+/* Self-test of the bounded wait every pipeline kernel relies on: one warp waits on a barrier at
+ * which nobody arrives, gives up after `limit_cycles` SM cycles (1 .. 2e9), writes its code into
+ * status[0] (device memory, 4 bytes) and the kernel returns normally.  Afterwards
+ * cce_b200_read_status(status, ...) answers CCE_ERR_KERNEL_WAIT.  Touches no TMA, tensor memory or
+ * tensor core; the context stays usable. */
+int cce_b200_selftest_wait(int64_t limit_cycles, int32_t* status, void* stream);
 
 /* Per-kernel timing of the tensor-core launches, for benchmarks.  While enabled, every launch
  * of the pipeline kernel is bracketed by a CUDA event pair on its stream.  cce_b200_profile_read
@@ -204,6 +234,16 @@ int cce_b200_profile_enable(int on);
  * CCE_B200_LIB); the default build answers CCE_ERR_UNSUPPORTED to a non-NULL array. */
 int cce_b200_profile_wait_counters(void* device_counters /* uint64[24] or NULL */);
 int cce_b200_profile_read(double* ms /* host [3] */, int64_t* launches /* host [3] */);
+/* SM clock the pipeline kernels really ran at.  Give a device array of 12 uint64 (3 kernel modes x
+ * 4); until it is reset to NULL, block 0 of every launch writes into the 4 words of its mode:
+ * [0] clock64 and [1] globaltimer (ns) at its start, [2], [3] the same at its end.  (cycles / ns)
+ * of the last launch of a mode is the SM clock in GHz during that launch, which a 100 ms
+ * nvidia-smi sample cannot resolve.  The array belongs to the caller. */
+int cce_b200_profile_clock_words(void* device_words /* uint64[12] or NULL */);
+/* How much of the logit-gradient matrix the block-list backward recomputes.  Give a device array
+ * of 3 int32; until it is reset to NULL every block-list backward writes {tiles (128 rows x 256
+ * columns) it recomputes, tiles in all, passes over the tile pool it needs} into it. */
+int cce_b200_profile_tile_counts(void* device_counts /* int32[3] or NULL */);
 
 /* Counters since library load (host side): kernels launched by this library. */
 int64_t cce_b200_launch_count(void);

@@ -51,6 +51,8 @@ std::mutex g_prof_mu;
 bool g_prof_on = false;
 std::vector<ProfRecord> g_prof;
 unsigned long long* g_wait_counters = nullptr;  // device memory of the caller, [3 modes][8]; null = off
+unsigned long long* g_clk_words = nullptr;      // device memory of the caller, [3 modes][4]; null = off
+int* g_tile_counts = nullptr;                   // device memory of the caller, 3 ints; null = off
 
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 inline long long cdiv(long long a, long long b) { return (a + b - 1) / b; }
@@ -139,6 +141,54 @@ int make_tmap(CUtensorMap* m, const void* base, int dtype, long long inner, long
         return CCE_ERR_CUDA;
     }
     return CCE_OK;
+}
+
+// 3-D tensor map over the same kind of matrix for an operand that is read MN-major (contiguous along
+// M/N): dimensions {64 contiguous elements, `rows` K rows of `pitch` elements, ceil(cols/64) groups
+// 128 bytes apart}, box {64, 64, box_groups}.  One load then fills `box_groups` swizzle atoms.
+// The last group is read in full, so `cols` rounded up to 64 must lie inside every row's memory.
+int make_tmap_mn3(CUtensorMap* m, const void* base, int dtype, long long cols, long long rows, long long pitch,
+                  int box_groups) {
+    EncodeTiledFn enc = get_encode();
+    if (!enc) {
+        g_last_cuda = -1;
+        return CCE_ERR_CUDA;
+    }
+    if ((reinterpret_cast<uintptr_t>(base) & 15) || (pitch * 2) % 16) return CCE_ERR_ALIGN;
+    cuuint64_t dims[3] = {64, (cuuint64_t)rows, (cuuint64_t)cdiv(cols, 64)};
+    cuuint64_t strides[2] = {(cuuint64_t)pitch * 2, 128};
+    cuuint32_t box[3] = {64, (cuuint32_t)BK, (cuuint32_t)box_groups};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(m, dtype == CCE_DT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                     3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        g_last_cuda = int(r);
+        return CCE_ERR_CUDA;
+    }
+    return CCE_OK;
+}
+
+// Map of an MN-major operand: the 3-D form when asked for (and the encoder takes it), else 2-D
+// boxes of 64 x 64.  *is3 tells the kernel which one it got.
+int make_tmap_mn(CUtensorMap* m, const void* base, int dtype, long long cols, long long rows, long long pitch,
+                 int box_groups, bool want3, int* is3) {
+    *is3 = 0;
+    if (want3 && make_tmap_mn3(m, base, dtype, cols, rows, pitch, box_groups) == CCE_OK) {
+        *is3 = 1;
+        return CCE_OK;
+    }
+    return make_tmap(m, base, dtype, cols, rows, pitch, 64, BK);
+}
+
+// CCE_B200_TMA3=0 keeps every MN-major operand on 2-D boxes (for comparisons); read once.
+bool tma3_enabled() {
+    static const bool on = [] {
+        const char* env = getenv("CCE_B200_TMA3");
+        return !(env && env[0] == '0');
+    }();
+    return on;
 }
 
 int check_operands(const cce_b200_operands* op) {
@@ -301,6 +351,7 @@ int launch_engine(const CUtensorMap& a, const CUtensorMap& b, const EngineParams
         std::lock_guard<std::mutex> lock(g_prof_mu);
         prof = g_prof_on;
         if (g_wait_counters) pp.wait_cycles = g_wait_counters + 8 * MODE;
+        if (g_clk_words) pp.clk_words = g_clk_words + 4 * MODE;
     }
     if (prof) {
         CCE_CUDA(cudaEventCreate(&rec.start));
@@ -364,6 +415,7 @@ long long pick_chunk(long long n_rows, long long V, long long D) {
 }
 
 constexpr size_t kSlotBytes = (size_t)BM * BN * 2;  // one 128x256 16-bit tile of the pool
+constexpr int kColsumRows = 512;                    // rows per block of the bias-gradient column sums
 
 // Two shapes of the backward.
 //  dense : the vocabulary is cut into chunks of Vc columns; G[B][Vc] is recomputed in full for a
@@ -379,6 +431,7 @@ struct BwdPlan {
     int n_chunk;
     int ld_flag_e, ld_flag_c;
     size_t off_flag_e, off_flag_c, flag_bytes;  // flag_e and flag_c are adjacent: one memset clears both
+    size_t off_colsum;                          // [ceil(B / kColsumRows)][Vc] fp32 partial column sums (bias gradient)
     // sparse
     int n_rb, n_vt, capacity, max_pass;
     size_t off_minlse, off_act, off_col_ptr, off_row_ptr, off_slot_tile, off_slot_of, off_row_slots, off_pass,
@@ -453,6 +506,8 @@ BwdPlan plan_bwd(const cce_b200_backward_args* a) {
         pl.off_flag_c = off;
         off = align_up(off + (size_t)(pl.Vc / 128) * pl.ld_flag_c, 256);
         pl.flag_bytes = off - pl.off_flag_e;
+        pl.off_colsum = off;
+        if (a->d_bias) off = align_up(off + (size_t)cdiv(op->n_rows, kColsumRows) * pl.Vc * sizeof(float), 256);
     }
     pl.total = off;
     return pl;
@@ -527,6 +582,18 @@ int cce_b200_profile_wait_counters(void* device_counters) {
     if (device_counters && !kTrace) return CCE_ERR_UNSUPPORTED;  // this build has no tracing code
     std::lock_guard<std::mutex> lock(g_prof_mu);
     g_wait_counters = reinterpret_cast<unsigned long long*>(device_counters);
+    return CCE_OK;
+}
+
+int cce_b200_profile_clock_words(void* device_words) {
+    std::lock_guard<std::mutex> lock(g_prof_mu);
+    g_clk_words = reinterpret_cast<unsigned long long*>(device_words);
+    return CCE_OK;
+}
+
+int cce_b200_profile_tile_counts(void* device_counts) {
+    std::lock_guard<std::mutex> lock(g_prof_mu);
+    g_tile_counts = reinterpret_cast<int*>(device_counts);
     return CCE_OK;
 }
 
@@ -638,7 +705,8 @@ int cce_b200_lse_forward(const cce_b200_operands* op, float* lse, float* tile_ma
         if (rc != CCE_OK) return rc;
     }
 
-    lse_combine_kernel<<<(unsigned)cdiv(op->n_rows, 256), 256, 0, st>>>(p.partial, pl.n_band, op->n_rows, lse);
+    lse_combine_kernel<<<(unsigned)cdiv(op->n_rows, 256), 256, 0, st>>>(p.partial, pl.n_band, op->n_rows, lse,
+                                                                        reinterpret_cast<const int*>(ws));
     CCE_LAUNCH_CHECK();
     return CCE_OK;
 }
@@ -680,6 +748,28 @@ int cce_b200_indexed_neg_dot(const cce_b200_operands* op, const int64_t* targets
             reinterpret_cast<const long long*>(targets), shift, vocab_start, op->V, op->D, op->n_rows,
             op->has_softcap, op->softcap, out);
     }
+    CCE_LAUNCH_CHECK();
+    return CCE_OK;
+}
+
+int cce_b200_loss_tail(const float* stats, int32_t world, int64_t n_rows, const void* rows, int32_t rows_dtype,
+                       int64_t shift, int64_t n_total, int32_t reduction, float* lse_rows, float* loss_out,
+                       float* lse_scatter, const void* status_workspace, void* stream) {
+    if (world < 1 || n_rows < 0 || n_total < n_rows || shift < 0 || reduction < 0 || reduction > 2 || !loss_out)
+        return CCE_ERR_ARG;
+    if (n_rows > 0 && !stats) return CCE_ERR_ARG;
+    if (rows && rows_dtype != CCE_IDX_I32 && rows_dtype != CCE_IDX_I64) return CCE_ERR_ARG;
+    if (!rows && n_rows != n_total && n_rows != 0) return CCE_ERR_ARG;
+    cudaStream_t st = (cudaStream_t)stream;
+    const bool scattered = rows != nullptr || n_rows != n_total;  // some positions receive no row: clear them first
+    if (scattered && n_total > 0) {
+        if (reduction == 2) CCE_CUDA(cudaMemsetAsync(loss_out, 0, (size_t)n_total * sizeof(float), st));
+        if (lse_scatter) CCE_CUDA(cudaMemsetAsync(lse_scatter, 0, (size_t)n_total * sizeof(float), st));
+    }
+    if (n_rows == 0 && reduction == 2) return CCE_OK;
+    loss_tail_kernel<<<1, TAIL_THREADS, 0, st>>>(stats, world, n_rows, rows, rows_dtype == CCE_IDX_I64, shift, reduction,
+                                                 lse_rows, loss_out, lse_scatter,
+                                                 reinterpret_cast<const int*>(status_workspace));
     CCE_LAUNCH_CHECK();
     return CCE_OK;
 }
@@ -748,8 +838,8 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
     CCE_CUDA(cudaMemsetAsync(ws, 0, kStatusBytes, st));
     const size_t de_esz = (a->d_e_f32 || split) ? 4 : esz;
     if (a->d_e && (op->valids || B == 0)) CCE_CUDA(cudaMemsetAsync(a->d_e, 0, (size_t)op->n_total * D * de_esz, st));
-    if (a->d_bias) CCE_CUDA(cudaMemsetAsync(a->d_bias, 0, (size_t)V * 4, st));
     if (B == 0) {
+        if (a->d_bias) CCE_CUDA(cudaMemsetAsync(a->d_bias, 0, (size_t)V * 4, st));
         if (a->d_c) CCE_CUDA(cudaMemsetAsync(a->d_c, 0, (size_t)V * D * esz, st));
         return CCE_OK;
     }
@@ -769,15 +859,19 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
     if (rc != CCE_OK) return rc;
     rc = make_tmap(&tmC_k, sg.c, cdt, sg.Dk, V, sg.ldc, BK, BN);
     if (rc != CCE_OK) return rc;
-    rc = make_tmap(&tmE_mn, sg.e, cdt, sg.Dmn, B, sg.lde, 64, BK);
+    // MN-major views (for G^T E and G C): one 3-D load per stage when the rows are whole 64-element groups
+    const bool mn3 = tma3_enabled() && sg.Dmn % 64 == 0 && (!split || sg.blk % 64 == 0);
+    int e_is3 = 0, c_is3 = 0;
+    rc = make_tmap_mn(&tmE_mn, sg.e, cdt, sg.Dmn, B, sg.lde, BN / 64, mn3, &e_is3);
     if (rc != CCE_OK) return rc;
-    rc = make_tmap(&tmC_mn, sg.c, cdt, sg.Dmn, V, sg.ldc, 64, BK);
+    rc = make_tmap_mn(&tmC_mn, sg.c, cdt, sg.Dmn, V, sg.ldc, BN / 64, mn3, &c_is3);
     if (rc != CCE_OK) return rc;
 
     // The two products.  With split fp32 operands the staged rows hold three column blocks
     // ([hi|hi|lo] for e, [hi|lo|hi] for c): dC = G^T e_hi + G^T e_lo and dE = G c_hi + G c_lo, i.e. the
     // same launch run twice on different column blocks of the B operand, the second adding in fp32.
     auto run_dc = [&](EngineParams p, const CUtensorMap& tmA) -> int {
+        p.b_tma3 = e_is3;
         int r = launch_engine<MODE_GEMM>(tmA, tmE_mn, p, dev->sms, st);
         if (r != CCE_OK || !split) return r;
         p.b_mn_off = int(2 * sg.blk);
@@ -785,6 +879,7 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
         return launch_engine<MODE_GEMM>(tmA, tmE_mn, p, dev->sms, st);
     };
     auto run_de = [&](EngineParams p, const CUtensorMap& tmA) -> int {
+        p.b_tma3 = c_is3;
         int r = launch_engine<MODE_GEMM>(tmA, tmC_mn, p, dev->sms, st);
         if (r != CCE_OK || !split) return r;
         p.b_mn_off = int(sg.blk);
@@ -838,14 +933,20 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
             op->valids, op->valids_dtype == CCE_IDX_I64, a->shift, a->vocab_start, V, B, act);
         CCE_LAUNCH_CHECK();
         const size_t sm_bytes = (size_t)(pl.n_rb + pl.n_vt + 2) * sizeof(int);
+        int* tile_counts = nullptr;
+        {
+            std::lock_guard<std::mutex> lock(g_prof_mu);
+            tile_counts = g_tile_counts;
+        }
         tile_index_kernel<<<1, 1024, sm_bytes, st>>>(act, pl.n_rb, pl.n_vt, pl.capacity, pl.max_pass, col_ptr, slot_tile,
-                                                    slot_of, row_ptr, row_slots, pass_info);
+                                                    slot_of, row_ptr, row_slots, pass_info, tile_counts);
         CCE_LAUNCH_CHECK();
 
         CUtensorMap tmP_k, tmP_mn;  // the pool seen as a [capacity*128][256] matrix
         rc = make_tmap(&tmP_k, g_buf, cdt, BN, (long long)pl.capacity * BM, BN, BK, BM);
         if (rc != CCE_OK) return rc;
-        rc = make_tmap(&tmP_mn, g_buf, cdt, BN, (long long)pl.capacity * BM, BN, 64, BK);
+        int p_is3 = 0;
+        rc = make_tmap_mn(&tmP_mn, g_buf, cdt, BN, (long long)pl.capacity * BM, BN, BM / 64, tma3_enabled(), &p_is3);
         if (rc != CCE_OK) return rc;
 
         for (int ps = 0; ps < pl.max_pass; ++ps) {
@@ -880,6 +981,7 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
                 p.n_vt = pl.n_vt;
                 p.klist = dc_list;
                 p.kcount = dc_cnt;
+                p.a_tma3 = p_is3;
                 rc = run_dc(p, tmP_mn);
                 if (rc != CCE_OK) return rc;
             }
@@ -928,10 +1030,12 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
             // phase 2: dC[v0 : v0 + Vw, :] = G^T E   (M = Vw, N = D, K = B; both operands MN-major)
             if (a->d_c) {
                 CUtensorMap tmG_mn;
-                rc = make_tmap(&tmG_mn, g_buf, cdt, Vw, B, pl.Vc, 64, BK);
+                int g_is3 = 0;  // the chunk's pitch (a multiple of 256) covers the last group of 64 columns
+                rc = make_tmap_mn(&tmG_mn, g_buf, cdt, Vw, B, pl.Vc, BM / 64, tma3_enabled(), &g_is3);
                 if (rc != CCE_OK) return rc;
                 EngineParams p;
                 base_params(&p, Vw, D, B, cdt, 1, 1, status);
+                p.a_tma3 = g_is3;
                 p.out = reinterpret_cast<char*>(a->d_c) + (size_t)v0 * D * esz;
                 p.ldo = D;
                 p.out_dtype = split ? CCE_DT_F32 : op->dtype;
@@ -964,17 +1068,20 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
                 if (rc != CCE_OK) return rc;
             }
 
-            // bias gradient: column sums of G
+            // bias gradient: column sums of G, partial sums per row block then a fixed-order finish
             if (a->d_bias) {
-                const int rows_per_block = 512;
-                dim3 grid((unsigned)cdiv(Vw, 256), (unsigned)cdiv(B, rows_per_block));
+                const int n_rowblk = int(cdiv(B, kColsumRows));
+                float* partial = reinterpret_cast<float*>(ws + pl.off_colsum);
+                dim3 grid((unsigned)cdiv(Vw, 256), (unsigned)n_rowblk);
                 if (cdt == CCE_DT_BF16)
-                    colsum_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(g_buf),
-                                                                       pl.Vc, B, int(Vw), rows_per_block,
-                                                                       a->d_bias + v0);
+                    colsum_partial_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(
+                        reinterpret_cast<const __nv_bfloat16*>(g_buf), pl.Vc, B, int(Vw), kColsumRows, partial, pl.Vc);
                 else
-                    colsum_kernel<__half><<<grid, 128, 0, st>>>(reinterpret_cast<const __half*>(g_buf), pl.Vc, B,
-                                                                int(Vw), rows_per_block, a->d_bias + v0);
+                    colsum_partial_kernel<__half><<<grid, 128, 0, st>>>(reinterpret_cast<const __half*>(g_buf), pl.Vc,
+                                                                        B, int(Vw), kColsumRows, partial, pl.Vc);
+                CCE_LAUNCH_CHECK();
+                colsum_finish_kernel<<<(unsigned)cdiv(Vw, 256), 256, 0, st>>>(partial, pl.Vc, n_rowblk, int(Vw),
+                                                                              a->d_bias + v0);
                 CCE_LAUNCH_CHECK();
             }
         }
@@ -983,16 +1090,33 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
     if (a->d_e) {
         if (a->d_e_f32 || split)
             scatter_cast_kernel<float><<<(unsigned)B, 128, 0, st>>>(
-                de32, D, op->valids, op->valids_dtype == CCE_IDX_I64, reinterpret_cast<float*>(a->d_e), D, D, B);
+                de32, D, op->valids, op->valids_dtype == CCE_IDX_I64, reinterpret_cast<float*>(a->d_e), D, D, B, status);
         else if (cdt == CCE_DT_BF16)
             scatter_cast_kernel<__nv_bfloat16><<<(unsigned)B, 128, 0, st>>>(
-                de32, D, op->valids, op->valids_dtype == CCE_IDX_I64, reinterpret_cast<__nv_bfloat16*>(a->d_e), D, D, B);
+                de32, D, op->valids, op->valids_dtype == CCE_IDX_I64, reinterpret_cast<__nv_bfloat16*>(a->d_e), D, D, B,
+                status);
         else
             scatter_cast_kernel<__half><<<(unsigned)B, 128, 0, st>>>(
-                de32, D, op->valids, op->valids_dtype == CCE_IDX_I64, reinterpret_cast<__half*>(a->d_e), D, D, B);
+                de32, D, op->valids, op->valids_dtype == CCE_IDX_I64, reinterpret_cast<__half*>(a->d_e), D, D, B, status);
         CCE_LAUNCH_CHECK();
     }
     return CCE_OK;
+}
+
+int cce_b200_selftest_wait(int64_t limit_cycles, int32_t* status, void* stream) {
+    if (!status || limit_cycles <= 0 || limit_cycles > 2000000000LL) return CCE_ERR_ARG;
+    cudaStream_t st = (cudaStream_t)stream;
+    CCE_CUDA(cudaMemsetAsync(status, 0, 4, st));
+    selftest_wait_kernel<<<1, 32, 0, st>>>((long long)limit_cycles, status);
+    CCE_LAUNCH_CHECK();
+    return CCE_OK;
+}
+
+int cce_b200_lse_forward_static_status(void* stream, int32_t* word) {
+    void* scratch = nullptr;
+    int rc = static_scratch_ptr(&scratch);
+    if (rc != CCE_OK) return rc;
+    return cce_b200_read_status(scratch, stream, word);
 }
 
 int cce_b200_gemm(const void* A, const void* Bm, void* out, int64_t M, int64_t N, int64_t K, int64_t lda,
@@ -1007,15 +1131,16 @@ int cce_b200_gemm(const void* A, const void* Bm, void* out, int64_t M, int64_t N
     if (rc != CCE_OK) return rc;
     cudaStream_t st = (cudaStream_t)stream;
     CUtensorMap tmA, tmB;
+    int a_is3 = 0, b_is3 = 0;
     if (!a_mn)
         rc = make_tmap(&tmA, A, dtype, K, M, lda, BK, BM);
     else
-        rc = make_tmap(&tmA, A, dtype, M, K, lda, 64, BK);
+        rc = make_tmap_mn(&tmA, A, dtype, M, K, lda, BM / 64, tma3_enabled() && M % 64 == 0, &a_is3);
     if (rc != CCE_OK) return rc;
     if (!b_mn)
         rc = make_tmap(&tmB, Bm, dtype, K, N, ldb, BK, BN);
     else
-        rc = make_tmap(&tmB, Bm, dtype, N, K, ldb, 64, BK);
+        rc = make_tmap_mn(&tmB, Bm, dtype, N, K, ldb, BN / 64, tma3_enabled() && N % 64 == 0, &b_is3);
     if (rc != CCE_OK) return rc;
     if (status) CCE_CUDA(cudaMemsetAsync(status, 0, 4, st));
     EngineParams p;
@@ -1026,6 +1151,8 @@ int cce_b200_gemm(const void* A, const void* Bm, void* out, int64_t M, int64_t N
     p.accumulate = accumulate;
     p.kflags = kflags;
     p.ld_kflags = int(cdiv(K, BK));
+    p.a_tma3 = a_is3;
+    p.b_tma3 = b_is3;
     return launch_engine<MODE_GEMM>(tmA, tmB, p, dev->sms, st);
 }
 

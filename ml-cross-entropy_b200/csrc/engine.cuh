@@ -48,12 +48,18 @@ struct EngineParams {
     // coordinate offsets added to the TMA coordinates of each operand
     int a_mn_off, a_k_off, b_mn_off, b_k_off;
     int a_mn_major, b_mn_major;  // 0: K contiguous in memory, 1: M/N contiguous in memory
+    // MN-major operand addressed through a 3-D tensor map {64 contiguous, K rows, 64-wide groups}: one
+    // TMA instruction lands every swizzle atom of a stage (else one 2-D box per 64-wide group)
+    int a_tma3, b_tma3;
     uint32_t idesc;
     int* status;
     // optional tracing: cycles each role spent waiting, summed over CTAs (null = off)
     //   [0] producer on a free stage, [1] MMA on a filled stage, [2] MMA on a free accumulator,
     //   [3] epilogue on a finished accumulator (sum over its 4 warps / 4), [4] CTA lifetime, [5] CTAs
     unsigned long long* wait_cycles;
+    // optional: CTA 0 records {clock64, globaltimer} at its start ([0], [1]) and end ([2], [3]), which
+    // gives the SM clock the kernel actually ran at (null = off)
+    unsigned long long* clk_words;
 
     // ---- MODE_LSE / MODE_PGRAD
     const float* bias;  // fp32 [>= col_off + N] or null
@@ -267,6 +273,28 @@ __device__ __forceinline__ bool kcand_eval(const EngineParams& p, const KTile& k
     return true;
 }
 
+// Operand loads of one ring stage (issued by one thread).
+__device__ __forceinline__ void load_stage(const EngineParams& p, const CUtensorMap* tmA, const CUtensorMap* tmB,
+                                           uint32_t sa, uint32_t sb, uint32_t bar, int a_mn, int a_k, int b_mn,
+                                           int b_k) {
+    if (!p.a_mn_major) {
+        tma_load_2d(sa, tmA, bar, a_k, a_mn);
+    } else if (p.a_tma3) {
+        tma_load_3d(sa, tmA, bar, 0, a_k, a_mn >> 6);
+    } else {
+#pragma unroll
+        for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * ATOM_BYTES, tmA, bar, a_mn + j * 64, a_k);
+    }
+    if (!p.b_mn_major) {
+        tma_load_2d(sb, tmB, bar, b_k, b_mn);
+    } else if (p.b_tma3) {
+        tma_load_3d(sb, tmB, bar, 0, b_k, b_mn >> 6);
+    } else {
+#pragma unroll
+        for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * ATOM_BYTES, tmB, bar, b_mn + j * 64, b_k);
+    }
+}
+
 template <int MODE>
 __device__ void producer_loop(const CUtensorMap* tmA, const CUtensorMap* tmB, const EngineParams& p,
                               const EngineSmem& s) {
@@ -291,18 +319,7 @@ __device__ void producer_loop(const CUtensorMap* tmA, const CUtensorMap* tmB, co
                     const uint32_t sb = sa + A_BYTES;
                     const int a_k = p.a_k_off + kb * BK, b_k = p.b_k_off + kb * BK;
                     mbar_expect_tx(bar, STAGE_BYTES);
-                    if (!p.a_mn_major) {
-                        tma_load_2d(sa, tmA, bar, a_k, a_mn);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * ATOM_BYTES, tmA, bar, a_mn + j * 64, a_k);
-                    }
-                    if (!p.b_mn_major) {
-                        tma_load_2d(sb, tmB, bar, b_k, b_mn);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * ATOM_BYTES, tmB, bar, b_mn + j * 64, b_k);
-                    }
+                    load_stage(p, tmA, tmB, sa, sb, bar, a_mn, a_k, b_mn, b_k);
                     if (++stage == NSTAGE) {
                         stage = 0;
                         phase ^= 1u;
@@ -337,20 +354,7 @@ __device__ void producer_loop(const CUtensorMap* tmA, const CUtensorMap* tmB, co
                         const uint32_t sa = smem_u32(s.stages + stage * STAGE_BYTES);
                         const uint32_t sb = sa + A_BYTES;
                         mbar_expect_tx(bar, STAGE_BYTES);
-                        if (!p.a_mn_major) {
-                            tma_load_2d(sa, tmA, bar, a_k, a_mn);
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < BM / 64; ++j)
-                                tma_load_2d(sa + j * ATOM_BYTES, tmA, bar, a_mn + j * 64, a_k);
-                        }
-                        if (!p.b_mn_major) {
-                            tma_load_2d(sb, tmB, bar, b_k, b_mn);
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < BN / 64; ++j)
-                                tma_load_2d(sb + j * ATOM_BYTES, tmB, bar, b_mn + j * 64, b_k);
-                        }
+                        load_stage(p, tmA, tmB, sa, sb, bar, a_mn, a_k, b_mn, b_k);
                     }
                 }
                 ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -808,6 +812,10 @@ engine_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
         if (int(blockIdx.x) >= probe.n_items) return;
     }
 
+    if (p.clk_words && blockIdx.x == 0 && threadIdx.x == 0) {
+        p.clk_words[0] = (unsigned long long)clock64();
+        p.clk_words[1] = global_timer_ns();
+    }
     if (threadIdx.x == 0) {
         for (int i = 0; i < NSTAGE; ++i) {
             mbar_init(smem_u32(&s.full[i]), 1);
@@ -854,6 +862,10 @@ engine_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
         __syncwarp();
         tc_fence_after();
         tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+    if (p.clk_words && blockIdx.x == 0 && threadIdx.x == 0) {
+        p.clk_words[2] = (unsigned long long)clock64();
+        p.clk_words[3] = global_timer_ns();
     }
     if (kTrace && p.wait_cycles && threadIdx.x == 0) {
         atomicAdd(p.wait_cycles + 4, (unsigned long long)(clock64() - t_start));

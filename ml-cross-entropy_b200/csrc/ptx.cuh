@@ -61,8 +61,9 @@ constexpr long long kWaitLimitCycles = 4000000000LL;
 
 // Bounded wait. Returns false if the wait was abandoned; in that case the
 // CTA abort flag is set and every other waiter of the CTA leaves promptly.
+// `limit` is the number of SM cycles after which the waiter gives up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status, int code) {
+                                          int* status, int code, long long limit = kWaitLimitCycles) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     uint32_t it = 0;
@@ -70,7 +71,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         if (mbar_try_wait(bar, parity)) return true;
         if ((++it & 0xffu) == 0) {
             if (*abort_flag) return false;
-            if (clock64() - t0 > kWaitLimitCycles) {
+            if (clock64() - t0 > limit) {
                 *abort_flag = 1;
                 if (status) atomicCAS(status, 0, code | (int(blockIdx.x) << 8));
                 return false;
@@ -93,6 +94,22 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* m, 
         "[%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(x), "r"(y)
         : "memory");
+}
+
+// 3-D tiled load; x (innermost) must make x*elemsize a multiple of 16.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* m, uint32_t bar,
+                                            int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
 }
 
 // ----------------------------------------------------------------- tcgen05

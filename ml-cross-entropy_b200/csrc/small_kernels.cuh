@@ -66,10 +66,16 @@ __global__ void to_f32_kernel(const void* __restrict__ src, int dtype, float* __
 }
 
 // lse[row] = ln2 * (M + log2(sum_b s_b * 2^(m_b - M))) over the bands of the forward kernel.
+// A non-zero status word (a pipeline kernel abandoned a wait, so `partial` is incomplete) turns
+// every output into NaN: the failure shows in the loss without a host read of the word.
 __global__ void lse_combine_kernel(const float2* __restrict__ partial, int n_band, long long n_rows,
-                                   float* __restrict__ lse) {
+                                   float* __restrict__ lse, const int* __restrict__ status) {
     const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
     if (i >= n_rows) return;
+    if (status && *status != 0) {
+        lse[i] = __int_as_float(0x7fc00000);
+        return;
+    }
     float m = -INFINITY;
     for (int b = 0; b < n_band; ++b) m = fmaxf(m, partial[(size_t)b * n_rows + i].x);
     float s = 0.0f;
@@ -169,7 +175,8 @@ __global__ void tile_mark_kernel(const float* __restrict__ tile_max, const float
 __global__ void tile_index_kernel(const uint8_t* __restrict__ act, int n_rb, int n_vt, int capacity,
                                   int max_pass, int* __restrict__ col_ptr, int* __restrict__ slot_tile,
                                   int* __restrict__ slot_of, int* __restrict__ row_ptr,
-                                  int* __restrict__ row_slots, int* __restrict__ pass_info) {
+                                  int* __restrict__ row_slots, int* __restrict__ pass_info,
+                                  int* __restrict__ counts_out) {
     extern __shared__ int sm[];
     int* col_s = sm;              // [n_vt + 1] column counts, then column starts
     int* row_s = sm + n_vt + 1;   // [n_rb + 1] row counts, then row starts
@@ -253,6 +260,11 @@ __global__ void tile_index_kernel(const uint8_t* __restrict__ act, int n_rb, int
             if (vt_end == n_vt) break;
             ++pass;
             vt0 = vt_end;
+        }
+        if (counts_out) {  // optional report: {active tiles, all tiles, passes that hold tiles}
+            counts_out[0] = total;
+            counts_out[1] = n_rb * n_vt;
+            counts_out[2] = total > 0 ? pass + 1 : 0;
         }
         for (int q = pass + 1; q < max_pass; ++q) {
             pass_info[4 * q + 0] = n_vt;
@@ -378,15 +390,17 @@ __global__ void klist_build_kernel(const int* __restrict__ pass_info, const int*
     }
 }
 
-// dbias[col] += sum_rows G[row][col] for a [n_rows][width] 16-bit block with pitch ldg.
+// Column sums of a [n_rows][width] 16-bit block with pitch ldg, in two deterministic stages.
+// Stage 1: partial[rb][col] = sum of rows [rb * rows_per_block, (rb + 1) * rows_per_block) of column col;
 // grid = (ceil(width/256), ceil(n_rows/rows_per_block)); 128 threads, two columns each.
 template <typename T>
-__global__ void colsum_kernel(const T* __restrict__ g, long long ldg, long long n_rows, int width,
-                              int rows_per_block, float* __restrict__ dbias) {
+__global__ void colsum_partial_kernel(const T* __restrict__ g, long long ldg, long long n_rows, int width,
+                                      int rows_per_block, float* __restrict__ partial, long long ld_partial) {
     const int col = (blockIdx.x * 128 + threadIdx.x) * 2;
     if (col >= width) return;
     const long long r0 = (long long)blockIdx.y * rows_per_block;
     const long long r1 = min(n_rows, r0 + rows_per_block);
+    float* out = partial + (size_t)blockIdx.y * ld_partial + col;
     float s0 = 0.0f, s1 = 0.0f;
     if (col + 1 < width) {
         for (long long r = r0; r < r1; ++r) {
@@ -395,25 +409,117 @@ __global__ void colsum_kernel(const T* __restrict__ g, long long ldg, long long 
             s0 += float(h[0]);
             s1 += float(h[1]);
         }
-        atomicAdd(dbias + col, s0);
-        atomicAdd(dbias + col + 1, s1);
+        out[0] = s0;
+        out[1] = s1;
     } else {
         for (long long r = r0; r < r1; ++r) s0 += float(g[r * ldg + col]);
-        atomicAdd(dbias + col, s0);
+        out[0] = s0;
     }
 }
+// Stage 2: dbias[col] = sum over the row blocks, in ascending order (no atomics: the same bits every run).
+__global__ void colsum_finish_kernel(const float* __restrict__ partial, long long ld_partial, int n_rowblk,
+                                     int width, float* __restrict__ dbias) {
+    const int col = blockIdx.x * blockDim.x + threadIdx.x;
+    if (col >= width) return;
+    float s = 0.0f;
+    for (int rb = 0; rb < n_rowblk; ++rb) s += partial[(size_t)rb * ld_partial + col];
+    dbias[col] = s;
+}
 
-// d_e[rows[i]][0..D) = cast(src[i][0..D)); one block per row.
+// A non-zero status word (a pipeline kernel abandoned a wait) turns the rows into NaN.
 template <typename T>
 __global__ void scatter_cast_kernel(const float* __restrict__ src, long long ld_src,
                                     const void* __restrict__ rows, int rows_i64, T* __restrict__ dst,
-                                    long long ld_dst, long long D, long long n_rows) {
+                                    long long ld_dst, long long D, long long n_rows,
+                                    const int* __restrict__ status) {
     const long long i = blockIdx.x;
     if (i >= n_rows) return;
     const long long r = rows ? load_index(rows, rows_i64, i) : i;
     const float* s = src + i * ld_src;
     T* d = dst + r * ld_dst;
-    for (long long j = threadIdx.x; j < D; j += blockDim.x) d[j] = T(s[j]);
+    const bool bad = status && *status != 0;
+    const bool vec = !bad && (D % 4 == 0) && ((reinterpret_cast<uintptr_t>(s) & 15) == 0) &&
+                     ((reinterpret_cast<uintptr_t>(d) & (4 * sizeof(T) - 1)) == 0);
+    if (vec) {
+        for (long long j = threadIdx.x; j < D / 4; j += blockDim.x) {
+            const float4 v = reinterpret_cast<const float4*>(s)[j];
+            if constexpr (sizeof(T) == 4) {
+                reinterpret_cast<float4*>(d)[j] = v;
+            } else {
+                T o[4] = {T(v.x), T(v.y), T(v.z), T(v.w)};
+                reinterpret_cast<uint2*>(d)[j] = *reinterpret_cast<const uint2*>(o);
+            }
+        }
+    } else {
+        for (long long j = threadIdx.x; j < D; j += blockDim.x) d[j] = bad ? T(__int_as_float(0x7fc00000)) : T(s[j]);
+    }
+}
+
+// Tail of the forward pass in one block: merges the per-rank statistics, forms the negative
+// log-likelihood of every row and reduces or scatters it.
+//   stats[r][0][i] = log-sum-exp of row i over rank r's vocabulary shard, stats[r][1][i] = minus the
+//   correct-token logit (0 on ranks that do not own the label); `world` ranks, rank pitch 2 * n_rows.
+//   lse_i = logsumexp_r stats[r][0][i],  nll_i = lse_i + sum_r stats[r][1][i]
+//   reduction 0 / 1: loss_out[0] = mean / sum of nll (fixed summation order: deterministic)
+//   reduction 2    : loss_out[pos_i] = nll_i, pos_i = rows[i] + shift (rows null: i)
+//   lse_rows (optional) [n_rows] receives lse_i; lse_scatter (optional) receives lse_i at pos_i.
+// Positions that no row maps to are cleared by the caller before the launch.
+constexpr int TAIL_THREADS = 1024;
+__global__ void __launch_bounds__(TAIL_THREADS)
+loss_tail_kernel(const float* __restrict__ stats, int world, long long n_rows, const void* __restrict__ rows,
+                 int rows_i64, long long shift, int reduction, float* __restrict__ lse_rows,
+                 float* __restrict__ loss_out, float* __restrict__ lse_scatter, const int* __restrict__ status) {
+    __shared__ double warp_sum[TAIL_THREADS / 32];
+    const bool bad = status && *status != 0;
+    double acc = 0.0;
+    for (long long i = threadIdx.x; i < n_rows; i += TAIL_THREADS) {
+        float m = -INFINITY, neg = 0.0f;
+        for (int r = 0; r < world; ++r) {
+            m = fmaxf(m, stats[(size_t)r * 2 * n_rows + i]);
+            neg += stats[((size_t)r * 2 + 1) * n_rows + i];
+        }
+        float lse = m;
+        if (world > 1 && m > -INFINITY) {
+            float ssum = 0.0f;
+            for (int r = 0; r < world; ++r) ssum += expf(stats[(size_t)r * 2 * n_rows + i] - m);
+            lse = m + logf(ssum);
+        }
+        float nll = lse + neg;
+        if (bad) lse = nll = __int_as_float(0x7fc00000);
+        const long long pos = rows ? load_index(rows, rows_i64, i) + shift : i;
+        if (lse_rows) lse_rows[i] = lse;
+        if (lse_scatter) lse_scatter[pos] = lse;
+        if (reduction == 2) loss_out[pos] = nll;
+        acc += (double)nll;
+    }
+    if (reduction == 2) return;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if ((threadIdx.x & 31) == 0) warp_sum[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double t = 0.0;
+        for (int w = 0; w < TAIL_THREADS / 32; ++w) t += warp_sum[w];
+        loss_out[0] = float(reduction == 0 ? t / double(n_rows) : t);
+    }
+}
+
+// One warp waits on an mbarrier at which nobody ever arrives, with a caller-chosen cycle limit: the
+// wait gives up, the status word receives ERR_WAIT_TMEM_FULL and the kernel returns normally.  It
+// exercises the bounded-wait path of the pipeline kernels (mbar_wait) without touching TMA, tensor
+// memory or the tensor cores.
+__global__ void selftest_wait_kernel(long long limit_cycles, int* __restrict__ status) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        abort_flag = 0;
+        fence_barrier_init();
+    }
+    __syncthreads();
+    // every lane waits, as the epilogue warps of the pipeline do; the first to time out raises the
+    // abort flag, the others see it at their next poll
+    mbar_wait(smem_u32(&bar), 0, &abort_flag, status, ERR_WAIT_TMEM_FULL, limit_cycles);
 }
 
 // ---- rows that enter the loss (ordered stream compaction in two launches)

@@ -27,16 +27,21 @@ EXPORTS = (
     "cce_b200_tile_max_elems",
     "cce_b200_lse_forward_static",
     "cce_b200_indexed_neg_dot",
+    "cce_b200_loss_tail",
     "cce_b200_valid_rows_workspace_bytes",
     "cce_b200_valid_rows",
     "cce_b200_backward_workspace_bytes",
     "cce_b200_backward",
     "cce_b200_gemm",
     "cce_b200_read_status",
+    "cce_b200_lse_forward_static_status",
+    "cce_b200_selftest_wait",
     "cce_b200_launch_count",
     "cce_b200_profile_enable",
     "cce_b200_profile_wait_counters",
     "cce_b200_profile_read",
+    "cce_b200_profile_clock_words",
+    "cce_b200_profile_tile_counts",
     "cce_b200_strerror",
     "cce_b200_last_cuda_error",
     "cce_b200_version",
@@ -115,6 +120,19 @@ def lib() -> ctypes.CDLL:
     L.cce_b200_lse_forward_static.argtypes = [POINTER(Operands), c_void_p, c_void_p]
     L.cce_b200_indexed_neg_dot.restype = c_int32
     L.cce_b200_indexed_neg_dot.argtypes = [POINTER(Operands), c_void_p, c_int64, c_int64, c_void_p, c_void_p]
+    L.cce_b200_loss_tail.restype = c_int32
+    L.cce_b200_loss_tail.argtypes = [
+        c_void_p, c_int32, c_int64, c_void_p, c_int32, c_int64, c_int64, c_int32, c_void_p, c_void_p, c_void_p,
+        c_void_p, c_void_p,
+    ]  # fmt: skip
+    L.cce_b200_lse_forward_static_status.restype = c_int32
+    L.cce_b200_lse_forward_static_status.argtypes = [c_void_p, POINTER(c_int32)]
+    L.cce_b200_selftest_wait.restype = c_int32
+    L.cce_b200_selftest_wait.argtypes = [c_int64, c_void_p, c_void_p]
+    L.cce_b200_profile_clock_words.restype = c_int32
+    L.cce_b200_profile_clock_words.argtypes = [c_void_p]
+    L.cce_b200_profile_tile_counts.restype = c_int32
+    L.cce_b200_profile_tile_counts.argtypes = [c_void_p]
     L.cce_b200_valid_rows_workspace_bytes.restype = c_size_t
     L.cce_b200_valid_rows_workspace_bytes.argtypes = [c_int64]
     L.cce_b200_valid_rows.restype = c_int32

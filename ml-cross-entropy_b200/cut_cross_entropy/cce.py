@@ -14,11 +14,12 @@ import torch
 import torch.amp
 
 from .cce_backward import cce_backward_kernel
+from .cce_loss_tail import loss_tail_kernel
 from .cce_lse_forward import cce_lse_forward_kernel
 from .constants import IGNORE_INDEX
 from .indexed_dot import indexed_neg_dot_forward_kernel
-from .utils import PendingValidRows, TensorInfo, _handle_eps, handle_reduction_none, launch_flat_valids
-from .vocab_parallel.utils import VocabParallelOptions, vp_merge_forward
+from .utils import PendingValidRows, TensorInfo, _handle_eps, launch_flat_valids
+from .vocab_parallel.utils import VocabParallelOptions, vp_gather_stats
 
 
 @dataclass
@@ -38,16 +39,6 @@ class CCEParams:
     return_lse: bool
     # the valid-row list while the GPU is still writing it; forward() turns it into `valids`
     pending_valids: PendingValidRows | None = None
-
-
-def _reduce_loss(nll: torch.Tensor, params: CCEParams) -> torch.Tensor:
-    if params.reduction == "mean":
-        return nll.mean()
-    if params.reduction == "sum":
-        return nll.sum()
-    if params.reduction == "none":
-        return handle_reduction_none(params.batch_shape, params.valids, params.shift, nll)
-    raise ValueError(f"Unknown reduction {params.reduction}")
 
 
 class LinearCrossEntropyFunction(torch.autograd.Function):
@@ -87,6 +78,12 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
             and (params.filter_c_grad or not c_info.requires_grad)
             and not (bias_info is not None and bias_info.requires_grad)
         )
+        if params.reduction not in ("mean", "sum", "none"):
+            raise ValueError(f"Unknown reduction {params.reduction}")
+        # (lse, -correct logit) of the valid rows sit side by side in one buffer, sized for every row
+        # until the length of the row list is known: the tail kernel (and, under vocab parallelism,
+        # the one all-gather) reads them as a [2, B] block.
+        stats_flat = torch.empty((2 * e.size(0),), dtype=torch.float32, device=e.device)
         # a pending row list is waited for inside the launcher, after everything that does not need it
         ret = cce_lse_forward_kernel(
             e=e,
@@ -95,13 +92,18 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
             valids=pending if pending is not None else params.valids,
             softcap=params.softcap,
             return_tile_max=want_tile_max,
+            stats_flat=stats_flat,
         )
         if pending is not None:
             params.valids = pending.resolve()
         lse, tile_max = ret if want_tile_max else (ret, None)
         assert isinstance(lse, torch.Tensor)
+        n_rows = lse.numel()
+        stats = stats_flat[: 2 * n_rows].view(1, 2, n_rows)
+        if lse.data_ptr() != stats_flat.data_ptr():  # a launcher that allocated its own result
+            stats[0, 0].copy_(lse)
         # labels this rank does not own give 0, so the same call serves the vocab-parallel case
-        neg_dot = indexed_neg_dot_forward_kernel(
+        indexed_neg_dot_forward_kernel(
             e=e,
             c=c,
             inds=params.targets,
@@ -109,22 +111,33 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
             shift=params.shift,
             valids=params.valids,
             softcap=params.softcap,
-            out_dtype=lse.dtype,
+            out_dtype=torch.float32,
             vocab_start=vocab_start,
+            out=stats[0, 1],
         )
         if vp is not None:
-            lse, neg_dot = vp_merge_forward(lse, neg_dot, vp.group)
+            stats = vp_gather_stats(stats[0], vp.group)  # [world, 2, B]
 
-        nll = neg_dot.add_(lse)
+        # one launch: merge over the ranks, nll = lse - correct logit, mean / sum / scatter
+        loss, lse_out, lse_rows = loss_tail_kernel(
+            stats,
+            params.valids,
+            params.shift,
+            params.batch_shape,
+            params.reduction,
+            return_lse=params.return_lse,
+            want_lse_rows=vp is not None,
+        )
+        if vp is not None:
+            assert lse_rows is not None
+            lse = lse_rows  # the global log-sum-exp; without vocab parallelism it is stats[0, 0] itself
+        else:
+            lse = stats[0, 0]
 
         ctx.save_for_backward(e, c, bias, lse, params.targets, params.valids, tile_max)
         ctx.params = params
         ctx.e_info, ctx.c_info, ctx.bias_info = e_info, c_info, bias_info
-
-        lse_out = None
-        if params.return_lse:
-            lse_out = handle_reduction_none(params.batch_shape, params.valids, params.shift, lse)
-        return _reduce_loss(nll, params), lse_out
+        return loss, lse_out
 
     @staticmethod
     @torch.amp.custom_bwd(device_type="cuda")

@@ -21,6 +21,7 @@ def cce_lse_forward_kernel(
     softcap: float | None = None,
     return_logit_avg: bool = False,
     return_tile_max: bool = False,
+    stats_flat: torch.Tensor | None = None,
 ) -> tuple[torch.Tensor, torch.Tensor | None] | torch.Tensor:
     """``lse[i] = logsumexp_v(softcap(e[valids[i]] @ c[v] + bias[v]))`` as float32 ``[B]``.
 
@@ -32,6 +33,10 @@ def cce_lse_forward_kernel(
     ``valids`` may be a :class:`~cut_cross_entropy.utils.PendingValidRows` (a row list the GPU is
     still writing): buffers are then sized for all rows and the operand description is prepared
     before the list's length is waited for, so the launch follows the wait at once.
+
+    ``stats_flat`` (float32, at least as many elements as there can be rows) receives the result in
+    its first ``B`` elements instead of a fresh tensor: the forward pass keeps the log-sum-exp and the
+    correct-token logit side by side for its tail kernel.
 
     ``return_tile_max`` asks for this backend's own by-product instead: the largest logit (in
     log2 units) of every (32-row group, 256-column tile) block, which lets the filtered
@@ -52,7 +57,11 @@ def cce_lse_forward_kernel(
         valids = valids.contiguous()
 
     op = _native.make_operands(e, c, bias, valids, softcap)
-    lse = torch.empty((op.n_rows,), dtype=torch.float32, device=e.device)
+    if stats_flat is not None:
+        assert stats_flat.dtype == torch.float32 and stats_flat.is_contiguous() and stats_flat.numel() >= op.n_rows
+        lse = stats_flat[: op.n_rows]
+    else:
+        lse = torch.empty((op.n_rows,), dtype=torch.float32, device=e.device)
     L = _native.lib()
     tile_max = None
     if return_tile_max:

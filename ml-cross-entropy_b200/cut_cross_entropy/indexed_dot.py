@@ -23,8 +23,11 @@ def indexed_neg_dot_forward_kernel(
     softcap: float | None = None,
     out_dtype: torch.dtype | None = None,
     vocab_start: int = 0,
+    out: torch.Tensor | None = None,
 ) -> torch.Tensor:
-    """``out[i] = -softcap(e[r] @ c[t] + bias[t])`` with ``r = valids[i]``, ``t = inds[r + shift] - vocab_start``."""
+    """``out[i] = -softcap(e[r] @ c[t] + bias[t])`` with ``r = valids[i]``, ``t = inds[r + shift] - vocab_start``.
+
+    ``out`` (float32, contiguous, one element per row) is written in place and returned when given."""
     assert inds.ndim == 1 and e.ndim == 2 and c.ndim == 2
     assert inds.size(0) == e.size(0)
     assert c.size(1) == e.size(1)
@@ -41,7 +44,11 @@ def indexed_neg_dot_forward_kernel(
         valids = valids.contiguous()
 
     op = _native.make_operands(e, c, bias, valids, softcap)
-    out = torch.empty((op.n_rows,), dtype=torch.float32, device=e.device)
+    if out is not None:
+        assert out.dtype == torch.float32 and out.is_contiguous() and out.numel() == op.n_rows
+        out_dtype = torch.float32
+    else:
+        out = torch.empty((op.n_rows,), dtype=torch.float32, device=e.device)
     with torch.cuda.device(e.device):
         rc = _native.lib().cce_b200_indexed_neg_dot(
             op, inds.data_ptr(), int(shift), int(vocab_start), out.data_ptr(), _native.stream_ptr(e.device)

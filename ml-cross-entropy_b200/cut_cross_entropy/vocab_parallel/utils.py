@@ -48,6 +48,18 @@ class VocabParallelOptions:
         return cls(start, stop, group, reduce_e_grad)
 
 
+def vp_gather_stats(local: torch.Tensor, pg: "dist.ProcessGroup | None") -> torch.Tensor:
+    """All-gather of the ranks' ``[2, B]`` float32 blocks (local log-sum-exp, minus the local
+    correct-token logit) into ``[world, 2, B]``: the forward's one exchange, merged afterwards by
+    the tail kernel (``cce_b200_loss_tail``)."""
+    world = dist.get_world_size(pg)
+    assert local.dim() == 2 and local.size(0) == 2 and local.dtype == torch.float32
+    local = local.contiguous()
+    out = local.new_empty((world, 2, local.size(1)))
+    dist.all_gather_into_tensor(out.view(world * 2, local.size(1)), local, group=pg)
+    return out
+
+
 def vp_merge_forward(
     local_lse: torch.Tensor, local_neg_dot: torch.Tensor, pg: "dist.ProcessGroup | None"
 ) -> tuple[torch.Tensor, torch.Tensor]:
@@ -73,3 +85,47 @@ def vp_reduce_e_grad_(e_grad_f32: torch.Tensor, pg: "dist.ProcessGroup | None") 
     assert e_grad_f32.dtype == torch.float32
     dist.all_reduce(e_grad_f32, group=pg)
     return e_grad_f32
+
+
+# ---- the reference's own helper names (cut_cross_entropy/vocab_parallel/utils.py:47-103), kept for
+# callers that import them; the loss path above needs one exchange where these take three.
+def vp_reduce_lse(vp_lse: torch.Tensor, pg: "dist.ProcessGroup | None") -> torch.Tensor:
+    """Global log-sum-exp from per-rank ones: max all-reduce, then sum all-reduce of the rescaled terms."""
+    lse_max = vp_lse.clone()
+    dist.all_reduce(lse_max, op=dist.ReduceOp.MAX, group=pg)
+    scaled = (vp_lse - lse_max).exp()
+    dist.all_reduce(scaled, group=pg)
+    return lse_max + scaled.log()
+
+
+def vp_reduce_correct_logit(
+    vp_correct_logit: torch.Tensor, pg: "dist.ProcessGroup | None", dtype: torch.dtype | None = None
+) -> torch.Tensor:
+    """Sum over the ranks of the correct-token logit (zero on ranks that do not own the label)."""
+    out = vp_correct_logit.to(dtype=dtype, copy=True)
+    dist.all_reduce(out, group=pg)
+    return out
+
+
+def vp_reduce_e_grad(e_grad: torch.Tensor, pg: "dist.ProcessGroup | None") -> torch.Tensor:
+    """Sum of the partial ``dE`` over the ranks, accumulated in float32, returned in ``e_grad``'s dtype."""
+    return vp_reduce_e_grad_(e_grad.to(dtype=torch.float32, copy=True), pg).type_as(e_grad)
+
+
+class _ReduceEGradHook(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, e: torch.Tensor, pg: "dist.ProcessGroup | None" = None) -> torch.Tensor:
+        ctx.pg = pg
+        return e
+
+    @staticmethod
+    def backward(ctx, e_grad: torch.Tensor) -> tuple[torch.Tensor, None]:
+        return vp_reduce_e_grad(e_grad, ctx.pg), None
+
+
+def vp_reduce_e_grad_hook(e: torch.Tensor, vocab_parallel_options: VocabParallelOptions) -> torch.Tensor:
+    """Identity in the forward pass; sums the gradient of ``e`` over the group in the backward pass
+    (when ``reduce_e_grad`` is set)."""
+    if vocab_parallel_options.reduce_e_grad:
+        return _ReduceEGradHook.apply(e, vocab_parallel_options.group)
+    return e

@@ -2,7 +2,9 @@
 
 Usage (in a container that has the reference checkout; it is not needed to run the tests):
 
-    TORCH_COMPILE_DISABLE=1 python tests/golden/make_golden.py /path/to/ml-cross-entropy
+    TORCH_COMPILE_DISABLE=1 python tests/golden/make_golden.py /path/to/ml-cross-entropy [case ...]
+
+(with case names, only those fixtures are rewritten).
 
 It imports the reference's ``cut_cross_entropy`` package from that path and calls its
 ``linear_cross_entropy(..., impl="torch_compile")`` — the materialised-logits code in
@@ -33,6 +35,9 @@ CASES = [
     ("mean_zloss_softcap", 128, 32, 300, 72, dict(z_loss=True, softcap=30.0)),
     ("odd_shapes", 252, 63, 507, 123, dict(bias=True, ignored=0.2, shift=1)),
     ("wide_vocab", 64, 64, 1100, 64, dict(reduction="sum", bias=True)),
+    # large enough for several forward bands, and (with a 1 MB logit-gradient buffer) for several
+    # vocabulary chunks / several passes of the block-list backward
+    ("multi_band", 700, 100, 2500, 192, dict(ignored=0.2, bias=True, softcap=25.0, z_loss=True)),
 ]
 
 
@@ -51,7 +56,7 @@ def make_inputs(N, T, V, D, opts, seed):
     return e.view(N // T, T, D), c, bias, targets.view(N // T, T)
 
 
-def main(ref_root: str) -> None:
+def main(ref_root: str, only: tuple[str, ...] = ()) -> None:
     assert os.environ.get("TORCH_COMPILE_DISABLE") == "1", "run with TORCH_COMPILE_DISABLE=1"
     sys.path.insert(0, ref_root)
     import cut_cross_entropy as ref
@@ -60,6 +65,8 @@ def main(ref_root: str) -> None:
     assert Path(ref.__file__).resolve().is_relative_to(Path(ref_root).resolve()), ref.__file__
     torch.set_float32_matmul_precision("highest")
     for i, (name, N, T, V, D, opts) in enumerate(CASES):
+        if only and name not in only:
+            continue
         e16, c16, b16, targets = make_inputs(N, T, V, D, opts, seed=100 + i)
         e = e16.float().requires_grad_(True)
         c = c16.float().requires_grad_(True)
@@ -87,6 +94,6 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    if len(sys.argv) != 2:
-        raise SystemExit("usage: make_golden.py /path/to/ml-cross-entropy")
-    main(sys.argv[1])
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py /path/to/ml-cross-entropy [case ...]")
+    main(sys.argv[1], tuple(sys.argv[2:]))

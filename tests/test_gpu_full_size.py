@@ -73,7 +73,7 @@ def _check_grad(got, want, what, slack=None, rel=1e-2, min_cos=0.9999):
 
 
 @pytest.mark.parametrize("cfg_name", ["gemma2-2b-head", "llama3-8b-head-shift", "gemma2-9b-head-softcap-zloss",
-                                      "qwen25-7b-head-long-kahan"])  # fmt: skip
+                                      "qwen25-7b-head-long-kahan", "vocab-parallel-head"])  # fmt: skip
 def test_full_size_against_float32(cfg_name):
     torch.backends.cuda.matmul.allow_tf32 = True  # exact for bf16-valued operands
     cfg, kw, e, c, bias, targets, loss, lse = _run(cfg_name)
@@ -229,10 +229,10 @@ def test_full_size_properties():
     _check_grad(de_b, de_a, "dE with a small tile pool")
 
 
-@pytest.mark.parametrize("world", [4, 8])
-def test_full_size_vocabulary_shards_on_one_gpu(world):
-    """The per-rank work of `bench.py --gpus N` at the Gemma-2-2B head shape, shard after shard on
-    one GPU, with the block-list backward each rank runs (per-shard tile maxima, global lse):
+@pytest.mark.parametrize("cfg_name,world", [("gemma2-2b-head", 4), ("gemma2-2b-head", 8), ("vocab-parallel-head", 8)])
+def test_full_size_vocabulary_shards_on_one_gpu(cfg_name, world):
+    """The per-rank work of `bench.py --gpus N` (Gemma-2-2B head, and the 32768 x 4096 x 262144
+    vocab-parallel head split 8 ways), shard after shard on one GPU, with the block-list backward each rank runs (per-shard tile maxima, global lse):
     the shards' log-sum-exps merge to the unsharded one, each shard's dC is the matching slice of
     the unsharded dC bit for bit (the same tiles, the same order of row blocks), and the fp32 dE
     partial sums add up to the unsharded dE within its bf16 rounding."""
@@ -241,11 +241,11 @@ def test_full_size_vocabulary_shards_on_one_gpu(world):
     from cut_cross_entropy.utils import TensorInfo, _build_flat_valids
     from cut_cross_entropy.vocab_parallel import partition_n_into_range
 
-    cfg = bench.CONFIGS["gemma2-2b-head"]
+    cfg = bench.CONFIGS[cfg_name]
     e, c, _, targets = bench.make_inputs(cfg, DEV)
     t = targets.flatten()
-    valids = _build_flat_valids(targets, IGNORE, 0)
-    B, V = valids.numel(), c.size(0)
+    valids = _build_flat_valids(targets, IGNORE, 0)  # None when no label is ignored
+    B, V = (e.size(0) if valids is None else valids.numel()), c.size(0)
     info = TensorInfo(torch.bfloat16, True)
     do = torch.ones((), device=DEV)
     eps = 2.0**-12

@@ -45,7 +45,7 @@ def _pad_pitch(t):
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("a_mn", [0, 1])
 @pytest.mark.parametrize("b_mn", [0, 1])
-@pytest.mark.parametrize("shape", [(128, 256, 64), (300, 700, 200), (1, 9, 24), (1024, 2304, 1000)])
+@pytest.mark.parametrize("shape", [(128, 256, 64), (300, 700, 200), (1, 9, 24), (1024, 2304, 1000), (192, 320, 130)])
 def test_gemm_pipeline_all_operand_orders(dtype, a_mn, b_mn, shape):
     M, N, K = shape
     torch.manual_seed(0)
@@ -262,3 +262,95 @@ def test_valid_rows_entry_point_rejects_bad_arguments():
     bad = list(args)
     bad[7] = None  # nowhere to put the count
     assert L.cce_b200_valid_rows(*bad, ws.numel(), st) == -1
+
+
+@pytest.mark.parametrize("world", [1, 3])
+@pytest.mark.parametrize("reduction", ["mean", "sum", "none"])
+@pytest.mark.parametrize("layout", ["all_rows", "some_rows", "shifted"])
+def test_loss_tail_kernel(world, reduction, layout):
+    """cce_b200_loss_tail against the PyTorch expressions it replaces: logsumexp over the ranks,
+    nll = lse - correct logit, mean / sum, or the scatter to the batch shape (zeros elsewhere)."""
+    from cut_cross_entropy.cce_loss_tail import loss_tail_kernel
+
+    g = torch.Generator(device="cpu").manual_seed(world * 7 + len(layout))
+    batch_shape = torch.Size((5, 400))
+    n_total = batch_shape.numel()
+    shift = 2 if layout == "shifted" else 0
+    if layout == "all_rows":
+        valids, n_rows = None, n_total
+    else:
+        keep = torch.rand(n_total, generator=g) < 0.7
+        if shift:
+            keep &= (torch.arange(n_total) % 400) < 400 - shift
+        valids = keep.nonzero().squeeze(1).to(torch.int64 if shift else torch.int32).to(DEV)
+        n_rows = valids.numel()
+    stats = torch.randn(world, 2, n_rows, generator=g).to(DEV) * 3 + 5
+    loss, lse_out, lse_rows = loss_tail_kernel(stats, valids, shift, batch_shape, reduction, True, True)
+    want_lse = torch.logsumexp(stats[:, 0].double(), 0)
+    want_nll = want_lse + stats[:, 1].double().sum(0)
+    torch.testing.assert_close(lse_rows.double(), want_lse, rtol=1e-6, atol=1e-6)
+    pos = torch.arange(n_total, device=DEV) if valids is None else valids.long() + shift
+    full = torch.zeros(n_total, dtype=torch.float64, device=DEV)
+    full[pos] = want_lse
+    torch.testing.assert_close(lse_out.double().view(-1), full, rtol=1e-6, atol=1e-6)
+    if reduction == "none":
+        full[pos] = want_nll
+        torch.testing.assert_close(loss.double().view(-1), full, rtol=1e-6, atol=1e-6)
+        assert loss.shape == batch_shape
+    else:
+        want = want_nll.mean() if reduction == "mean" else want_nll.sum()
+        torch.testing.assert_close(loss.double(), want, rtol=1e-6, atol=0)
+        again, _, _ = loss_tail_kernel(stats, valids, shift, batch_shape, reduction, False, False)
+        assert again.item() == loss.item()  # fixed summation order
+
+
+def test_a_wait_that_runs_out_sets_the_status_word_and_the_kernel_returns():
+    """The bounded wait every pipeline kernel relies on, made to run out on purpose: one warp waits
+    on a barrier nobody arrives at with a limit of a million cycles.  The kernel must come back,
+    the status word must carry the wait's code, cce_b200_read_status must answer
+    CCE_ERR_KERNEL_WAIT, and the context must stay usable."""
+    import ctypes
+
+    from cut_cross_entropy import _native
+
+    L = _native.lib()
+    status = torch.zeros(64, dtype=torch.int32, device=DEV)
+    st = torch.cuda.current_stream().cuda_stream
+    assert L.cce_b200_selftest_wait(1_000_000, status.data_ptr(), st) == 0
+    word = ctypes.c_int32(0)
+    rc = L.cce_b200_read_status(status.data_ptr(), st, ctypes.byref(word))
+    assert rc == -6 and b"wait" in L.cce_b200_strerror(rc)
+    assert word.value & 0xFF == 4 and word.value >> 8 == 0  # ERR_WAIT_TMEM_FULL, block 0
+    assert int(status[0].item()) == word.value
+    assert L.cce_b200_selftest_wait(0, status.data_ptr(), st) == -1  # a limit must be given
+    # the context still works, and a clean call reads back a clean word
+    e, c, _, _ = planted_inputs(128, 256, 64, torch.bfloat16, DEV)
+    from cut_cross_entropy.cce_lse_forward import cce_lse_forward_kernel
+
+    torch.testing.assert_close(cce_lse_forward_kernel(e, c), torch.logsumexp(e.float() @ c.float().T, -1),
+                               rtol=1e-5, atol=2e-5)
+
+
+def test_bias_gradient_is_bit_reproducible():
+    """dBias is summed in a fixed order (per-row-block partial sums, then an ordered finish): the
+    same call gives the same bits every time, over several row blocks and vocabulary chunks."""
+    import os
+
+    from cut_cross_entropy import linear_cross_entropy
+
+    e, c, bias, t = planted_inputs(1500, 3000, 128, torch.bfloat16, DEV, bias=True)
+    bias = bias.float().requires_grad_(True)
+    os.environ["CCE_B200_GBUF_MB"] = "1"  # several chunks
+    try:
+        outs = []
+        for _ in range(3):
+            bias.grad = None
+            linear_cross_entropy(e, c, t, bias=bias, impl="cce_exact").backward()
+            outs.append(bias.grad.clone())
+    finally:
+        del os.environ["CCE_B200_GBUF_MB"]
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    x = e.float() @ c.float().T + bias.detach()
+    p = torch.softmax(x, -1)
+    p[torch.arange(1500), t] -= 1
+    torch.testing.assert_close(outs[0], p.sum(0) / 1500, rtol=2e-2, atol=2e-5)

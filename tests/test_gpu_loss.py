@@ -223,6 +223,20 @@ def test_golden_fixtures(name, impl):
         assert cos >= 0.9999, cos
 
 
+@pytest.mark.parametrize("impl", ["cce_exact", "cce", "cce_kahan_full_c", "cce_kahan_full_e"])
+def test_golden_fixture_across_bands_chunks_and_passes(impl):
+    """The largest reference-made fixture (700 x 2500 x 192) with a 1 MB logit-gradient buffer: the
+    forward runs 10 vocabulary bands, the dense backward 4 vocabulary chunks, the block-list
+    backward several passes over a pool of 16 tiles."""
+    import os
+
+    os.environ["CCE_B200_GBUF_MB"] = "1"
+    try:
+        test_golden_fixtures("multi_band", impl)
+    finally:
+        del os.environ["CCE_B200_GBUF_MB"]
+
+
 @pytest.mark.parametrize("cfg", ["softmax_flat", "planted"])
 @pytest.mark.parametrize("impl", ["cce_exact", "cce", "cce_kahan_full_c"])
 def test_stated_tolerances_against_cpu_oracle(cfg, impl):

@@ -263,16 +263,18 @@ def test_pending_row_list_resolution_rules():
 
 
 def test_reference_arm_of_the_benchmark_prints_the_contract_line():
-    """`bench.py --impl reference` needs no GPU: it times the CPU port on a bounded sample and
-    prints one JSON line with the metric, the config and the keys of the GPU arm's line."""
+    """Without a GPU `bench.py --impl reference` times the CPU port on a bounded sample and prints
+    one JSON line with the metric, the config and the keys of the GPU arm's line.  It uses every
+    host core it may run on even when the launcher exported OMP_NUM_THREADS=1, as torchrun does."""
     import json
+    import os
     import subprocess
     import sys
 
     out = subprocess.run(
         [sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--config", "gemma2-2b-head-small",
          "--steps", "3", "--warmup", "3"],
-        check=True, capture_output=True, text=True, timeout=600, cwd=ROOT,
+        check=True, capture_output=True, text=True, timeout=600, cwd=ROOT, env=dict(os.environ, OMP_NUM_THREADS="1"),
     )  # fmt: skip
     line = json.loads(out.stdout.strip().splitlines()[-1])
     assert line["impl"] == "reference" and line["metric"] == "linear-CE fwd+bwd tokens/s"
@@ -280,6 +282,28 @@ def test_reference_arm_of_the_benchmark_prints_the_contract_line():
     assert line["steps"] == 3 and line["warmup"] == 3 and line["ms_per_step"] > 0 and line["value"] > 0
     assert line["config"]["workload"] == "gemma2-2b-head-small" and line["vs_baseline"] is None
     cb = line["cpu_baseline"]
-    assert cb["kind"] == "port" and cb["cores"] >= 1 and cb["value"] == line["value"] and "1024 rows" in cb["sample"]
+    assert cb["kind"] == "port" and cb["value"] == line["value"] and "1024 rows" in cb["sample"]
+    assert cb["cores"] == len(os.sched_getaffinity(0)) and line["reference_kind"] == "cpu_port"
     assert line["e2e"] == {"value": line["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
     assert line["gpu_launches"] == 0
+
+
+def test_reference_and_this_package_import_side_by_side():
+    """baseline/reference_loader.py files the unmodified reference under another name without
+    disturbing this repository's package of the same name (skipped where the reference is not installed)."""
+    import sys
+
+    from baseline.reference_loader import load_reference, reference_available
+
+    ok, why = reference_available()
+    if not ok:
+        pytest.skip(why)
+    import cut_cross_entropy as ours
+
+    ref = load_reference()
+    import cut_cross_entropy as again
+
+    assert again is ours and ref is not ours
+    assert "baseline/_ref" in ref.__file__ and "ml-cross-entropy_b200" in ours.__file__
+    assert sys.modules["cce_reference"] is ref and "cce_reference.utils" in sys.modules
+    assert hasattr(ref, "linear_cross_entropy") and ref.linear_cross_entropy is not ours.linear_cross_entropy

@@ -2,7 +2,7 @@
 
 The three kernel launchers are replaced, in this test only, by CPU stand-ins built on the
 oracle, so what runs for real is the package's own orchestration: label ownership, the single
-all-gather that merges per-rank (lse, correct logit), the fp32 all-reduce of dE, the local dC.
+all-gather of the per-rank (lse, correct logit) blocks, the fp32 all-reduce of dE, the local dC.
 """
 
 from __future__ import annotations
@@ -62,12 +62,30 @@ def _install_cpu_stand_ins():
     import cut_cross_entropy.cce as cce_mod
     import cut_cross_entropy.cce_backward as bwd_mod
 
-    def lse_kernel(e, c, bias=None, valids=None, softcap=None, return_logit_avg=False, return_tile_max=False):
+    def lse_kernel(e, c, bias=None, valids=None, softcap=None, return_logit_avg=False, return_tile_max=False,
+                   stats_flat=None):
         assert not return_tile_max
         return O.lse_forward(e, c, bias, valids, softcap).float()
 
-    def dot_kernel(e, c, inds, bias=None, shift=0, valids=None, softcap=None, out_dtype=None, vocab_start=0):
-        return O.indexed_neg_dot(e, c, inds, bias, shift, valids, softcap, vocab_start=vocab_start).to(out_dtype)
+    def dot_kernel(e, c, inds, bias=None, shift=0, valids=None, softcap=None, out_dtype=None, vocab_start=0,
+                   out=None):
+        r = O.indexed_neg_dot(e, c, inds, bias, shift, valids, softcap, vocab_start=vocab_start).to(out_dtype)
+        return r if out is None else out.copy_(r)
+
+    def tail_kernel(stats, valids, shift, batch_shape, reduction, return_lse, want_lse_rows):
+        # what cce_b200_loss_tail computes, in PyTorch
+        lse = torch.logsumexp(stats[:, 0], dim=0)
+        nll = lse + stats[:, 1].sum(dim=0)
+
+        def scatter(x):
+            if valids is None:
+                return x.view(batch_shape)
+            full = x.new_zeros((batch_shape.numel(),))
+            full[valids.long() + shift] = x
+            return full.view(batch_shape)
+
+        loss = {"mean": nll.mean, "sum": nll.sum, "none": lambda: scatter(nll)}[reduction]()
+        return loss, (scatter(lse) if return_lse else None), (lse if want_lse_rows else None)
 
     def launch(do, dlse, e, c, bias, lse, valids, softcap, filter_eps, targets, shift, grad_scale,
                filter_e, filter_c, vocab_start, de, dc, dbias, tile_max=None):
@@ -99,6 +117,7 @@ def _install_cpu_stand_ins():
 
     cce_mod.cce_lse_forward_kernel = lse_kernel
     cce_mod.indexed_neg_dot_forward_kernel = dot_kernel
+    cce_mod.loss_tail_kernel = tail_kernel
     bwd_mod._launch = launch
     # no CUDA stream on CPU
     import cut_cross_entropy._native as nat
