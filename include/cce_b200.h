@@ -88,6 +88,24 @@ int cce_b200_lse_forward(const cce_b200_operands* op, float* lse /* [n_rows] */,
  * softmax value is provably below filter_eps and no label falls.  (The reference keeps a
  * different by-product for its filter, the mean logit per column, cce_lse_forward.py:95-97.) */
 size_t cce_b200_tile_max_elems(const cce_b200_operands* op);
+/* cce_b200_lse_forward with one more optional by-product: col_max_key [V] int32, the largest logit
+ * (log2 units) of every vocabulary entry over all rows, stored as an order-preserving integer key
+ * (a float f >= 0 as its bit pattern, f < 0 as its bit pattern with the low 31 bits inverted), so
+ * that an integer sort of the keys sorts the maxima.  cce_b200_backward uses it, with a vocabulary
+ * order, to bound the softmax values of reordered tiles. */
+int cce_b200_lse_forward_ex(const cce_b200_operands* op, float* lse, float* tile_max, int32_t* col_max_key,
+                            void* workspace, size_t workspace_bytes, void* stream);
+
+/* The reference's ordering key (cut_cross_entropy/cce_lse_forward.py:95-97, the optional
+ * `logit_avg` result of its forward kernel): out[v] = softcap(mean_i(e[row_i]) . c[v] + bias[v]).
+ * Without soft-capping this is the mean over the rows of the logits of column v, which is what the
+ * reference accumulates; with soft-capping it is the soft-cap of the mean of the uncapped logits
+ * (monotone in it, so it sorts the vocabulary the same way; the reference averages after capping).
+ * Three HBM-bound launches (column means of the listed rows of e, then one warp per row of c),
+ * summed in a fixed order. */
+size_t cce_b200_logit_avg_workspace_bytes(const cce_b200_operands* op);
+int cce_b200_logit_avg(const cce_b200_operands* op, float* out /* [V] */, void* workspace,
+                       size_t workspace_bytes, void* stream);
 
 /* Same result as cce_b200_lse_forward, for callers that cannot hand over a workspace.
  * (No counterpart in the reference, whose launcher allocates its own buffers through PyTorch.)
@@ -180,6 +198,15 @@ typedef struct cce_b200_backward_args {
     void* d_c;               /* [V, D] in op.dtype (fp32 for fp32 operands), row stride D, or NULL */
     float* d_bias;           /* [V] fp32 or NULL */
     const float* tile_max;   /* by-product of cce_b200_lse_forward for the same operands, or NULL */
+    /* Optional vocabulary ordering (the reference's `vocab_ordering`, cce_backward.py:154-155): a
+     * permutation of 0..V-1; the backward forms its tiles from consecutive entries of this order
+     * instead of consecutive vocabulary indices, so that entries with large probabilities share few
+     * tiles and the filter removes the rest.  Honoured when the block-list backward runs (every
+     * requested product filtered, tile_max given, no bias gradient) and col_max_key (by-product of
+     * cce_b200_lse_forward_ex for the same operands) is given too; ignored otherwise.  Costs a
+     * reordered copy of c in the workspace.  Both NULL: natural vocabulary order. */
+    const int32_t* vocab_order;
+    const int32_t* col_max_key;
 } cce_b200_backward_args;
 
 /* Gradient of sum_i d_out_i * grad_scale * (lse_i - logit_i[t_i]) + sum_i d_lse_i * lse_i

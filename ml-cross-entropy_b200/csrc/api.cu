@@ -436,6 +436,10 @@ struct BwdPlan {
     int n_rb, n_vt, capacity, max_pass;
     size_t off_minlse, off_act, off_col_ptr, off_row_ptr, off_slot_tile, off_slot_of, off_row_slots, off_pass,
         off_sflags, off_de_list, off_dc_list, off_de_cnt, off_dc_cnt;
+    // sparse with a vocabulary order: reordered copies of the classifier (and bias), inverse order, per-tile column maxima
+    bool ordered;
+    long long Dkp;  // row length (elements) of the reordered classifier copy
+    size_t off_cperm, off_bias_perm, off_inv_order, off_tile_colmax;
     // both
     size_t off_g, off_de32, total;
 };
@@ -494,6 +498,19 @@ BwdPlan plan_bwd(const cce_b200_backward_args* a) {
         off = align_up(off + (size_t)pl.n_vt * 2 * sizeof(int), 256);
         pl.off_g = off;
         off = align_up(off + (size_t)pl.capacity * kSlotBytes, 1024);
+        pl.ordered = a->vocab_order && a->col_max_key;
+        if (pl.ordered) {
+            const long long Dk = pl.ops.split ? pl.ops.Drow : op->D;
+            pl.Dkp = (Dk + 7) / 8 * 8;
+            pl.off_cperm = off;
+            off = align_up(off + (size_t)op->V * pl.Dkp * 2, 256);
+            pl.off_bias_perm = off;
+            if (op->bias) off = align_up(off + (size_t)op->V * sizeof(float), 256);
+            pl.off_inv_order = off;
+            off = align_up(off + (size_t)op->V * sizeof(int), 256);
+            pl.off_tile_colmax = off;
+            off = align_up(off + (size_t)pl.n_vt * sizeof(float), 256);
+        }
     } else {
         pl.Vc = pick_chunk(op->n_rows, op->V, op->D);
         pl.n_chunk = int(cdiv(op->V, pl.Vc));
@@ -638,6 +655,11 @@ size_t cce_b200_tile_max_elems(const cce_b200_operands* op) {
 
 int cce_b200_lse_forward(const cce_b200_operands* op, float* lse, float* tile_max, void* workspace,
                          size_t workspace_bytes, void* stream) {
+    return cce_b200_lse_forward_ex(op, lse, tile_max, nullptr, workspace, workspace_bytes, stream);
+}
+
+int cce_b200_lse_forward_ex(const cce_b200_operands* op, float* lse, float* tile_max, int32_t* col_max_key,
+                            void* workspace, size_t workspace_bytes, void* stream) {
     int rc = check_operands(op);
     if (rc != CCE_OK) return rc;
     if (!workspace || (op->n_rows > 0 && !lse)) return CCE_ERR_ARG;
@@ -650,6 +672,8 @@ int cce_b200_lse_forward(const cce_b200_operands* op, float* lse, float* tile_ma
     cudaStream_t st = (cudaStream_t)stream;
     char* ws = reinterpret_cast<char*>(workspace);
     CCE_CUDA(cudaMemsetAsync(ws, 0, kStatusBytes, st));
+    // every byte 0x80 makes each key an integer below the key of any logit (about -3.4e38 as a float)
+    if (col_max_key) CCE_CUDA(cudaMemsetAsync(col_max_key, 0x80, (size_t)op->V * sizeof(int32_t), st));
     if (op->n_rows == 0) return CCE_OK;
 
     Staged sg;
@@ -671,7 +695,8 @@ int cce_b200_lse_forward(const cce_b200_operands* op, float* lse, float* tile_ma
     p.band_len = pl.band_len;
     p.partial = reinterpret_cast<float2*>(ws + pl.off_partial);
     p.tile_max = tile_max;
-    if (use_cta_pairs()) {
+    p.col_max_key = col_max_key;
+    if (use_cta_pairs() && !col_max_key) {
         // two-CTA form: each CTA of a pair stages 128 rows of each operand, the MMA is M = 256
         rc = make_tmap(&tmB, sg.c, cdt, sg.Dk, op->V, sg.ldc, BK, BN / 2);
         if (rc != CCE_OK) return rc;
@@ -749,6 +774,45 @@ int cce_b200_indexed_neg_dot(const cce_b200_operands* op, const int64_t* targets
             op->has_softcap, op->softcap, out);
     }
     CCE_LAUNCH_CHECK();
+    return CCE_OK;
+}
+
+size_t cce_b200_logit_avg_workspace_bytes(const cce_b200_operands* op) {
+    if (check_operands(op) != CCE_OK) return 0;
+    return align_up((size_t)(cdiv(std::max<long long>(op->n_rows, 1), kColsumRows) + 1) * op->D * sizeof(float), 256);
+}
+
+int cce_b200_logit_avg(const cce_b200_operands* op, float* out, void* workspace, size_t workspace_bytes,
+                       void* stream) {
+    int rc = check_operands(op);
+    if (rc != CCE_OK) return rc;
+    if (!out || !workspace) return CCE_ERR_ARG;
+    if (workspace_bytes < cce_b200_logit_avg_workspace_bytes(op)) return CCE_ERR_WORKSPACE;
+    cudaStream_t st = (cudaStream_t)stream;
+    const long long B = op->n_rows, D = op->D, V = op->V;
+    const int n_slices = int(cdiv(std::max<long long>(B, 1), kColsumRows));
+    float* partial = reinterpret_cast<float*>(workspace);
+    float* mean_e = partial + (size_t)n_slices * D;
+    const dim3 grid1((unsigned)cdiv(D, 256), (unsigned)n_slices);
+    const int vi64 = op->valids_dtype == CCE_IDX_I64;
+    const unsigned blocks3 = (unsigned)cdiv(V, 8);
+#define CCE_LOGIT_AVG(T)                                                                                       \
+    rows_colsum_partial_kernel<T><<<grid1, 256, 0, st>>>(reinterpret_cast<const T*>(op->e), op->lde, op->valids, \
+                                                         vi64, B, D, kColsumRows, partial);                    \
+    CCE_LAUNCH_CHECK();                                                                                        \
+    rows_colsum_finish_kernel<<<(unsigned)cdiv(D, 256), 256, 0, st>>>(partial, n_slices, D, B, mean_e);         \
+    CCE_LAUNCH_CHECK();                                                                                        \
+    logit_avg_kernel<T><<<blocks3, 256, 0, st>>>(mean_e, reinterpret_cast<const T*>(op->c), op->ldc, op->bias,  \
+                                                 op->bias_dtype, V, D, op->has_softcap, op->softcap, out);     \
+    CCE_LAUNCH_CHECK();
+    if (op->dtype == CCE_DT_F32) {
+        CCE_LOGIT_AVG(float)
+    } else if (op->dtype == CCE_DT_BF16) {
+        CCE_LOGIT_AVG(__nv_bfloat16)
+    } else {
+        CCE_LOGIT_AVG(__half)
+    }
+#undef CCE_LOGIT_AVG
     return CCE_OK;
 }
 
@@ -848,6 +912,29 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
     rc = stage_operands(op, pl.ops, ws, st, &sg);
     if (rc != CCE_OK) return rc;
 
+    // A vocabulary order (block-list form only): the products and the recomputation read a copy of the
+    // classifier (and bias) whose rows are in that order, labels are looked up through the inverse
+    // order, and dC rows are stored back at their own positions.
+    int* inv_order = nullptr;
+    float* tile_colmax = nullptr;
+    if (pl.sparse && pl.ordered) {
+        inv_order = reinterpret_cast<int*>(ws + pl.off_inv_order);
+        tile_colmax = reinterpret_cast<float*>(ws + pl.off_tile_colmax);
+        order_prepare_kernel<<<(unsigned)pl.n_vt, 256, 0, st>>>(a->vocab_order, V, a->col_max_key, inv_order, tile_colmax);
+        CCE_LAUNCH_CHECK();
+        pack_rows_kernel<<<(unsigned)V, 128, 0, st>>>(reinterpret_cast<const uint16_t*>(sg.c), sg.ldc, a->vocab_order, 0,
+                                                     reinterpret_cast<uint16_t*>(ws + pl.off_cperm), pl.Dkp, sg.Dk, V);
+        CCE_LAUNCH_CHECK();
+        sg.c = ws + pl.off_cperm;
+        sg.ldc = pl.Dkp;
+        if (sg.bias) {
+            float* bias_perm = reinterpret_cast<float*>(ws + pl.off_bias_perm);
+            gather_f32_kernel<<<(unsigned)cdiv(V, 256), 256, 0, st>>>(sg.bias, CCE_DT_F32, a->vocab_order, bias_perm, V);
+            CCE_LAUNCH_CHECK();
+            sg.bias = bias_perm;
+        }
+    }
+
     const bool use_flags = a->has_filter && ((a->filter_e && a->d_e) || (a->filter_c && a->d_c));
     int* status = reinterpret_cast<int*>(ws);
     char* g_buf = ws + pl.off_g;
@@ -906,6 +993,7 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
     pg.filter_eps = use_flags ? a->filter_eps : -1.0f;
     pg.g_out = g_buf;
     pg.g_is_bf16 = cdt == CCE_DT_BF16;
+    pg.inv_order = inv_order;
 
     if (pl.sparse) {
         // ---- index of the tiles worth recomputing
@@ -927,10 +1015,19 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
         CCE_CUDA(cudaMemsetAsync(act, 0, (size_t)pl.n_rb * pl.n_vt, st));
         rowgroup_min_lse_kernel<<<(unsigned)cdiv(n_groups, 8), 256, 0, st>>>(a->lse, B, minlse, n_groups);
         CCE_LAUNCH_CHECK();
-        const long long n_thr = std::max<long long>(B, (long long)n_groups * pl.n_vt);
-        tile_mark_kernel<<<(unsigned)cdiv(n_thr, 256), 256, 0, st>>>(
-            a->tile_max, minlse, n_groups, pl.n_vt, log2f(a->filter_eps), reinterpret_cast<const long long*>(a->targets),
-            op->valids, op->valids_dtype == CCE_IDX_I64, a->shift, a->vocab_start, V, B, act);
+        if (inv_order) {
+            const long long n_thr = std::max<long long>(B, (long long)n_groups * pl.n_vt * 32);
+            tile_mark_ordered_kernel<<<(unsigned)cdiv(n_thr, 256), 256, 0, st>>>(
+                a->tile_max, minlse, tile_colmax, a->vocab_order, inv_order, n_groups, pl.n_vt, log2f(a->filter_eps),
+                reinterpret_cast<const long long*>(a->targets), op->valids, op->valids_dtype == CCE_IDX_I64, a->shift,
+                a->vocab_start, V, B, act);
+        } else {
+            const long long n_thr = std::max<long long>(B, (long long)n_groups * pl.n_vt);
+            tile_mark_kernel<<<(unsigned)cdiv(n_thr, 256), 256, 0, st>>>(
+                a->tile_max, minlse, n_groups, pl.n_vt, log2f(a->filter_eps),
+                reinterpret_cast<const long long*>(a->targets), op->valids, op->valids_dtype == CCE_IDX_I64, a->shift,
+                a->vocab_start, V, B, act);
+        }
         CCE_LAUNCH_CHECK();
         const size_t sm_bytes = (size_t)(pl.n_rb + pl.n_vt + 2) * sizeof(int);
         int* tile_counts = nullptr;
@@ -982,6 +1079,7 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
                 p.klist = dc_list;
                 p.kcount = dc_cnt;
                 p.a_tma3 = p_is3;
+                p.row_map = inv_order ? a->vocab_order : nullptr;
                 rc = run_dc(p, tmP_mn);
                 if (rc != CCE_OK) return rc;
             }

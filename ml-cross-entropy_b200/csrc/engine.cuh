@@ -69,6 +69,9 @@ struct EngineParams {
     int band_len;       // vocabulary tiles per work item (MODE_LSE)
     float2* partial;    // [n_band][M]  (running max in log2 units, sum)
     float* tile_max;    // null or [n_mblk*4][n_nblk]: max logit (log2 units) of each 32-row x 256-col block
+    // null or [N]: running maximum over all rows of each column's logit (log2 units), kept as an
+    // order-preserving integer key (float_to_key) so that it can be raised with an integer atomic max
+    int* col_max_key;
     // ---- block-list ("sparse") forms of the backward, used when every product is filtered:
     // only tiles that can hold a value >= eps are recomputed, each into its own slot of a pool
     // of 128x256 tiles, and the two products walk per-row / per-column lists of those slots.
@@ -96,6 +99,9 @@ struct EngineParams {
     int valids_i64;
     long long shift;
     long long vocab_start;
+    // null, or [V]: position of every (local) vocabulary index in the reordered classifier this
+    // launch reads; a row's label is looked up through it
+    const int* inv_order;
     const float* d_out;  // 1 element or indexed at (row + shift)
     int d_out_scalar;
     const float* d_lse;  // null or indexed at (row + shift)
@@ -111,11 +117,24 @@ struct EngineParams {
     // ---- MODE_GEMM
     void* out;
     long long ldo;
+    const int* row_map;  // null, or [M]: output row of accumulator row r (dC of a reordered classifier)
     int out_dtype;   // CCE_DT_*
     int accumulate;  // fp32 out only: 0 store, 1 read-add-store, 2 vector red.add (out pre-zeroed)
     const uint8_t* kflags;  // null or [n_mblk][ld_kflags]
     int ld_kflags;
 };
+
+// Order-preserving map from float to int32 (and back): a < b  <=>  key(a) < key(b).
+__host__ __device__ __forceinline__ int float_to_key(float f) {
+#ifdef __CUDA_ARCH__
+    const int b = __float_as_int(f);
+#else
+    int b;
+    memcpy(&b, &f, 4);
+#endif
+    return b >= 0 ? b : (b ^ 0x7fffffff);
+}
+__device__ __forceinline__ float key_to_float(int k) { return __int_as_float(k >= 0 ? k : (k ^ 0x7fffffff)); }
 
 struct EngineSmem {
     uint8_t* stages;
@@ -612,6 +631,7 @@ __device__ void epilogue_loop(const EngineParams& p, const EngineSmem& s, uint32
                 const long long ti = src + p.shift;
                 const long long t = p.targets[ti] - p.vocab_start;
                 row_t = (t >= 0 && t < 0x7fffffffLL) ? int(t) : -1;
+                if (p.inv_order) row_t = (row_t >= 0 && row_t < p.N) ? p.inv_order[row_t] : -1;
                 row_l2 = p.lse[row] * kLog2e;
                 row_g = p.grad_scale * (p.d_out_scalar ? p.d_out[0] : p.d_out[ti]);
                 row_dl = p.d_lse ? p.d_lse[ti] : 0.0f;
@@ -642,6 +662,7 @@ __device__ void epilogue_loop(const EngineParams& p, const EngineSmem& s, uint32
         } else if constexpr (MODE == MODE_GEMM) {
             // Store-only epilogue: two 32-column loads from TMEM are in flight per wait, so half of
             // the load latency is exposed compared with one load per wait.
+            const int orow = (row_ok && p.row_map) ? p.row_map[row] : row;
 #pragma unroll 1
             for (int c = 0; c < BN / 32; c += 2) {
                 const int col0 = it.nblk * BN + c * 32;
@@ -656,8 +677,8 @@ __device__ void epilogue_loop(const EngineParams& p, const EngineSmem& s, uint32
                     for (int j = 0; j < 32; ++j) r0[j] = r1[j] = 0u;
                 }
                 if (row_ok) {
-                    gemm_store_chunk(p, row, col0, r0);
-                    if (col0 + 32 < p.N) gemm_store_chunk(p, row, col0 + 32, r1);
+                    gemm_store_chunk(p, orow, col0, r0);
+                    if (col0 + 32 < p.N) gemm_store_chunk(p, orow, col0 + 32, r1);
                 }
             }
         } else {
@@ -700,6 +721,26 @@ __device__ void epilogue_loop(const EngineParams& p, const EngineSmem& s, uint32
                         cmax = fmaxf(cmax, x[j]);
                     }
                     tile_rowmax = fmaxf(tile_rowmax, cmax);
+                    if (p.col_max_key) {
+                        // column maxima over this warp's 32 rows: a butterfly that halves the live
+                        // values at every step (31 shuffles); lane l ends up with column col0 + l
+                        float v[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = row_ok ? x[j] : -INFINITY;
+#pragma unroll
+                        for (int o = 16; o >= 1; o >>= 1) {
+                            const bool up = (lane & o) != 0;
+#pragma unroll
+                            for (int j = 0; j < o; ++j) {
+                                const float keep = up ? v[j + o] : v[j];
+                                const float send = up ? v[j] : v[j + o];
+                                v[j] = fmaxf(keep, __shfl_xor_sync(0xffffffffu, send, o));
+                            }
+                        }
+                        // one coalesced 128-byte atomic request per warp and chunk; max is order
+                        // independent, so the result is the same every run
+                        if (col0 + lane < p.N) atomicMax(p.col_max_key + p.col_off + col0 + lane, float_to_key(v[0]));
+                    }
                     if (cmax > run_m) {
                         run_s *= ex2f(run_m - cmax);  // run_m = -inf gives 0
                         run_m = cmax;

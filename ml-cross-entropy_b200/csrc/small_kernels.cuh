@@ -1,7 +1,7 @@
 // Bandwidth-bound helper kernels around the tensor-core pipeline: row gather/pad,
 // correct-token gather-dot, log-sum-exp merge, column sums and the final cast/scatter.
 #pragma once
-#include "ptx.cuh"
+#include "engine.cuh"
 
 namespace cce {
 
@@ -164,6 +164,137 @@ __global__ void tile_mark_kernel(const float* __restrict__ tile_max, const float
     if (i < (long long)n_groups * n_vt) {
         const int g = int(i / n_vt), vt = int(i % n_vt);
         if (tile_max[i] - min_lse2[g] >= log2_eps) act[(size_t)(g >> 2) * n_vt + vt] = 1;
+    }
+}
+
+// ---- vocabulary ordering (the classifier rows are visited in a caller-given order, so that the
+// columns that hold large probabilities share few tiles)
+// One block per 256 positions of the order: inv_order[order[i]] = i, and tile_colmax[T] = the largest
+// column maximum (log2 units) among the 256 columns that make up reordered tile T.
+__global__ void __launch_bounds__(256)
+order_prepare_kernel(const int* __restrict__ order, long long V, const int* __restrict__ col_max_key,
+                     int* __restrict__ inv_order, float* __restrict__ tile_colmax) {
+    __shared__ int warp_max[8];
+    const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+    int k = INT_MIN;
+    if (i < V) {
+        const int o = order[i];
+        inv_order[o] = int(i);
+        k = col_max_key[o];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) k = max(k, __shfl_xor_sync(0xffffffffu, k, o));
+    if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = k;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int m = warp_max[0];
+#pragma unroll
+        for (int w = 1; w < 8; ++w) m = max(m, warp_max[w]);
+        tile_colmax[blockIdx.x] = key_to_float(m);
+    }
+}
+
+// dst[i] = float(src[order[i]])
+__global__ void gather_f32_kernel(const void* __restrict__ src, int dtype, const int* __restrict__ order,
+                                  float* __restrict__ dst, long long n) {
+    const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    if (i < n) dst[i] = load_as_float(src, dtype, order[i]);
+}
+
+// tile_mark_kernel for a reordered vocabulary.  Reordered tile T (columns order[256 T .. 256 T + 255])
+// can hold a value >= eps for 32-row group g only if BOTH upper bounds of its softmax values allow it:
+//   tile_colmax[T] - min_lse[g]                                   (column maxima over all rows)
+//   max_j tile_max[g][order[256 T + j] / 256] - min_lse[g]        (the forward's per-tile maxima)
+// One warp per (g, T) pair evaluates the second bound only where the first one passes.  Thread i < n_rows
+// also marks the tile that holds row i's label (its position in the order comes from inv_order).
+__global__ void tile_mark_ordered_kernel(const float* __restrict__ tile_max, const float* __restrict__ min_lse2,
+                                         const float* __restrict__ tile_colmax, const int* __restrict__ order,
+                                         const int* __restrict__ inv_order, int n_groups, int n_vt, float log2_eps,
+                                         const long long* __restrict__ targets, const void* __restrict__ valids,
+                                         int valids_i64, long long shift, long long vocab_start, long long V,
+                                         long long n_rows, uint8_t* __restrict__ act) {
+    const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    if (i < n_rows) {
+        const long long r = valids ? load_index(valids, valids_i64, i) : i;
+        const long long t = targets[r + shift] - vocab_start;
+        if (t >= 0 && t < V) act[(i >> 7) * n_vt + (inv_order[t] >> 8)] = 1;
+    }
+    const long long w = i >> 5;
+    const int lane = threadIdx.x & 31;
+    if (w < (long long)n_groups * n_vt) {
+        const int g = int(w / n_vt), T = int(w % n_vt);
+        const float floor2 = min_lse2[g] + log2_eps;
+        if (tile_colmax[T] >= floor2) {  // warp-uniform
+            float m = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const long long pos = (long long)T * 256 + j * 32 + lane;
+                if (pos < V) m = fmaxf(m, tile_max[(size_t)g * n_vt + (order[pos] >> 8)]);
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+            if (lane == 0 && m >= floor2) act[(size_t)(g >> 2) * n_vt + T] = 1;
+        }
+    }
+}
+
+// ---- mean logit per vocabulary entry (the reference's ordering key, cce_lse_forward.py:95-97):
+// logit_avg[v] = softcap(mean_rows(e) . c[v] + bias[v]).  Without soft-capping that is the mean of
+// the logits of column v; with it, the soft-cap of the mean (monotone in it, hence the same order).
+// Stage 1: partial[slice][d] = sum of the listed rows [slice * rows_per_block, ...) of column d.
+template <typename T>
+__global__ void rows_colsum_partial_kernel(const T* __restrict__ e, long long lde, const void* __restrict__ valids,
+                                           int valids_i64, long long n_rows, long long D, int rows_per_block,
+                                           float* __restrict__ partial) {
+    const long long d = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (d >= D) return;
+    const long long r0 = (long long)blockIdx.y * rows_per_block;
+    const long long r1 = min(n_rows, r0 + rows_per_block);
+    float s = 0.0f;
+    for (long long i = r0; i < r1; ++i) {
+        const long long r = valids ? load_index(valids, valids_i64, i) : i;
+        s += float(e[r * lde + d]);
+    }
+    partial[(size_t)blockIdx.y * D + d] = s;
+}
+// Stage 2: mean_e[d] = (sum over the slices, ascending) / n_rows
+__global__ void rows_colsum_finish_kernel(const float* __restrict__ partial, int n_slices, long long D,
+                                          long long n_rows, float* __restrict__ mean_e) {
+    const long long d = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (d >= D) return;
+    float s = 0.0f;
+    for (int k = 0; k < n_slices; ++k) s += partial[(size_t)k * D + d];
+    mean_e[d] = s / float(n_rows > 0 ? n_rows : 1);
+}
+// Stage 3: one warp per vocabulary entry
+template <typename T>
+__global__ void logit_avg_kernel(const float* __restrict__ mean_e, const T* __restrict__ c, long long ldc,
+                                 const void* __restrict__ bias, int bias_dtype, long long V, long long D,
+                                 int has_softcap, float softcap, float* __restrict__ out) {
+    const long long v = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (v >= V) return;
+    const T* cp = c + v * ldc;
+    float acc = 0.0f;
+    constexpr int VE = 16 / int(sizeof(T));
+    const bool vec = (D % VE == 0) && ((reinterpret_cast<uintptr_t>(cp) & 15) == 0);
+    if (vec) {
+        const uint4* c4 = reinterpret_cast<const uint4*>(cp);
+        for (long long j = lane; j < D / VE; j += 32) {
+            const uint4 b = __ldg(c4 + j);
+            const T* bh = reinterpret_cast<const T*>(&b);
+#pragma unroll
+            for (int k = 0; k < VE; ++k) acc = fmaf(__ldg(mean_e + j * VE + k), float(bh[k]), acc);
+        }
+    } else {
+        for (long long j = lane; j < D; j += 32) acc = fmaf(mean_e[j], float(cp[j]), acc);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) {
+        if (bias) acc += load_as_float(bias, bias_dtype, v);
+        if (has_softcap) acc = softcap * tanhf(acc / softcap);
+        out[v] = acc;
     }
 }
 

@@ -25,6 +25,9 @@ EXPORTS = (
     "cce_b200_lse_workspace_bytes",
     "cce_b200_lse_forward",
     "cce_b200_tile_max_elems",
+    "cce_b200_lse_forward_ex",
+    "cce_b200_logit_avg_workspace_bytes",
+    "cce_b200_logit_avg",
     "cce_b200_lse_forward_static",
     "cce_b200_indexed_neg_dot",
     "cce_b200_loss_tail",
@@ -88,6 +91,8 @@ class BackwardArgs(Structure):
         ("d_c", c_void_p),
         ("d_bias", c_void_p),
         ("tile_max", c_void_p),
+        ("vocab_order", c_void_p),
+        ("col_max_key", c_void_p),
     ]
 
 
@@ -114,6 +119,12 @@ def lib() -> ctypes.CDLL:
     L.cce_b200_lse_workspace_bytes.argtypes = [POINTER(Operands)]
     L.cce_b200_lse_forward.restype = c_int32
     L.cce_b200_lse_forward.argtypes = [POINTER(Operands), c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]
+    L.cce_b200_lse_forward_ex.restype = c_int32
+    L.cce_b200_lse_forward_ex.argtypes = [POINTER(Operands), c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]
+    L.cce_b200_logit_avg_workspace_bytes.restype = c_size_t
+    L.cce_b200_logit_avg_workspace_bytes.argtypes = [POINTER(Operands)]
+    L.cce_b200_logit_avg.restype = c_int32
+    L.cce_b200_logit_avg.argtypes = [POINTER(Operands), c_void_p, c_void_p, c_size_t, c_void_p]
     L.cce_b200_tile_max_elems.restype = c_size_t
     L.cce_b200_tile_max_elems.argtypes = [POINTER(Operands)]
     L.cce_b200_lse_forward_static.restype = c_int32

@@ -7,6 +7,7 @@ launchers it calls are this package's C-ABI wrappers.
 
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import cast
 
@@ -20,6 +21,37 @@ from .constants import IGNORE_INDEX
 from .indexed_dot import indexed_neg_dot_forward_kernel
 from .utils import PendingValidRows, TensorInfo, _handle_eps, launch_flat_valids
 from .vocab_parallel.utils import VocabParallelOptions, vp_gather_stats
+
+
+# Vocabulary ordering of the filtered backward (reference cce.py:43-45,171-174): "off" = tiles are
+# formed in natural vocabulary order; "max" = sorted by each entry's largest logit over the batch
+# (the quantity this backend's tile bound uses); "mean" = sorted by the mean logit, the reference's
+# key.  It pays when the entries with large probabilities are scattered over the vocabulary; it
+# costs a reordered copy of the classifier per backward, so it is off unless asked for
+# (set_vocab_ordering, or CCE_B200_VOCAB_ORDER in the environment).
+_VOCAB_ORDERING = os.environ.get("CCE_B200_VOCAB_ORDER", "off").lower()
+if _VOCAB_ORDERING in ("", "0", "false"):
+    _VOCAB_ORDERING = "off"
+elif _VOCAB_ORDERING in ("1", "true", "on"):
+    _VOCAB_ORDERING = "max"
+
+
+def set_vocab_ordering(mode: bool | str) -> str:
+    """Choose how the filtered backward orders the vocabulary (``"off"``, ``"max"``, ``"mean"``;
+    ``True`` = ``"max"``, ``False`` = ``"off"``).  Returns the previous setting."""
+    global _VOCAB_ORDERING
+    if isinstance(mode, bool):
+        mode = "max" if mode else "off"
+    if mode not in ("off", "max", "mean"):
+        raise ValueError(f"unknown vocabulary ordering {mode!r}")
+    prev, _VOCAB_ORDERING = _VOCAB_ORDERING, mode
+    return prev
+
+
+def sort_logit_avg(logit_avg: torch.Tensor) -> torch.Tensor:
+    """Vocabulary order from a per-entry key, hottest entries first (reference cce.py:43-45; there
+    ascending, which clusters the same entries at the other end)."""
+    return torch.argsort(logit_avg, descending=True).to(torch.int32)
 
 
 @dataclass
@@ -78,6 +110,8 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
             and (params.filter_c_grad or not c_info.requires_grad)
             and not (bias_info is not None and bias_info.requires_grad)
         )
+        # a vocabulary order only matters to the block-list backward, which is what tile_max is for
+        order_mode = _VOCAB_ORDERING if want_tile_max else "off"
         if params.reduction not in ("mean", "sum", "none"):
             raise ValueError(f"Unknown reduction {params.reduction}")
         # (lse, -correct logit) of the valid rows sit side by side in one buffer, sized for every row
@@ -93,10 +127,17 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
             softcap=params.softcap,
             return_tile_max=want_tile_max,
             stats_flat=stats_flat,
+            return_logit_avg=order_mode == "mean",
+            return_col_max=order_mode != "off",
         )
         if pending is not None:
             params.valids = pending.resolve()
-        lse, tile_max = ret if want_tile_max else (ret, None)
+        ret = list(ret) if isinstance(ret, tuple) else [ret]
+        lse = ret.pop(0)
+        logit_avg = ret.pop(0) if order_mode == "mean" else None
+        tile_max = ret.pop(0) if want_tile_max else None
+        col_max = ret.pop(0) if order_mode != "off" else None
+        order_key = logit_avg if order_mode == "mean" else col_max
         assert isinstance(lse, torch.Tensor)
         n_rows = lse.numel()
         stats = stats_flat[: 2 * n_rows].view(1, 2, n_rows)
@@ -134,7 +175,7 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
         else:
             lse = stats[0, 0]
 
-        ctx.save_for_backward(e, c, bias, lse, params.targets, params.valids, tile_max)
+        ctx.save_for_backward(e, c, bias, lse, params.targets, params.valids, tile_max, col_max, order_key)
         ctx.params = params
         ctx.e_info, ctx.c_info, ctx.bias_info = e_info, c_info, bias_info
         return loss, lse_out
@@ -144,7 +185,9 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
     def backward(
         ctx, grad_out: torch.Tensor, grad_lse_out: torch.Tensor | None
     ) -> tuple[torch.Tensor | None, torch.Tensor | None, torch.Tensor | None, None]:
-        e, c, bias, lse, targets, valids, tile_max = ctx.saved_tensors
+        e, c, bias, lse, targets, valids, tile_max, col_max, order_key = ctx.saved_tensors
+        # integer keys (column maxima) and float keys (mean logits) both sort with the hottest entry first
+        vocab_ordering = sort_logit_avg(order_key) if order_key is not None else None
         params = cast(CCEParams, ctx.params)
 
         if params.reduction == "mean":
@@ -174,7 +217,7 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
             filter_eps=params.filter_eps,
             targets=targets,
             shift=params.shift,
-            vocab_ordering=None,
+            vocab_ordering=vocab_ordering,
             grad_scale=grad_scale,
             accum_e_fp32=params.accum_e_fp32,
             accum_c_fp32=params.accum_c_fp32,
@@ -184,6 +227,7 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
             pg=vp.group if vp is not None else None,
             vocab_start=vp.start if vp is not None else 0,
             tile_max=tile_max,
+            col_max=col_max,
         )
         return de, dc, dbias, None
 

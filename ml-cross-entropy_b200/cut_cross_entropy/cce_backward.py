@@ -17,7 +17,7 @@ from .vocab_parallel.utils import vp_reduce_e_grad_
 
 
 def _launch(do, dlse, e, c, bias, lse, valids, softcap, filter_eps, targets, shift, grad_scale,
-            filter_e, filter_c, vocab_start, de, dc, dbias, tile_max=None) -> None:
+            filter_e, filter_c, vocab_start, de, dc, dbias, tile_max=None, vocab_ordering=None, col_max=None) -> None:
     """Fill the (pre-allocated, possibly ``None``) outputs ``de``/``dc``/``dbias`` through the C ABI."""
     dev = e.device
     a = _native.BackwardArgs()
@@ -39,6 +39,9 @@ def _launch(do, dlse, e, c, bias, lse, valids, softcap, filter_eps, targets, shi
     a.d_c = _native._ptr(dc)
     a.d_bias = _native._ptr(dbias)
     a.tile_max = _native._ptr(tile_max)
+    if vocab_ordering is not None and col_max is not None and tile_max is not None:
+        a.vocab_order = vocab_ordering.data_ptr()
+        a.col_max_key = col_max.data_ptr()
     L = _native.lib()
     ws = _native.workspace(L.cce_b200_backward_workspace_bytes(a), dev)
     with torch.cuda.device(dev):
@@ -72,6 +75,7 @@ def cce_backward_kernel(
     pg: "torch.distributed.ProcessGroup | None" = None,
     vocab_start: int = 0,
     tile_max: torch.Tensor | None = None,
+    col_max: torch.Tensor | None = None,
 ) -> tuple[torch.Tensor | None, torch.Tensor | None, torch.Tensor | None]:
     """Returns ``(de, dc, dbias)``, each ``None`` unless its ``*_info.requires_grad``.
 
@@ -79,10 +83,14 @@ def cce_backward_kernel(
     ``targets`` and read at the label position), ``dlse`` the upstream gradient of
     the returned log-sum-exp (or ``None``).  ``targets`` holds global labels;
     ``vocab_start`` is the first label this rank's ``c`` covers.  ``vocab_ordering``
-    and the ``accum_*_fp32`` switches are accepted and ignored: blocks are filtered
-    in natural vocabulary order and every accumulation is fp32.  With
+    (int32 permutation of the local vocabulary, reference ``cce_backward.py:154-155``) makes
+    the backward form its tiles from consecutive entries of that order; it takes effect when
+    the block-list backward runs (both products filtered, ``tile_max`` and ``col_max`` given,
+    no bias gradient) and is ignored otherwise.  The ``accum_*_fp32`` switches are accepted
+    and ignored: every accumulation is fp32.  With
     ``reduce_e_grad`` the fp32 partial ``de`` is summed over ``pg`` before the cast.
-    ``tile_max`` is the optional by-product of ``cce_lse_forward_kernel(return_tile_max=True)``.
+    ``tile_max`` / ``col_max`` are the optional by-products of
+    ``cce_lse_forward_kernel(return_tile_max=True, return_col_max=True)``.
     """
     assert targets is not None
     assert do.numel() in (e.size(0), 1)
@@ -107,6 +115,9 @@ def cce_backward_kernel(
         bias = bias.contiguous()
     if valids is not None:
         valids = valids.contiguous()
+    if vocab_ordering is not None:
+        assert vocab_ordering.ndim == 1 and vocab_ordering.numel() == c.size(0)
+        vocab_ordering = vocab_ordering.to(torch.int32).contiguous()
 
     want_de = e_info.requires_grad
     want_dc = c_info.requires_grad
@@ -119,7 +130,8 @@ def cce_backward_kernel(
 
     if want_de or want_dc or want_dbias:
         _launch(do, dlse, e, c, bias, lse, valids, softcap, filter_eps, targets, int(shift), float(grad_scale),
-                bool(filter_e_grad), bool(filter_c_grad), int(vocab_start), de, dc, dbias, tile_max)
+                bool(filter_e_grad), bool(filter_c_grad), int(vocab_start), de, dc, dbias, tile_max,
+                vocab_ordering, col_max)
 
     if de_f32:
         assert de is not None

@@ -22,13 +22,15 @@ def cce_lse_forward_kernel(
     return_logit_avg: bool = False,
     return_tile_max: bool = False,
     stats_flat: torch.Tensor | None = None,
-) -> tuple[torch.Tensor, torch.Tensor | None] | torch.Tensor:
+    return_col_max: bool = False,
+) -> tuple[torch.Tensor, ...] | torch.Tensor:
     """``lse[i] = logsumexp_v(softcap(e[valids[i]] @ c[v] + bias[v]))`` as float32 ``[B]``.
 
-    ``return_logit_avg`` exists for call compatibility.  The reference uses the
-    per-column mean logit only to reorder the vocabulary before filtering
-    (``cce.py:171-174``); this backend filters in natural vocabulary order, so the
-    second return value is always ``None``.
+    ``return_logit_avg`` also returns the reference's vocabulary-ordering key (its
+    ``cce_lse_forward.py:95-97``), float32 ``[V]``: the mean over the valid rows of each column's
+    logit, computed as ``softcap(mean(e) @ c.T + bias)`` by ``cce_b200_logit_avg`` (with
+    soft-capping that is the cap of the mean rather than the mean of the capped values: the same
+    ordering).
 
     ``valids`` may be a :class:`~cut_cross_entropy.utils.PendingValidRows` (a row list the GPU is
     still writing): buffers are then sized for all rows and the operand description is prepared
@@ -41,6 +43,10 @@ def cce_lse_forward_kernel(
     ``return_tile_max`` asks for this backend's own by-product instead: the largest logit (in
     log2 units) of every (32-row group, 256-column tile) block, which lets the filtered
     backward skip recomputing tiles that cannot hold a value above the filter threshold.
+    ``return_col_max`` adds the largest logit of every vocabulary entry over all rows (int32 keys
+    ``[V]``, see ``cce_b200_lse_forward_ex``), which a backward with a vocabulary order needs.
+
+    Returns ``lse`` alone, or a tuple ``(lse[, logit_avg][, tile_max][, col_max])`` of what was asked for.
     """
     assert e.shape[1] == c.shape[1], "Incompatible dimensions"
     assert e.is_contiguous(), "Matrix A must be contiguous"
@@ -78,14 +84,18 @@ def cce_lse_forward_kernel(
         need = L.cce_b200_lse_workspace_bytes(op)  # not monotonic in n_rows (the band split changes)
         if need > ws.numel():
             ws = _native.workspace(need, e.device)
+    col_max = torch.empty((op.V,), dtype=torch.int32, device=e.device) if return_col_max else None
     with torch.cuda.device(e.device):
-        rc = L.cce_b200_lse_forward(
-            op, lse.data_ptr(), _native._ptr(tile_max), ws.data_ptr(), ws.numel(), stream
+        rc = L.cce_b200_lse_forward_ex(
+            op, lse.data_ptr(), _native._ptr(tile_max), _native._ptr(col_max), ws.data_ptr(), ws.numel(), stream
         )
-    _native.check(rc, "cce_b200_lse_forward")
+        _native.check(rc, "cce_b200_lse_forward")
+        logit_avg = None
+        if return_logit_avg:
+            logit_avg = torch.empty((op.V,), dtype=torch.float32, device=e.device)
+            ws2 = _native.workspace(L.cce_b200_logit_avg_workspace_bytes(op), e.device)
+            rc = L.cce_b200_logit_avg(op, logit_avg.data_ptr(), ws2.data_ptr(), ws2.numel(), stream)
+            _native.check(rc, "cce_b200_logit_avg")
     _native.finish(ws, "cce_b200_lse_forward")
-    if return_tile_max:
-        return lse, tile_max
-    if return_logit_avg:
-        return lse, None
-    return lse
+    extras = [x for x, want in ((logit_avg, return_logit_avg), (tile_max, return_tile_max), (col_max, return_col_max)) if want]
+    return (lse, *extras) if extras else lse

@@ -63,8 +63,8 @@ def _install_cpu_stand_ins():
     import cut_cross_entropy.cce_backward as bwd_mod
 
     def lse_kernel(e, c, bias=None, valids=None, softcap=None, return_logit_avg=False, return_tile_max=False,
-                   stats_flat=None):
-        assert not return_tile_max
+                   stats_flat=None, return_col_max=False):
+        assert not return_tile_max and not return_col_max and not return_logit_avg
         return O.lse_forward(e, c, bias, valids, softcap).float()
 
     def dot_kernel(e, c, inds, bias=None, shift=0, valids=None, softcap=None, out_dtype=None, vocab_start=0,
@@ -88,7 +88,7 @@ def _install_cpu_stand_ins():
         return loss, (scatter(lse) if return_lse else None), (lse if want_lse_rows else None)
 
     def launch(do, dlse, e, c, bias, lse, valids, softcap, filter_eps, targets, shift, grad_scale,
-               filter_e, filter_c, vocab_start, de, dc, dbias, tile_max=None):
+               filter_e, filter_c, vocab_start, de, dc, dbias, tile_max=None, vocab_ordering=None, col_max=None):
         # restates one rank of cce_backward.py:182-310 with the global lse
         n = e.size(0)
         rows = torch.arange(n) if valids is None else valids.long()
