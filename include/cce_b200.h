@@ -74,6 +74,12 @@ typedef struct cce_b200_operands {
     int32_t valids_dtype; /* CCE_IDX_* */
     int32_t has_softcap;  /* 0/1 */
     float softcap;
+    /* Optional: the number of rows that enter the loss, kept on the DEVICE (one int64, for instance
+     * the count_out of cce_b200_valid_rows in device memory) by a caller that does not want to read
+     * it back.  When set, `valids` must be given, n_rows is only an upper bound of the count (buffers
+     * and launches are sized for it; n_total is always one) and every kernel takes the real count
+     * from here: outputs are written for the first *n_rows_dev rows only.  NULL: n_rows is the count. */
+    const int64_t* n_rows_dev;
 } cce_b200_operands;
 
 /* lse[i] = log sum_v exp(softcap(e[row_i] . c[v] + bias[v])), i < n_rows.
@@ -155,11 +161,13 @@ int cce_b200_indexed_neg_dot(const cce_b200_operands* op, const int64_t* targets
  *   takes); lse_scatter (optional, [n_total]) receives lse_i at the same positions as the loss, 0 elsewhere.
  *   status_workspace (optional): the workspace of the cce_b200_lse_forward call that produced the
  *   statistics; if its status word is non-zero (a kernel abandoned a wait) every output is NaN.
+ *   n_rows_dev (optional): the row count on the device, as in cce_b200_operands; n_rows is then the
+ *   upper bound the statistics block is laid out for, and `rows` must be given.
  * Replaces, in cut_cross_entropy/cce.py:139-160 and utils.py:52-61, the element-wise add, the
  * mean/sum and the index-put of handle_reduction_none, and vocab_parallel/utils.py:47-65's merges. */
 int cce_b200_loss_tail(const float* stats, int32_t world, int64_t n_rows, const void* rows, int32_t rows_dtype,
                        int64_t shift, int64_t n_total, int32_t reduction, float* lse_rows, float* loss_out,
-                       float* lse_scatter, const void* status_workspace, void* stream);
+                       float* lse_scatter, const void* status_workspace, const int64_t* n_rows_dev, void* stream);
 
 /* The rows of the flattened embedding matrix that enter the loss, in ascending order:
  * row r (0 <= r < n_total) is paired with label targets[r + shift] and is listed when that label
@@ -189,6 +197,8 @@ typedef struct cce_b200_backward_args {
     int64_t d_out_numel;     /* 1 or n_total */
     const float* d_lse;      /* upstream gradient of the returned lse, [n_total] indexed at row_i + shift, or NULL */
     float grad_scale;        /* 1/n_rows for reduction=mean, else 1 */
+    int32_t grad_scale_by_inv_rows; /* 1: multiply grad_scale by 1/(row count) on the device (reduction=mean
+                                        when the count lives in op.n_rows_dev); 0 otherwise */
     int32_t has_filter;      /* 0: exact gradient; 1: skip tiles whose |softmax - onehot| < filter_eps everywhere */
     float filter_eps;
     int32_t filter_e;        /* apply the filter to the dE product */

@@ -202,6 +202,7 @@ int check_operands(const cce_b200_operands* op) {
     if (op->lde < op->D || op->ldc < op->D) return CCE_ERR_ARG;
     if (op->n_total >= (1LL << 31) - 256 || op->V >= (1LL << 31) - 256 || op->D >= (1LL << 30)) return CCE_ERR_ARG;
     if (op->has_softcap && !(op->softcap > 0.0f)) return CCE_ERR_ARG;
+    if (op->n_rows_dev && !op->valids) return CCE_ERR_ARG;  // a count on the device comes with its row list
     return CCE_OK;
 }
 
@@ -222,7 +223,7 @@ OperandPlan plan_operands(const cce_b200_operands* op, size_t start) {
     OperandPlan pl;
     pl.Dp = (op->D + 7) / 8 * 8;
     const bool d_ok = (op->D % 8 == 0);
-    pl.pack_e = op->valids || !d_ok || (op->lde % 8) || (reinterpret_cast<uintptr_t>(op->e) & 15);
+    pl.pack_e = op->valids || op->n_rows_dev || !d_ok || (op->lde % 8) || (reinterpret_cast<uintptr_t>(op->e) & 15);
     pl.pad_c = !d_ok || (op->ldc % 8) || (reinterpret_cast<uintptr_t>(op->c) & 15);
     pl.bias32 = op->bias && op->bias_dtype != CCE_DT_F32;
     pl.split = is_split(op);
@@ -251,6 +252,7 @@ struct Staged {
 };
 
 int stage_operands(const cce_b200_operands* op, const OperandPlan& pl, char* ws, cudaStream_t st, Staged* out) {
+    const long long* ndev = reinterpret_cast<const long long*>(op->n_rows_dev);
     out->Dk = out->Dmn = op->D;
     out->blk = 0;
     if (pl.split) {
@@ -259,12 +261,12 @@ int stage_operands(const cce_b200_operands* op, const OperandPlan& pl, char* ws,
         if (op->n_rows > 0) {
             split_rows_kernel<<<(unsigned)op->n_rows, 128, 0, st>>>(
                 reinterpret_cast<const float*>(op->e), op->lde, op->valids, op->valids_dtype == CCE_IDX_I64,
-                reinterpret_cast<__nv_bfloat16*>(ws + pl.off_e), pl.Dp, op->D, op->n_rows, 0);
+                reinterpret_cast<__nv_bfloat16*>(ws + pl.off_e), pl.Dp, op->D, op->n_rows, 0, ndev);
             CCE_LAUNCH_CHECK();
         }
         split_rows_kernel<<<(unsigned)op->V, 128, 0, st>>>(reinterpret_cast<const float*>(op->c), op->ldc, nullptr, 0,
                                                           reinterpret_cast<__nv_bfloat16*>(ws + pl.off_c), pl.Dp,
-                                                          op->D, op->V, 1);
+                                                          op->D, op->V, 1, nullptr);
         CCE_LAUNCH_CHECK();
         out->e = ws + pl.off_e;
         out->c = ws + pl.off_c;
@@ -273,7 +275,7 @@ int stage_operands(const cce_b200_operands* op, const OperandPlan& pl, char* ws,
         if (op->n_rows > 0) {
             pack_rows_kernel<<<(unsigned)op->n_rows, 128, 0, st>>>(
                 reinterpret_cast<const uint16_t*>(op->e), op->lde, op->valids, op->valids_dtype == CCE_IDX_I64,
-                reinterpret_cast<uint16_t*>(ws + pl.off_e), pl.Dp, op->D, op->n_rows);
+                reinterpret_cast<uint16_t*>(ws + pl.off_e), pl.Dp, op->D, op->n_rows, ndev);
             CCE_LAUNCH_CHECK();
         }
         out->e = ws + pl.off_e;
@@ -287,7 +289,7 @@ int stage_operands(const cce_b200_operands* op, const OperandPlan& pl, char* ws,
     } else if (pl.pad_c) {
         pack_rows_kernel<<<(unsigned)op->V, 128, 0, st>>>(reinterpret_cast<const uint16_t*>(op->c), op->ldc, nullptr, 0,
                                                          reinterpret_cast<uint16_t*>(ws + pl.off_c), pl.Dp, op->D,
-                                                         op->V);
+                                                         op->V, nullptr);
         CCE_LAUNCH_CHECK();
         out->c = ws + pl.off_c;
         out->ldc = pl.Dp;
@@ -696,7 +698,8 @@ int cce_b200_lse_forward_ex(const cce_b200_operands* op, float* lse, float* tile
     p.partial = reinterpret_cast<float2*>(ws + pl.off_partial);
     p.tile_max = tile_max;
     p.col_max_key = col_max_key;
-    if (use_cta_pairs() && !col_max_key) {
+    p.m_dev = reinterpret_cast<const long long*>(op->n_rows_dev);
+    if (use_cta_pairs() && !col_max_key && !p.m_dev) {
         // two-CTA form: each CTA of a pair stages 128 rows of each operand, the MMA is M = 256
         rc = make_tmap(&tmB, sg.c, cdt, sg.Dk, op->V, sg.ldc, BK, BN / 2);
         if (rc != CCE_OK) return rc;
@@ -731,7 +734,7 @@ int cce_b200_lse_forward_ex(const cce_b200_operands* op, float* lse, float* tile
     }
 
     lse_combine_kernel<<<(unsigned)cdiv(op->n_rows, 256), 256, 0, st>>>(p.partial, pl.n_band, op->n_rows, lse,
-                                                                        reinterpret_cast<const int*>(ws));
+                                                                        reinterpret_cast<const int*>(ws), p.m_dev);
     CCE_LAUNCH_CHECK();
     return CCE_OK;
 }
@@ -754,24 +757,25 @@ int cce_b200_indexed_neg_dot(const cce_b200_operands* op, const int64_t* targets
     if (!targets || (op->n_rows > 0 && !out) || shift < 0) return CCE_ERR_ARG;
     if (op->n_rows == 0) return CCE_OK;
     cudaStream_t st = (cudaStream_t)stream;
+    const long long* ndev = reinterpret_cast<const long long*>(op->n_rows_dev);
     const unsigned blocks = (unsigned)cdiv(op->n_rows, 8);  // 8 warps per block
     if (op->dtype == CCE_DT_F32) {
         indexed_neg_dot_kernel<float><<<blocks, 256, 0, st>>>(
             reinterpret_cast<const float*>(op->e), op->lde, reinterpret_cast<const float*>(op->c), op->ldc, op->bias,
             op->bias_dtype, op->valids, op->valids_dtype == CCE_IDX_I64, reinterpret_cast<const long long*>(targets),
-            shift, vocab_start, op->V, op->D, op->n_rows, op->has_softcap, op->softcap, out);
+            shift, vocab_start, op->V, op->D, op->n_rows, op->has_softcap, op->softcap, out, ndev);
     } else if (op->dtype == CCE_DT_BF16) {
         indexed_neg_dot_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(
             reinterpret_cast<const __nv_bfloat16*>(op->e), op->lde, reinterpret_cast<const __nv_bfloat16*>(op->c),
             op->ldc, op->bias, op->bias_dtype, op->valids, op->valids_dtype == CCE_IDX_I64,
             reinterpret_cast<const long long*>(targets), shift, vocab_start, op->V, op->D, op->n_rows,
-            op->has_softcap, op->softcap, out);
+            op->has_softcap, op->softcap, out, ndev);
     } else {
         indexed_neg_dot_kernel<__half><<<blocks, 256, 0, st>>>(
             reinterpret_cast<const __half*>(op->e), op->lde, reinterpret_cast<const __half*>(op->c), op->ldc,
             op->bias, op->bias_dtype, op->valids, op->valids_dtype == CCE_IDX_I64,
             reinterpret_cast<const long long*>(targets), shift, vocab_start, op->V, op->D, op->n_rows,
-            op->has_softcap, op->softcap, out);
+            op->has_softcap, op->softcap, out, ndev);
     }
     CCE_LAUNCH_CHECK();
     return CCE_OK;
@@ -795,12 +799,13 @@ int cce_b200_logit_avg(const cce_b200_operands* op, float* out, void* workspace,
     float* mean_e = partial + (size_t)n_slices * D;
     const dim3 grid1((unsigned)cdiv(D, 256), (unsigned)n_slices);
     const int vi64 = op->valids_dtype == CCE_IDX_I64;
+    const long long* ndev = reinterpret_cast<const long long*>(op->n_rows_dev);
     const unsigned blocks3 = (unsigned)cdiv(V, 8);
 #define CCE_LOGIT_AVG(T)                                                                                       \
     rows_colsum_partial_kernel<T><<<grid1, 256, 0, st>>>(reinterpret_cast<const T*>(op->e), op->lde, op->valids, \
-                                                         vi64, B, D, kColsumRows, partial);                    \
+                                                         vi64, B, D, kColsumRows, partial, ndev);              \
     CCE_LAUNCH_CHECK();                                                                                        \
-    rows_colsum_finish_kernel<<<(unsigned)cdiv(D, 256), 256, 0, st>>>(partial, n_slices, D, B, mean_e);         \
+    rows_colsum_finish_kernel<<<(unsigned)cdiv(D, 256), 256, 0, st>>>(partial, n_slices, D, B, mean_e, ndev);   \
     CCE_LAUNCH_CHECK();                                                                                        \
     logit_avg_kernel<T><<<blocks3, 256, 0, st>>>(mean_e, reinterpret_cast<const T*>(op->c), op->ldc, op->bias,  \
                                                  op->bias_dtype, V, D, op->has_softcap, op->softcap, out);     \
@@ -818,22 +823,24 @@ int cce_b200_logit_avg(const cce_b200_operands* op, float* out, void* workspace,
 
 int cce_b200_loss_tail(const float* stats, int32_t world, int64_t n_rows, const void* rows, int32_t rows_dtype,
                        int64_t shift, int64_t n_total, int32_t reduction, float* lse_rows, float* loss_out,
-                       float* lse_scatter, const void* status_workspace, void* stream) {
+                       float* lse_scatter, const void* status_workspace, const int64_t* n_rows_dev, void* stream) {
     if (world < 1 || n_rows < 0 || n_total < n_rows || shift < 0 || reduction < 0 || reduction > 2 || !loss_out)
         return CCE_ERR_ARG;
     if (n_rows > 0 && !stats) return CCE_ERR_ARG;
     if (rows && rows_dtype != CCE_IDX_I32 && rows_dtype != CCE_IDX_I64) return CCE_ERR_ARG;
     if (!rows && n_rows != n_total && n_rows != 0) return CCE_ERR_ARG;
+    if (n_rows_dev && !rows) return CCE_ERR_ARG;
     cudaStream_t st = (cudaStream_t)stream;
     const bool scattered = rows != nullptr || n_rows != n_total;  // some positions receive no row: clear them first
     if (scattered && n_total > 0) {
         if (reduction == 2) CCE_CUDA(cudaMemsetAsync(loss_out, 0, (size_t)n_total * sizeof(float), st));
         if (lse_scatter) CCE_CUDA(cudaMemsetAsync(lse_scatter, 0, (size_t)n_total * sizeof(float), st));
     }
-    if (n_rows == 0 && reduction == 2) return CCE_OK;
+    if (n_rows == 0 && reduction == 2) return CCE_OK;  // (an upper bound of 0 leaves nothing to scatter either)
     loss_tail_kernel<<<1, TAIL_THREADS, 0, st>>>(stats, world, n_rows, rows, rows_dtype == CCE_IDX_I64, shift, reduction,
                                                  lse_rows, loss_out, lse_scatter,
-                                                 reinterpret_cast<const int*>(status_workspace));
+                                                 reinterpret_cast<const int*>(status_workspace),
+                                                 reinterpret_cast<const long long*>(n_rows_dev));
     CCE_LAUNCH_CHECK();
     return CCE_OK;
 }
@@ -894,7 +901,8 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
     if (rc != CCE_OK) return rc;
     cudaStream_t st = (cudaStream_t)stream;
     char* ws = reinterpret_cast<char*>(workspace);
-    const long long D = op->D, V = op->V, B = op->n_rows;
+    const long long D = op->D, V = op->V, B = op->n_rows;  // B: the row count, or its upper bound when the count is on the device
+    const long long* ndev = reinterpret_cast<const long long*>(op->n_rows_dev);
     const int cdt = compute_dtype(op);      // type the tensor cores see (fp32 operands are split into bf16)
     const bool split = is_split(op);
     const size_t esz = split ? 4 : 2;       // element size of the caller's e, c, d_c (and d_e unless d_e_f32)
@@ -923,7 +931,7 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
         order_prepare_kernel<<<(unsigned)pl.n_vt, 256, 0, st>>>(a->vocab_order, V, a->col_max_key, inv_order, tile_colmax);
         CCE_LAUNCH_CHECK();
         pack_rows_kernel<<<(unsigned)V, 128, 0, st>>>(reinterpret_cast<const uint16_t*>(sg.c), sg.ldc, a->vocab_order, 0,
-                                                     reinterpret_cast<uint16_t*>(ws + pl.off_cperm), pl.Dkp, sg.Dk, V);
+                                                     reinterpret_cast<uint16_t*>(ws + pl.off_cperm), pl.Dkp, sg.Dk, V, nullptr);
         CCE_LAUNCH_CHECK();
         sg.c = ws + pl.off_cperm;
         sg.ldc = pl.Dkp;
@@ -990,6 +998,8 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
     pg.d_out_scalar = a->d_out_numel == 1;
     pg.d_lse = a->d_lse;
     pg.grad_scale = a->grad_scale;
+    pg.scale_by_inv_rows = a->grad_scale_by_inv_rows;
+    pg.m_dev = ndev;
     pg.filter_eps = use_flags ? a->filter_eps : -1.0f;
     pg.g_out = g_buf;
     pg.g_is_bf16 = cdt == CCE_DT_BF16;
@@ -1013,20 +1023,20 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
         int* de_cnt = reinterpret_cast<int*>(ws + pl.off_de_cnt);
         int* dc_cnt = reinterpret_cast<int*>(ws + pl.off_dc_cnt);
         CCE_CUDA(cudaMemsetAsync(act, 0, (size_t)pl.n_rb * pl.n_vt, st));
-        rowgroup_min_lse_kernel<<<(unsigned)cdiv(n_groups, 8), 256, 0, st>>>(a->lse, B, minlse, n_groups);
+        rowgroup_min_lse_kernel<<<(unsigned)cdiv(n_groups, 8), 256, 0, st>>>(a->lse, B, minlse, n_groups, ndev);
         CCE_LAUNCH_CHECK();
         if (inv_order) {
             const long long n_thr = std::max<long long>(B, (long long)n_groups * pl.n_vt * 32);
             tile_mark_ordered_kernel<<<(unsigned)cdiv(n_thr, 256), 256, 0, st>>>(
                 a->tile_max, minlse, tile_colmax, a->vocab_order, inv_order, n_groups, pl.n_vt, log2f(a->filter_eps),
                 reinterpret_cast<const long long*>(a->targets), op->valids, op->valids_dtype == CCE_IDX_I64, a->shift,
-                a->vocab_start, V, B, act);
+                a->vocab_start, V, B, act, ndev);
         } else {
             const long long n_thr = std::max<long long>(B, (long long)n_groups * pl.n_vt);
             tile_mark_kernel<<<(unsigned)cdiv(n_thr, 256), 256, 0, st>>>(
                 a->tile_max, minlse, n_groups, pl.n_vt, log2f(a->filter_eps),
                 reinterpret_cast<const long long*>(a->targets), op->valids, op->valids_dtype == CCE_IDX_I64, a->shift,
-                a->vocab_start, V, B, act);
+                a->vocab_start, V, B, act, ndev);
         }
         CCE_LAUNCH_CHECK();
         const size_t sm_bytes = (size_t)(pl.n_rb + pl.n_vt + 2) * sizeof(int);
@@ -1097,6 +1107,7 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
                 p.n_vt = pl.n_vt;
                 p.klist = de_list;
                 p.kcount = de_cnt;
+                p.m_dev = ndev;
                 rc = run_de(p, tmP_k);
                 if (rc != CCE_OK) return rc;
             }
@@ -1134,6 +1145,7 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
                 EngineParams p;
                 base_params(&p, Vw, D, B, cdt, 1, 1, status);
                 p.a_tma3 = g_is3;
+                p.k_dev = ndev;
                 p.out = reinterpret_cast<char*>(a->d_c) + (size_t)v0 * D * esz;
                 p.ldo = D;
                 p.out_dtype = split ? CCE_DT_F32 : op->dtype;
@@ -1158,6 +1170,7 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
                 p.ldo = D;
                 p.out_dtype = CCE_DT_F32;
                 p.accumulate = ch == 0 ? 0 : 2;  // the first chunk stores every tile, later chunks add with red
+                p.m_dev = ndev;
                 if (a->has_filter && a->filter_e) {
                     p.kflags = flag_e;
                     p.ld_kflags = pl.ld_flag_e;
@@ -1173,10 +1186,10 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
                 dim3 grid((unsigned)cdiv(Vw, 256), (unsigned)n_rowblk);
                 if (cdt == CCE_DT_BF16)
                     colsum_partial_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(
-                        reinterpret_cast<const __nv_bfloat16*>(g_buf), pl.Vc, B, int(Vw), kColsumRows, partial, pl.Vc);
+                        reinterpret_cast<const __nv_bfloat16*>(g_buf), pl.Vc, B, int(Vw), kColsumRows, partial, pl.Vc, ndev);
                 else
                     colsum_partial_kernel<__half><<<grid, 128, 0, st>>>(reinterpret_cast<const __half*>(g_buf), pl.Vc,
-                                                                        B, int(Vw), kColsumRows, partial, pl.Vc);
+                                                                        B, int(Vw), kColsumRows, partial, pl.Vc, ndev);
                 CCE_LAUNCH_CHECK();
                 colsum_finish_kernel<<<(unsigned)cdiv(Vw, 256), 256, 0, st>>>(partial, pl.Vc, n_rowblk, int(Vw),
                                                                               a->d_bias + v0);
@@ -1188,14 +1201,14 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
     if (a->d_e) {
         if (a->d_e_f32 || split)
             scatter_cast_kernel<float><<<(unsigned)B, 128, 0, st>>>(
-                de32, D, op->valids, op->valids_dtype == CCE_IDX_I64, reinterpret_cast<float*>(a->d_e), D, D, B, status);
+                de32, D, op->valids, op->valids_dtype == CCE_IDX_I64, reinterpret_cast<float*>(a->d_e), D, D, B, status, ndev);
         else if (cdt == CCE_DT_BF16)
             scatter_cast_kernel<__nv_bfloat16><<<(unsigned)B, 128, 0, st>>>(
                 de32, D, op->valids, op->valids_dtype == CCE_IDX_I64, reinterpret_cast<__nv_bfloat16*>(a->d_e), D, D, B,
-                status);
+                status, ndev);
         else
             scatter_cast_kernel<__half><<<(unsigned)B, 128, 0, st>>>(
-                de32, D, op->valids, op->valids_dtype == CCE_IDX_I64, reinterpret_cast<__half*>(a->d_e), D, D, B, status);
+                de32, D, op->valids, op->valids_dtype == CCE_IDX_I64, reinterpret_cast<__half*>(a->d_e), D, D, B, status, ndev);
         CCE_LAUNCH_CHECK();
     }
     return CCE_OK;

@@ -52,6 +52,11 @@ struct EngineParams {
     // TMA instruction lands every swizzle atom of a stage (else one 2-D box per 64-wide group)
     int a_tma3, b_tma3;
     uint32_t idesc;
+    // Optional row count kept on the device (a caller that never read it back): when set, the
+    // launch is sized on the host for the upper bound (M, or K for a product whose reduction runs
+    // over the rows) and the kernel takes the real extent, min(*ptr, bound), from here.
+    const long long* m_dev;
+    const long long* k_dev;
     int* status;
     // optional tracing: cycles each role spent waiting, summed over CTAs (null = off)
     //   [0] producer on a free stage, [1] MMA on a filled stage, [2] MMA on a free accumulator,
@@ -106,6 +111,7 @@ struct EngineParams {
     int d_out_scalar;
     const float* d_lse;  // null or indexed at (row + shift)
     float grad_scale;
+    int scale_by_inv_rows;  // multiply grad_scale by 1 / (rows of this launch): reduction "mean" with the count on the device
     float filter_eps;  // < 0: no flags are produced
     void* g_out;       // [M][ldg] 16-bit
     long long ldg;
@@ -151,6 +157,24 @@ struct EngineSmem {
 struct PassInfo {
     int vt_lo, vt_hi, slot_lo, slot_hi;
 };
+// Extents that may come from the device (see EngineParams::m_dev / k_dev).
+struct Dyn {
+    int M, n_mblk, n_kblk;
+};
+__device__ __forceinline__ Dyn load_dyn(const EngineParams& p) {
+    Dyn d{p.M, p.n_mblk, p.n_kblk};
+    if (p.m_dev) {
+        const long long m = *p.m_dev;
+        d.M = int(m < 0 ? 0 : (m > p.M ? p.M : m));
+        d.n_mblk = (d.M + BM - 1) / BM;
+    }
+    if (p.k_dev) {
+        const long long k = *p.k_dev;
+        const int kk = int(k < 0 ? 0 : (k > p.K ? p.K : k));
+        d.n_kblk = (kk + BK - 1) / BK;
+    }
+    return d;
+}
 __device__ __forceinline__ PassInfo load_pass(const EngineParams& p) {
     PassInfo pi{0, 0, 0, 0};
     if (p.sparse) {
@@ -166,17 +190,19 @@ template <int MODE>
 struct TileIter {
     const EngineParams& p;
     const PassInfo& pass;
+    const int n_mblk;  // row blocks of this launch (from the device when the row count lives there)
     int item, n_items, sub, sub_end;
     int mblk, nblk, band, slot;
     bool first, last;
-    __device__ TileIter(const EngineParams& p_, const PassInfo& pass_) : p(p_), pass(pass_) {
+    __device__ TileIter(const EngineParams& p_, const PassInfo& pass_, const Dyn& dyn)
+        : p(p_), pass(pass_), n_mblk(dyn.n_mblk) {
         item = int(blockIdx.x) - int(gridDim.x);
         sub = 0;
         sub_end = 0;
         slot = 0;
         if (MODE == MODE_LSE) {
             const int n_band = (p.n_nblk + p.band_len - 1) / p.band_len;
-            n_items = n_band * p.n_mblk;
+            n_items = n_band * n_mblk;
         } else if (MODE == MODE_PGRAD && p.sparse) {
             n_items = pass.slot_hi - pass.slot_lo;
         } else if (MODE == MODE_GEMM && p.sparse == 2) {
@@ -184,7 +210,7 @@ struct TileIter {
         } else if (MODE == MODE_GEMM && p.sparse == 1 && p.accumulate == 2 && pass.slot_lo == pass.slot_hi) {
             n_items = 0;  // an adding launch over an empty pass has nothing to add anywhere
         } else {
-            n_items = p.n_mblk * p.n_nblk;
+            n_items = n_mblk * p.n_nblk;
         }
     }
     __device__ bool next() {
@@ -194,8 +220,8 @@ struct TileIter {
             } else {
                 item += gridDim.x;
                 if (item >= n_items) return false;
-                band = item / p.n_mblk;
-                mblk = item % p.n_mblk;
+                band = item / n_mblk;
+                mblk = item % n_mblk;
                 sub = band * p.band_len;
                 sub_end = min(p.n_nblk, sub + p.band_len);
             }
@@ -213,8 +239,8 @@ struct TileIter {
                     nblk = t % p.n_vt;
                     slot = item;
                 } else {
-                    nblk = item / p.n_mblk;  // concurrent CTAs share the classifier tile
-                    mblk = item % p.n_mblk;
+                    nblk = item / n_mblk;  // concurrent CTAs share the classifier tile
+                    mblk = item % n_mblk;
                 }
             } else if (p.sparse == 2) {
                 mblk = pass.vt_lo * 2 + item / p.n_nblk;
@@ -244,8 +270,8 @@ struct KCoord {
 };
 
 template <int MODE>
-__device__ __forceinline__ KTile ktile_setup(const EngineParams& p, int mblk) {
-    KTile kt{p.n_kblk, 0, 0};
+__device__ __forceinline__ KTile ktile_setup(const EngineParams& p, const Dyn& dyn, int mblk) {
+    KTile kt{dyn.n_kblk, 0, 0};
     if (MODE == MODE_GEMM) {
         if (p.sparse == 1) {
             kt.e0 = 4 * p.row_ptr[mblk];
@@ -322,14 +348,15 @@ __device__ void producer_loop(const CUtensorMap* tmA, const CUtensorMap* tmB, co
     uint32_t phase = 0;
     long long waited = 0;
     const PassInfo pass = load_pass(p);
-    TileIter<MODE> it(p, pass);
+    const Dyn dyn = load_dyn(p);
+    TileIter<MODE> it(p, pass, dyn);
     const bool plain = (MODE != MODE_GEMM) || (!p.sparse && !p.kflags);  // every K block of every tile
     if (plain) {
         // One lane runs the whole loop: no ballots or shuffles on the per-K-block path.
         if (lane == 0) {
             while (it.next()) {
                 const int a_mn = p.a_mn_off + it.mblk * BM, b_mn = p.b_mn_off + it.nblk * BN;
-                for (int kb = 0; kb < p.n_kblk; ++kb) {
+                for (int kb = 0; kb < dyn.n_kblk; ++kb) {
                     if (!mbar_wait(smem_u32(&s.empty[stage]), phase ^ 1u, s.abort_flag, p.status,
                                    ERR_WAIT_SMEM_EMPTY))
                         return;
@@ -350,7 +377,7 @@ __device__ void producer_loop(const CUtensorMap* tmA, const CUtensorMap* tmB, co
     }
     if constexpr (MODE == MODE_GEMM) {  // only the products have sparse or flagged reductions
     while (it.next()) {
-        const KTile kt = ktile_setup<MODE>(p, it.mblk);
+        const KTile kt = ktile_setup<MODE>(p, dyn, it.mblk);
         for (int base = 0; base < kt.n_cand; base += 32) {
             KCoord kc{0, 0, 0, 0};
             const bool take = kcand_eval<MODE>(p, kt, it.mblk, it.nblk, base + lane, kc);
@@ -402,9 +429,10 @@ __device__ void mma_loop(const EngineParams& p, const EngineSmem& s, uint32_t tm
     const uint32_t b_kstep = p.b_mn_major ? (UMMA_K / 8) * 1024 : UMMA_K * 2;
     long long waited_full = 0, waited_acc = 0;
     const PassInfo pass = load_pass(p);
-    TileIter<MODE> it(p, pass);
+    const Dyn dyn = load_dyn(p);
+    TileIter<MODE> it(p, pass, dyn);
     const bool plain = (MODE != MODE_GEMM) || (!p.sparse && !p.kflags);  // every K block of every tile
-    if (plain && p.n_kblk > 0) {
+    if (plain && dyn.n_kblk > 0) {
         if (lane == 0) {
             // descriptors of the four ring stages, built once; a K step adds to the address field
             uint64_t adesc[NSTAGE], bdesc[NSTAGE];
@@ -421,7 +449,7 @@ __device__ void mma_loop(const EngineParams& p, const EngineSmem& s, uint32_t tm
                     return;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
-                for (int kb = 0; kb < p.n_kblk; ++kb) {
+                for (int kb = 0; kb < dyn.n_kblk; ++kb) {
                     if (!mbar_wait(smem_u32(&s.full[stage]), phase, s.abort_flag, p.status, ERR_WAIT_SMEM_FULL))
                         return;
                     tc_fence_after();
@@ -467,7 +495,7 @@ __device__ void mma_loop(const EngineParams& p, const EngineSmem& s, uint32_t tm
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         int n_issued = 0;
-        const KTile kt = ktile_setup<MODE>(p, it.mblk);
+        const KTile kt = ktile_setup<MODE>(p, dyn, it.mblk);
         for (int base = 0; base < kt.n_cand; base += 32) {
             KCoord kc{0, 0, 0, 0};
             const bool take = kcand_eval<MODE>(p, kt, it.mblk, it.nblk, base + lane, kc);
@@ -614,10 +642,11 @@ __device__ void epilogue_loop(const EngineParams& p, const EngineSmem& s, uint32
     long long waited_epi = 0;
 
     const PassInfo pass = load_pass(p);
-    TileIter<MODE> it(p, pass);
+    const Dyn dyn = load_dyn(p);
+    TileIter<MODE> it(p, pass, dyn);
     while (it.next()) {
         const int row = it.mblk * BM + q * 32 + lane;
-        const bool row_ok = row < p.M;
+        const bool row_ok = row < dyn.M;
 
         // per-row constants (loaded before the wait so the latency overlaps the MMAs)
         float row_l2 = 0.0f, row_g = 0.0f, row_dl = 0.0f;
@@ -634,6 +663,7 @@ __device__ void epilogue_loop(const EngineParams& p, const EngineSmem& s, uint32
                 if (p.inv_order) row_t = (row_t >= 0 && row_t < p.N) ? p.inv_order[row_t] : -1;
                 row_l2 = p.lse[row] * kLog2e;
                 row_g = p.grad_scale * (p.d_out_scalar ? p.d_out[0] : p.d_out[ti]);
+                if (p.scale_by_inv_rows) row_g /= float(dyn.M);
                 row_dl = p.d_lse ? p.d_lse[ti] : 0.0f;
             }
         }
@@ -775,7 +805,9 @@ __device__ void epilogue_loop(const EngineParams& p, const EngineSmem& s, uint32
                         char* dst = reinterpret_cast<char*>(p.g_out) +
                                     (((size_t)it.slot * BM + q * 32 + lane) * BN + c * 32) * 2;
                         store_g16(dst, g, p.g_is_bf16 != 0);
-                    } else if (row_ok) {
+                    } else {
+                        // rows past the count (within a visited block of 128) are stored as zeros, so
+                        // that the products never meet stale values there
                         char* dst = reinterpret_cast<char*>(p.g_out) + ((size_t)row * p.ldg + col0) * 2;
                         store_g16(dst, g, p.g_is_bf16 != 0);
                     }
@@ -849,7 +881,7 @@ engine_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
     {   // a CTA without a first item (a small problem, or an empty pass of the block-list backward)
         // leaves before it sets up barriers or tensor memory; the test is uniform over the CTA
         const PassInfo pass = load_pass(p);
-        const TileIter<MODE> probe(p, pass);
+        const TileIter<MODE> probe(p, pass, load_dyn(p));
         if (int(blockIdx.x) >= probe.n_items) return;
     }
 

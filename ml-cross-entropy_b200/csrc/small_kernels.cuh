@@ -10,6 +10,14 @@ __device__ __forceinline__ long long load_index(const void* idx, int is_i64, lon
                   : (long long)reinterpret_cast<const int*>(idx)[i];
 }
 
+// Row count of a launch: the host's value, or (when the caller kept the count on the device and
+// sized the launch for an upper bound) min(*n_dev, bound).
+__device__ __forceinline__ long long actual_rows(long long bound, const long long* n_dev) {
+    if (!n_dev) return bound;
+    const long long n = *n_dev;
+    return n < 0 ? 0 : (n < bound ? n : bound);
+}
+
 __device__ __forceinline__ float load_as_float(const void* p, int dtype, long long i) {
     if (dtype == 2) return reinterpret_cast<const float*>(p)[i];
     if (dtype == 1) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
@@ -17,15 +25,19 @@ __device__ __forceinline__ float load_as_float(const void* p, int dtype, long lo
 }
 
 // dst[i][0..Dp) = src[rows[i]][0..D) (16-bit elements), zero padded to Dp columns.
-// One block per output row.
+// One block per output row; rows past a device-side count (n_dev) are written as zeros.
 __global__ void pack_rows_kernel(const uint16_t* __restrict__ src, long long ld_src,
                                  const void* __restrict__ rows, int rows_i64, uint16_t* __restrict__ dst,
-                                 long long Dp, long long D, long long n_rows) {
+                                 long long Dp, long long D, long long n_rows, const long long* __restrict__ n_dev) {
     const long long i = blockIdx.x;
     if (i >= n_rows) return;
+    uint16_t* d = dst + i * Dp;
+    if (i >= actual_rows(n_rows, n_dev)) {  // past the list: a row of zeros
+        for (long long j = threadIdx.x; j < Dp; j += blockDim.x) d[j] = 0;
+        return;
+    }
     const long long r = rows ? load_index(rows, rows_i64, i) : i;
     const uint16_t* s = src + r * ld_src;
-    uint16_t* d = dst + i * Dp;
     const bool vec = ((reinterpret_cast<uintptr_t>(s) & 15) == 0) && (D % 8 == 0);
     if (vec) {
         const uint4* s4 = reinterpret_cast<const uint4*>(s);
@@ -44,12 +56,16 @@ __global__ void pack_rows_kernel(const uint16_t* __restrict__ src, long long ld_
 // one K = 3*Dp contraction of the staged rows gives the three-term sum.  One block per row.
 __global__ void split_rows_kernel(const float* __restrict__ src, long long ld_src, const void* __restrict__ rows,
                                   int rows_i64, __nv_bfloat16* __restrict__ dst, long long Dp, long long D,
-                                  long long n_rows, int pattern) {
+                                  long long n_rows, int pattern, const long long* __restrict__ n_dev) {
     const long long i = blockIdx.x;
     if (i >= n_rows) return;
+    __nv_bfloat16* d = dst + i * 3 * Dp;
+    if (i >= actual_rows(n_rows, n_dev)) {
+        for (long long j = threadIdx.x; j < 3 * Dp; j += blockDim.x) d[j] = __float2bfloat16_rn(0.0f);
+        return;
+    }
     const long long r = rows ? load_index(rows, rows_i64, i) : i;
     const float* s = src + r * ld_src;
-    __nv_bfloat16* d = dst + i * 3 * Dp;
     for (long long j = threadIdx.x; j < Dp; j += blockDim.x) {
         const float x = j < D ? s[j] : 0.0f;
         const __nv_bfloat16 hi = __float2bfloat16_rn(x);
@@ -69,9 +85,10 @@ __global__ void to_f32_kernel(const void* __restrict__ src, int dtype, float* __
 // A non-zero status word (a pipeline kernel abandoned a wait, so `partial` is incomplete) turns
 // every output into NaN: the failure shows in the loss without a host read of the word.
 __global__ void lse_combine_kernel(const float2* __restrict__ partial, int n_band, long long n_rows,
-                                   float* __restrict__ lse, const int* __restrict__ status) {
+                                   float* __restrict__ lse, const int* __restrict__ status,
+                                   const long long* __restrict__ n_dev) {
     const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
-    if (i >= n_rows) return;
+    if (i >= actual_rows(n_rows, n_dev)) return;  // `partial` keeps the pitch n_rows
     if (status && *status != 0) {
         lse[i] = __int_as_float(0x7fc00000);
         return;
@@ -95,10 +112,11 @@ __global__ void indexed_neg_dot_kernel(const T* __restrict__ e, long long lde, c
                                        const void* __restrict__ valids, int valids_i64,
                                        const long long* __restrict__ targets, long long shift,
                                        long long vocab_start, long long V, long long D, long long n_rows,
-                                       int has_softcap, float softcap, float* __restrict__ out) {
+                                       int has_softcap, float softcap, float* __restrict__ out,
+                                       const long long* __restrict__ n_dev) {
     const long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
-    if (i >= n_rows) return;
+    if (i >= actual_rows(n_rows, n_dev)) return;
     const long long r = valids ? load_index(valids, valids_i64, i) : i;
     const long long t = targets[r + shift] - vocab_start;
     if (t < 0 || t >= V) {
@@ -135,10 +153,11 @@ __global__ void indexed_neg_dot_kernel(const T* __restrict__ e, long long lde, c
 
 // out[g] = log2(e) * min(lse[32g .. 32g+31]); one warp per group of 32 rows.
 __global__ void rowgroup_min_lse_kernel(const float* __restrict__ lse, long long n_rows,
-                                        float* __restrict__ out, int n_groups) {
+                                        float* __restrict__ out, int n_groups, const long long* __restrict__ n_dev) {
     const int g = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     if (g >= n_groups) return;
+    n_rows = actual_rows(n_rows, n_dev);  // groups past the count get +inf: nothing there is ever active
     const long long r = (long long)g * 32 + lane;
     float v = r < n_rows ? lse[r] * kLog2e : INFINITY;
 #pragma unroll
@@ -154,9 +173,9 @@ __global__ void tile_mark_kernel(const float* __restrict__ tile_max, const float
                                  int n_groups, int n_vt, float log2_eps, const long long* __restrict__ targets,
                                  const void* __restrict__ valids, int valids_i64, long long shift,
                                  long long vocab_start, long long V, long long n_rows,
-                                 uint8_t* __restrict__ act) {
+                                 uint8_t* __restrict__ act, const long long* __restrict__ n_dev) {
     const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
-    if (i < n_rows) {
+    if (i < actual_rows(n_rows, n_dev)) {
         const long long r = valids ? load_index(valids, valids_i64, i) : i;
         const long long t = targets[r + shift] - vocab_start;
         if (t >= 0 && t < V) act[(i >> 7) * n_vt + (t >> 8)] = 1;
@@ -212,9 +231,10 @@ __global__ void tile_mark_ordered_kernel(const float* __restrict__ tile_max, con
                                          const int* __restrict__ inv_order, int n_groups, int n_vt, float log2_eps,
                                          const long long* __restrict__ targets, const void* __restrict__ valids,
                                          int valids_i64, long long shift, long long vocab_start, long long V,
-                                         long long n_rows, uint8_t* __restrict__ act) {
+                                         long long n_rows, uint8_t* __restrict__ act,
+                                         const long long* __restrict__ n_dev) {
     const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
-    if (i < n_rows) {
+    if (i < actual_rows(n_rows, n_dev)) {
         const long long r = valids ? load_index(valids, valids_i64, i) : i;
         const long long t = targets[r + shift] - vocab_start;
         if (t >= 0 && t < V) act[(i >> 7) * n_vt + (inv_order[t] >> 8)] = 1;
@@ -245,9 +265,10 @@ __global__ void tile_mark_ordered_kernel(const float* __restrict__ tile_max, con
 template <typename T>
 __global__ void rows_colsum_partial_kernel(const T* __restrict__ e, long long lde, const void* __restrict__ valids,
                                            int valids_i64, long long n_rows, long long D, int rows_per_block,
-                                           float* __restrict__ partial) {
+                                           float* __restrict__ partial, const long long* __restrict__ n_dev) {
     const long long d = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (d >= D) return;
+    n_rows = actual_rows(n_rows, n_dev);
     const long long r0 = (long long)blockIdx.y * rows_per_block;
     const long long r1 = min(n_rows, r0 + rows_per_block);
     float s = 0.0f;
@@ -259,9 +280,11 @@ __global__ void rows_colsum_partial_kernel(const T* __restrict__ e, long long ld
 }
 // Stage 2: mean_e[d] = (sum over the slices, ascending) / n_rows
 __global__ void rows_colsum_finish_kernel(const float* __restrict__ partial, int n_slices, long long D,
-                                          long long n_rows, float* __restrict__ mean_e) {
+                                          long long n_rows, float* __restrict__ mean_e,
+                                          const long long* __restrict__ n_dev) {
     const long long d = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (d >= D) return;
+    n_rows = actual_rows(n_rows, n_dev);
     float s = 0.0f;
     for (int k = 0; k < n_slices; ++k) s += partial[(size_t)k * D + d];
     mean_e[d] = s / float(n_rows > 0 ? n_rows : 1);
@@ -526,9 +549,11 @@ __global__ void klist_build_kernel(const int* __restrict__ pass_info, const int*
 // grid = (ceil(width/256), ceil(n_rows/rows_per_block)); 128 threads, two columns each.
 template <typename T>
 __global__ void colsum_partial_kernel(const T* __restrict__ g, long long ldg, long long n_rows, int width,
-                                      int rows_per_block, float* __restrict__ partial, long long ld_partial) {
+                                      int rows_per_block, float* __restrict__ partial, long long ld_partial,
+                                      const long long* __restrict__ n_dev) {
     const int col = (blockIdx.x * 128 + threadIdx.x) * 2;
     if (col >= width) return;
+    n_rows = actual_rows(n_rows, n_dev);  // a slice past the count sums nothing and writes 0
     const long long r0 = (long long)blockIdx.y * rows_per_block;
     const long long r1 = min(n_rows, r0 + rows_per_block);
     float* out = partial + (size_t)blockIdx.y * ld_partial + col;
@@ -562,9 +587,9 @@ template <typename T>
 __global__ void scatter_cast_kernel(const float* __restrict__ src, long long ld_src,
                                     const void* __restrict__ rows, int rows_i64, T* __restrict__ dst,
                                     long long ld_dst, long long D, long long n_rows,
-                                    const int* __restrict__ status) {
+                                    const int* __restrict__ status, const long long* __restrict__ n_dev) {
     const long long i = blockIdx.x;
-    if (i >= n_rows) return;
+    if (i >= actual_rows(n_rows, n_dev)) return;
     const long long r = rows ? load_index(rows, rows_i64, i) : i;
     const float* s = src + i * ld_src;
     T* d = dst + r * ld_dst;
@@ -599,11 +624,13 @@ constexpr int TAIL_THREADS = 1024;
 __global__ void __launch_bounds__(TAIL_THREADS)
 loss_tail_kernel(const float* __restrict__ stats, int world, long long n_rows, const void* __restrict__ rows,
                  int rows_i64, long long shift, int reduction, float* __restrict__ lse_rows,
-                 float* __restrict__ loss_out, float* __restrict__ lse_scatter, const int* __restrict__ status) {
+                 float* __restrict__ loss_out, float* __restrict__ lse_scatter, const int* __restrict__ status,
+                 const long long* __restrict__ n_dev) {
     __shared__ double warp_sum[TAIL_THREADS / 32];
     const bool bad = status && *status != 0;
     double acc = 0.0;
-    for (long long i = threadIdx.x; i < n_rows; i += TAIL_THREADS) {
+    const long long n_act = actual_rows(n_rows, n_dev);  // `stats` keeps the pitch n_rows
+    for (long long i = threadIdx.x; i < n_act; i += TAIL_THREADS) {
         float m = -INFINITY, neg = 0.0f;
         for (int r = 0; r < world; ++r) {
             m = fmaxf(m, stats[(size_t)r * 2 * n_rows + i]);
@@ -631,7 +658,7 @@ loss_tail_kernel(const float* __restrict__ stats, int world, long long n_rows, c
     if (threadIdx.x == 0) {
         double t = 0.0;
         for (int w = 0; w < TAIL_THREADS / 32; ++w) t += warp_sum[w];
-        loss_out[0] = float(reduction == 0 ? t / double(n_rows) : t);
+        loss_out[0] = float(reduction == 0 ? t / double(n_act) : t);
     }
 }
 

@@ -68,6 +68,7 @@ class Operands(Structure):
         ("valids_dtype", c_int32),
         ("has_softcap", c_int32),
         ("softcap", c_float),
+        ("n_rows_dev", c_void_p),
     ]
 
 
@@ -82,6 +83,7 @@ class BackwardArgs(Structure):
         ("d_out_numel", c_int64),
         ("d_lse", c_void_p),
         ("grad_scale", c_float),
+        ("grad_scale_by_inv_rows", c_int32),
         ("has_filter", c_int32),
         ("filter_eps", c_float),
         ("filter_e", c_int32),
@@ -134,7 +136,7 @@ def lib() -> ctypes.CDLL:
     L.cce_b200_loss_tail.restype = c_int32
     L.cce_b200_loss_tail.argtypes = [
         c_void_p, c_int32, c_int64, c_void_p, c_int32, c_int64, c_int64, c_int32, c_void_p, c_void_p, c_void_p,
-        c_void_p, c_void_p,
+        c_void_p, c_void_p, c_void_p,
     ]  # fmt: skip
     L.cce_b200_lse_forward_static_status.restype = c_int32
     L.cce_b200_lse_forward_static_status.argtypes = [c_void_p, POINTER(c_int32)]
@@ -203,8 +205,12 @@ def make_operands(
     bias: torch.Tensor | None,
     valids: torch.Tensor | None,
     softcap: float | None,
+    n_rows_dev: torch.Tensor | None = None,
 ) -> Operands:
-    """Describe ``e`` [n_total, D], ``c`` [V, D], ``bias`` and the valid-row list for the C ABI."""
+    """Describe ``e`` [n_total, D], ``c`` [V, D], ``bias`` and the valid-row list for the C ABI.
+
+    ``n_rows_dev`` (one int64 on the device) is the length of the list when the host never read it:
+    ``valids`` is then the whole list buffer and its size the upper bound of the row count."""
     if not e.is_cuda:
         raise RuntimeError("cut_cross_entropy (B200 backend) needs CUDA tensors; it has no CPU path")
     if e.dtype not in (torch.float16, torch.bfloat16, torch.float32):
@@ -226,6 +232,9 @@ def make_operands(
     op.valids_dtype = IDX_I64 if (valids is not None and valids.dtype == torch.int64) else IDX_I32
     op.has_softcap = int(softcap is not None)
     op.softcap = float(softcap) if softcap is not None else 0.0
+    if n_rows_dev is not None:
+        assert valids is not None and n_rows_dev.dtype == torch.int64 and n_rows_dev.is_cuda
+        op.n_rows_dev = n_rows_dev.data_ptr()
     return op
 
 

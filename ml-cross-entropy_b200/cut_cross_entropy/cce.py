@@ -48,6 +48,22 @@ def set_vocab_ordering(mode: bool | str) -> str:
     return prev
 
 
+# Whether the forward pass reads the number of valid rows back to the host (one stream
+# synchronisation per call, as the reference's `nonzero` does, reference utils.py:28-49), or
+# leaves it on the device: launches and buffers are then sized for every row, the kernels take the
+# real count from device memory, and the host never waits for the GPU.  CCE_B200_SYNC_FREE=0 in
+# the environment, or set_sync_free(False), selects the read-back.
+_SYNC_FREE = os.environ.get("CCE_B200_SYNC_FREE", "1").lower() not in ("0", "false", "off", "")
+
+
+def set_sync_free(on: bool) -> bool:
+    """Keep the valid-row count on the device (``True``) or read it back in the forward pass
+    (``False``).  Returns the previous setting."""
+    global _SYNC_FREE
+    prev, _SYNC_FREE = _SYNC_FREE, bool(on)
+    return prev
+
+
 def sort_logit_avg(logit_avg: torch.Tensor) -> torch.Tensor:
     """Vocabulary order from a per-entry key, hottest entries first (reference cce.py:43-45; there
     ascending, which clusters the same entries at the other end)."""
@@ -71,6 +87,8 @@ class CCEParams:
     return_lse: bool
     # the valid-row list while the GPU is still writing it; forward() turns it into `valids`
     pending_valids: PendingValidRows | None = None
+    # length of `valids` on the device when the host never read it (then `valids` is the whole buffer)
+    n_rows_dev: torch.Tensor | None = None
 
 
 class LinearCrossEntropyFunction(torch.autograd.Function):
@@ -119,6 +137,11 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
         # the one all-gather) reads them as a [2, B] block.
         stats_flat = torch.empty((2 * e.size(0),), dtype=torch.float32, device=e.device)
         # a pending row list is waited for inside the launcher, after everything that does not need it
+        if pending is not None and pending.count_dev is not None:
+            # nothing is read back: the whole list buffer goes in, its length stays on the device
+            params.valids, params.n_rows_dev = pending.rows, pending.count_dev
+            pending = None
+        n_dev = params.n_rows_dev
         ret = cce_lse_forward_kernel(
             e=e,
             c=c,
@@ -129,6 +152,7 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
             stats_flat=stats_flat,
             return_logit_avg=order_mode == "mean",
             return_col_max=order_mode != "off",
+            n_rows_dev=n_dev,
         )
         if pending is not None:
             params.valids = pending.resolve()
@@ -155,6 +179,7 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
             out_dtype=torch.float32,
             vocab_start=vocab_start,
             out=stats[0, 1],
+            n_rows_dev=n_dev,
         )
         if vp is not None:
             stats = vp_gather_stats(stats[0], vp.group)  # [world, 2, B]
@@ -168,6 +193,7 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
             params.reduction,
             return_lse=params.return_lse,
             want_lse_rows=vp is not None,
+            n_rows_dev=n_dev,
         )
         if vp is not None:
             assert lse_rows is not None
@@ -175,7 +201,7 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
         else:
             lse = stats[0, 0]
 
-        ctx.save_for_backward(e, c, bias, lse, params.targets, params.valids, tile_max, col_max, order_key)
+        ctx.save_for_backward(e, c, bias, lse, params.targets, params.valids, tile_max, col_max, order_key, n_dev)
         ctx.params = params
         ctx.e_info, ctx.c_info, ctx.bias_info = e_info, c_info, bias_info
         return loss, lse_out
@@ -185,13 +211,14 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
     def backward(
         ctx, grad_out: torch.Tensor, grad_lse_out: torch.Tensor | None
     ) -> tuple[torch.Tensor | None, torch.Tensor | None, torch.Tensor | None, None]:
-        e, c, bias, lse, targets, valids, tile_max, col_max, order_key = ctx.saved_tensors
+        e, c, bias, lse, targets, valids, tile_max, col_max, order_key, n_dev = ctx.saved_tensors
         # integer keys (column maxima) and float keys (mean logits) both sort with the hottest entry first
         vocab_ordering = sort_logit_avg(order_key) if order_key is not None else None
         params = cast(CCEParams, ctx.params)
 
         if params.reduction == "mean":
-            grad_scale = 1.0 / max(lse.numel(), 1)
+            # with the count on the device, lse has a slot per row and the division happens in the kernel
+            grad_scale = 1.0 if n_dev is not None else 1.0 / max(lse.numel(), 1)
         elif params.reduction in ("sum", "none"):
             grad_scale = 1.0
         else:
@@ -228,6 +255,8 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
             vocab_start=vp.start if vp is not None else 0,
             tile_max=tile_max,
             col_max=col_max,
+            n_rows_dev=n_dev,
+            scale_by_inv_rows=n_dev is not None and params.reduction == "mean",
         )
         return de, dc, dbias, None
 
@@ -281,7 +310,7 @@ def cce_linear_cross_entropy(
     e = e.contiguous()
     targets = targets.contiguous()
     shift = int(shift)
-    pending = launch_flat_valids(targets, ignore_index, shift)
+    pending = launch_flat_valids(targets, ignore_index, shift, count_on_device=_SYNC_FREE)
 
     e = e.flatten(0, -2)
     targets = targets.flatten()

@@ -17,11 +17,12 @@ from .vocab_parallel.utils import vp_reduce_e_grad_
 
 
 def _launch(do, dlse, e, c, bias, lse, valids, softcap, filter_eps, targets, shift, grad_scale,
-            filter_e, filter_c, vocab_start, de, dc, dbias, tile_max=None, vocab_ordering=None, col_max=None) -> None:
+            filter_e, filter_c, vocab_start, de, dc, dbias, tile_max=None, vocab_ordering=None, col_max=None,
+            n_rows_dev=None, scale_by_inv_rows=False) -> None:
     """Fill the (pre-allocated, possibly ``None``) outputs ``de``/``dc``/``dbias`` through the C ABI."""
     dev = e.device
     a = _native.BackwardArgs()
-    a.op = _native.make_operands(e, c, bias, valids, softcap)
+    a.op = _native.make_operands(e, c, bias, valids, softcap, n_rows_dev)
     a.lse = lse.data_ptr()
     a.targets = targets.data_ptr()
     a.shift = shift
@@ -30,6 +31,7 @@ def _launch(do, dlse, e, c, bias, lse, valids, softcap, filter_eps, targets, shi
     a.d_out_numel = do.numel()
     a.d_lse = _native._ptr(dlse)
     a.grad_scale = grad_scale
+    a.grad_scale_by_inv_rows = int(scale_by_inv_rows)
     a.has_filter = int(filter_eps is not None)
     a.filter_eps = float(filter_eps) if filter_eps is not None else 0.0
     a.filter_e = int(filter_e)
@@ -76,6 +78,8 @@ def cce_backward_kernel(
     vocab_start: int = 0,
     tile_max: torch.Tensor | None = None,
     col_max: torch.Tensor | None = None,
+    n_rows_dev: torch.Tensor | None = None,
+    scale_by_inv_rows: bool = False,
 ) -> tuple[torch.Tensor | None, torch.Tensor | None, torch.Tensor | None]:
     """Returns ``(de, dc, dbias)``, each ``None`` unless its ``*_info.requires_grad``.
 
@@ -89,6 +93,9 @@ def cce_backward_kernel(
     no bias gradient) and is ignored otherwise.  The ``accum_*_fp32`` switches are accepted
     and ignored: every accumulation is fp32.  With
     ``reduce_e_grad`` the fp32 partial ``de`` is summed over ``pg`` before the cast.
+    ``n_rows_dev`` (one int64 on the device) is the number of valid rows when the host never read
+    it (``valids`` and ``lse`` are then sized for all rows); ``scale_by_inv_rows`` divides
+    ``grad_scale`` by that number on the device (``reduction="mean"``).
     ``tile_max`` / ``col_max`` are the optional by-products of
     ``cce_lse_forward_kernel(return_tile_max=True, return_col_max=True)``.
     """
@@ -131,7 +138,7 @@ def cce_backward_kernel(
     if want_de or want_dc or want_dbias:
         _launch(do, dlse, e, c, bias, lse, valids, softcap, filter_eps, targets, int(shift), float(grad_scale),
                 bool(filter_e_grad), bool(filter_c_grad), int(vocab_start), de, dc, dbias, tile_max,
-                vocab_ordering, col_max)
+                vocab_ordering, col_max, n_rows_dev, bool(scale_by_inv_rows))
 
     if de_f32:
         assert de is not None

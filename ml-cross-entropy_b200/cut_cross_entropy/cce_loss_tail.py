@@ -24,13 +24,15 @@ def loss_tail_kernel(
     reduction: str,
     return_lse: bool,
     want_lse_rows: bool,
+    n_rows_dev: torch.Tensor | None = None,
 ) -> tuple[torch.Tensor, torch.Tensor | None, torch.Tensor | None]:
     """``stats`` is ``[world, 2, B]`` float32: per vocabulary shard the log-sum-exp of every valid
     row and minus its correct-token logit (``world = 1`` without vocab parallelism).
 
     Returns ``(loss, lse_out, lse_rows)``: the reduced loss (a scalar, or ``batch_shape`` for
     ``"none"`` with zeros where no row lands), the log-sum-exp scattered to ``batch_shape`` (only
-    with ``return_lse``), and the merged log-sum-exp per valid row (only with ``want_lse_rows``)."""
+    with ``return_lse``), and the merged log-sum-exp per valid row (only with ``want_lse_rows``).
+    With ``n_rows_dev`` (the row count on the device) ``B`` is only the pitch of ``stats``."""
     if reduction not in _REDUCTION_CODE:
         raise ValueError(f"Unknown reduction {reduction}")
     assert stats.dim() == 3 and stats.size(1) == 2 and stats.dtype == torch.float32 and stats.is_contiguous()
@@ -45,7 +47,7 @@ def loss_tail_kernel(
             stats.data_ptr(), world, n_rows, _native._ptr(valids),
             _native.IDX_I64 if (valids is not None and valids.dtype == torch.int64) else _native.IDX_I32,
             int(shift), n_total, _REDUCTION_CODE[reduction], _native._ptr(lse_rows), loss.data_ptr(),
-            _native._ptr(lse_out), None, _native.stream_ptr(dev),
+            _native._ptr(lse_out), None, _native._ptr(n_rows_dev), _native.stream_ptr(dev),
         )  # fmt: skip
     _native.check(rc, "cce_b200_loss_tail")
     return loss, lse_out, lse_rows

@@ -23,6 +23,7 @@ def cce_lse_forward_kernel(
     return_tile_max: bool = False,
     stats_flat: torch.Tensor | None = None,
     return_col_max: bool = False,
+    n_rows_dev: torch.Tensor | None = None,
 ) -> tuple[torch.Tensor, ...] | torch.Tensor:
     """``lse[i] = logsumexp_v(softcap(e[valids[i]] @ c[v] + bias[v]))`` as float32 ``[B]``.
 
@@ -46,6 +47,10 @@ def cce_lse_forward_kernel(
     ``return_col_max`` adds the largest logit of every vocabulary entry over all rows (int32 keys
     ``[V]``, see ``cce_b200_lse_forward_ex``), which a backward with a vocabulary order needs.
 
+    ``n_rows_dev`` (one int64 on the device) is the length of ``valids`` when the host never read it:
+    ``valids`` is then the whole list buffer, the result has one slot per entry of that buffer and
+    only the first ``n_rows_dev`` are written.
+
     Returns ``lse`` alone, or a tuple ``(lse[, logit_avg][, tile_max][, col_max])`` of what was asked for.
     """
     assert e.shape[1] == c.shape[1], "Incompatible dimensions"
@@ -62,7 +67,7 @@ def cce_lse_forward_kernel(
         assert valids.ndim == 1
         valids = valids.contiguous()
 
-    op = _native.make_operands(e, c, bias, valids, softcap)
+    op = _native.make_operands(e, c, bias, valids, softcap, n_rows_dev)
     if stats_flat is not None:
         assert stats_flat.dtype == torch.float32 and stats_flat.is_contiguous() and stats_flat.numel() >= op.n_rows
         lse = stats_flat[: op.n_rows]

@@ -24,10 +24,12 @@ def indexed_neg_dot_forward_kernel(
     out_dtype: torch.dtype | None = None,
     vocab_start: int = 0,
     out: torch.Tensor | None = None,
+    n_rows_dev: torch.Tensor | None = None,
 ) -> torch.Tensor:
     """``out[i] = -softcap(e[r] @ c[t] + bias[t])`` with ``r = valids[i]``, ``t = inds[r + shift] - vocab_start``.
 
-    ``out`` (float32, contiguous, one element per row) is written in place and returned when given."""
+    ``out`` (float32, contiguous, one element per row) is written in place and returned when given;
+    ``n_rows_dev`` as in :func:`cut_cross_entropy.cce_lse_forward.cce_lse_forward_kernel`."""
     assert inds.ndim == 1 and e.ndim == 2 and c.ndim == 2
     assert inds.size(0) == e.size(0)
     assert c.size(1) == e.size(1)
@@ -43,7 +45,7 @@ def indexed_neg_dot_forward_kernel(
     if valids is not None:
         valids = valids.contiguous()
 
-    op = _native.make_operands(e, c, bias, valids, softcap)
+    op = _native.make_operands(e, c, bias, valids, softcap, n_rows_dev)
     if out is not None:
         assert out.dtype == torch.float32 and out.is_contiguous() and out.numel() == op.n_rows
         out_dtype = torch.float32

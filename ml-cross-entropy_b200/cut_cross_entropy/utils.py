@@ -42,11 +42,17 @@ class PendingValidRows:
     of the list has not been read back.  :meth:`resolve` reads it (the one host synchronisation of
     the forward pass) and returns what ``_build_flat_valids`` returns."""
 
-    def __init__(self, rows: torch.Tensor, count: torch.Tensor, done: torch.cuda.Event, n_total: int, shift: int):
+    def __init__(self, rows: torch.Tensor, count: torch.Tensor, done: "torch.cuda.Event | None", n_total: int,
+                 shift: int, count_dev: torch.Tensor | None = None):
         self.rows, self.count, self.done, self.n_total, self.shift = rows, count, done, n_total, shift
+        # the list's length in device memory, for a caller that never reads it (then `count`/`done` are unused)
+        self.count_dev = count_dev
         self._resolved: torch.Tensor | None | object = _UNRESOLVED
 
     def resolve(self) -> torch.Tensor | None:
+        if self._resolved is _UNRESOLVED and self.count_dev is not None:
+            n = int(self.count_dev.item())  # synchronises; the sync-free path never calls this
+            self._resolved = None if (self.shift == 0 and n == self.n_total) else self.rows[:n]
         if self._resolved is _UNRESOLVED:
             # The kernel wrote the length straight into pinned host memory: waiting for the event
             # is all it takes, no device-to-host copy that could queue behind a bulk download.
@@ -56,9 +62,13 @@ class PendingValidRows:
         return self._resolved
 
 
-def launch_flat_valids(targets: torch.Tensor, ignore_index: int, shift: int) -> PendingValidRows:
+def launch_flat_valids(
+    targets: torch.Tensor, ignore_index: int, shift: int, count_on_device: bool = False
+) -> PendingValidRows:
     """Enqueue ``cce_b200_valid_rows`` on the current stream for CUDA ``targets`` of shape
-    ``[..., seq_len]``; host work that does not need the list can follow before ``resolve()``."""
+    ``[..., seq_len]``; host work that does not need the list can follow before ``resolve()``.
+    With ``count_on_device`` the length of the list is written to device memory (``count_dev``) and
+    nothing is prepared for reading it back: the kernels of the loss take it from there."""
     from . import _native
 
     flat = targets.reshape(-1)
@@ -69,7 +79,10 @@ def launch_flat_valids(targets: torch.Tensor, ignore_index: int, shift: int) -> 
     seq = targets.size(-1) if targets.dim() > 0 else 1
     L = _native.lib()
     rows = torch.empty((n_total,), dtype=torch.int32 if shift == 0 else torch.int64, device=targets.device)
-    count = torch.empty((1,), dtype=torch.int64, pin_memory=True)  # device-writable through unified addressing
+    if count_on_device:
+        count = torch.empty((1,), dtype=torch.int64, device=targets.device)
+    else:
+        count = torch.empty((1,), dtype=torch.int64, pin_memory=True)  # device-writable through unified addressing
     ws = _native.workspace(L.cce_b200_valid_rows_workspace_bytes(n_total), targets.device)
     with torch.cuda.device(targets.device):
         rc = L.cce_b200_valid_rows(
@@ -78,6 +91,8 @@ def launch_flat_valids(targets: torch.Tensor, ignore_index: int, shift: int) -> 
             _native.stream_ptr(targets.device),
         )  # fmt: skip
     _native.check(rc, "cce_b200_valid_rows")
+    if count_on_device:
+        return PendingValidRows(rows, count, None, n_total, shift, count_dev=count)
     done = torch.cuda.Event()
     done.record(torch.cuda.current_stream(targets.device))
     return PendingValidRows(rows, count, done, n_total, shift)

@@ -454,3 +454,38 @@ def test_vocabulary_shards_on_one_gpu(world, impl_filter):
         torch.testing.assert_close(db.float(), db_full[s0:s1].float(), rtol=2e-2, atol=1e-4)
         de_sum += de.float()
     assert (de_sum - de_full.float()).abs().max().item() <= 1e-2 * de_full.float().abs().max().item()
+
+
+@pytest.mark.parametrize("impl", ["cce", "cce_exact", "cce_kahan_full_c"])
+@pytest.mark.parametrize("reduction", ["mean", "sum", "none"])
+@pytest.mark.parametrize("shift,ignored", [(0, 0.0), (0, 0.3), (2, 0.3), (0, 1.0)])
+def test_row_count_on_the_device_gives_the_same_bits_as_reading_it_back(impl, reduction, shift, ignored):
+    """The forward pass either reads the number of valid rows back (one synchronisation) or leaves
+    it on the device and sizes everything for all rows.  Same kernels, same arithmetic: loss,
+    log-sum-exp and gradients must agree bit for bit, also when no row or every row is valid."""
+    from cut_cross_entropy import cce as cce_mod
+    from cut_cross_entropy import linear_cross_entropy
+
+    N, T, V, D = 768, 64, 1500, 192
+    e, c, bias, t = planted_inputs(N, V, D, torch.bfloat16, DEV, seed=11, bias=True, ignored=ignored)
+    e = e.view(N // T, T, D).requires_grad_(True)
+    t = t.view(N // T, T)
+    c.requires_grad_(True)
+    bias = bias.float().requires_grad_(impl != "cce")
+    outs = []
+    for sync_free in (False, True):
+        prev = cce_mod.set_sync_free(sync_free)
+        try:
+            e.grad = c.grad = bias.grad = None
+            loss, lse = linear_cross_entropy(e, c, t, bias=bias, shift=shift, reduction=reduction, impl=impl,
+                                             softcap=25.0, return_lse=True)
+            (loss.sum() + 1e-2 * lse.pow(2).sum()).backward()
+            outs.append((loss.detach().clone(), lse.detach().clone(), e.grad.clone(), c.grad.clone(),
+                         None if bias.grad is None else bias.grad.clone()))
+        finally:
+            cce_mod.set_sync_free(prev)
+    for a, b in zip(*outs):
+        if a is None:
+            assert b is None
+        else:
+            torch.testing.assert_close(a, b, rtol=0, atol=0, equal_nan=True)

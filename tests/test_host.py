@@ -34,9 +34,9 @@ def test_library_loads_and_exports_every_declared_symbol():
 def test_ctypes_structs_match_the_header_layout():
     from cut_cross_entropy import _native
 
-    # 4 pointers, 6 int64, 4 int32, 1 float -> 100 bytes, padded to 8-byte alignment
-    assert ctypes.sizeof(_native.Operands) == 104
-    assert _native.BackwardArgs.op.offset == 0 and _native.BackwardArgs.lse.offset == 104
+    # 4 pointers, 6 int64, 4 int32, 1 float -> 100 bytes, padded to 8-byte alignment, then 1 pointer
+    assert ctypes.sizeof(_native.Operands) == 112 and _native.Operands.n_rows_dev.offset == 104
+    assert _native.BackwardArgs.op.offset == 0 and _native.BackwardArgs.lse.offset == 112
     # no GPU here: argument checks must reject, not crash
     L = _native.lib()
     op = _native.Operands()

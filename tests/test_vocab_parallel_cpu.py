@@ -63,16 +63,16 @@ def _install_cpu_stand_ins():
     import cut_cross_entropy.cce_backward as bwd_mod
 
     def lse_kernel(e, c, bias=None, valids=None, softcap=None, return_logit_avg=False, return_tile_max=False,
-                   stats_flat=None, return_col_max=False):
+                   stats_flat=None, return_col_max=False, n_rows_dev=None):
         assert not return_tile_max and not return_col_max and not return_logit_avg
         return O.lse_forward(e, c, bias, valids, softcap).float()
 
     def dot_kernel(e, c, inds, bias=None, shift=0, valids=None, softcap=None, out_dtype=None, vocab_start=0,
-                   out=None):
+                   out=None, n_rows_dev=None):
         r = O.indexed_neg_dot(e, c, inds, bias, shift, valids, softcap, vocab_start=vocab_start).to(out_dtype)
         return r if out is None else out.copy_(r)
 
-    def tail_kernel(stats, valids, shift, batch_shape, reduction, return_lse, want_lse_rows):
+    def tail_kernel(stats, valids, shift, batch_shape, reduction, return_lse, want_lse_rows, n_rows_dev=None):
         # what cce_b200_loss_tail computes, in PyTorch
         lse = torch.logsumexp(stats[:, 0], dim=0)
         nll = lse + stats[:, 1].sum(dim=0)
@@ -88,7 +88,8 @@ def _install_cpu_stand_ins():
         return loss, (scatter(lse) if return_lse else None), (lse if want_lse_rows else None)
 
     def launch(do, dlse, e, c, bias, lse, valids, softcap, filter_eps, targets, shift, grad_scale,
-               filter_e, filter_c, vocab_start, de, dc, dbias, tile_max=None, vocab_ordering=None, col_max=None):
+               filter_e, filter_c, vocab_start, de, dc, dbias, tile_max=None, vocab_ordering=None, col_max=None,
+               n_rows_dev=None, scale_by_inv_rows=False):
         # restates one rank of cce_backward.py:182-310 with the global lse
         n = e.size(0)
         rows = torch.arange(n) if valids is None else valids.long()
