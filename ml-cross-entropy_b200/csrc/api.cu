@@ -1,6 +1,7 @@
 // Host side of the C ABI declared in include/cce_b200.h: argument checks, workspace
 // planning, TMA descriptor encoding and kernel launches.  No device allocation happens here.
 #include "../../include/cce_b200.h"
+#include "../../include/cce_b200_testing.h"
 
 #include <algorithm>
 #include <atomic>
@@ -75,14 +76,16 @@ EncodeTiledFn get_encode() {
     return fn;
 }
 
-// CCE_B200_LSE_PAIR=1 selects the two-CTA (cta_group::2) forward kernel; read once.
-bool use_cta_pairs() {
-    static const bool on = [] {
+// CCE_B200_LSE_PAIR=<n> selects the two-CTA (cta_group::2) forward kernel; read once.
+// bit 0: on; bit 1: one multicast commit per event instead of one commit per CTA; bit 2: 128 K elements per stage.
+int cta_pair_mode() {
+    static const int mode = [] {
         const char* env = getenv("CCE_B200_LSE_PAIR");
-        return env && env[0] == '1';
+        return env ? atoi(env) : 0;
     }();
-    return on;
+    return mode;
 }
+bool use_cta_pairs() { return (cta_pair_mode() & 1) != 0; }
 
 struct DeviceInfo {
     int sms = 0;
@@ -111,7 +114,8 @@ int device_info(DeviceInfo** out) {
                                       ENGINE_SMEM));
         CCE_CUDA(cudaFuncSetAttribute(engine_kernel<MODE_GEMM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       ENGINE_SMEM));
-        CCE_CUDA(cudaFuncSetAttribute(lse_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM));
+        CCE_CUDA(cudaFuncSetAttribute(lse_pair_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg<1>::SMEM));
+        CCE_CUDA(cudaFuncSetAttribute(lse_pair_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg<2>::SMEM));
         d.attr_set = true;
     }
     *out = &d;
@@ -721,7 +725,15 @@ int cce_b200_lse_forward_ex(const cce_b200_operands* op, float* lse, float* tile
             std::lock_guard<std::mutex> lock(g_prof_mu);
             if (g_wait_counters) p.wait_cycles = g_wait_counters;
         }
-        lse_pair_kernel<<<(unsigned)(2 * pairs), ENGINE_THREADS, PAIR_SMEM, st>>>(tmA, tmB, p);
+        {
+            std::lock_guard<std::mutex> lock(g_prof_mu);
+            if (g_clk_words) p.clk_words = g_clk_words;
+        }
+        const int mc = (cta_pair_mode() >> 1) & 1;
+        if (cta_pair_mode() & 4)
+            lse_pair_kernel<2><<<(unsigned)(2 * pairs), ENGINE_THREADS, PairCfg<2>::SMEM, st>>>(tmA, tmB, p, mc);
+        else
+            lse_pair_kernel<1><<<(unsigned)(2 * pairs), ENGINE_THREADS, PairCfg<1>::SMEM, st>>>(tmA, tmB, p, mc);
         CCE_LAUNCH_CHECK();
         if (prof) {
             CCE_CUDA(cudaEventRecord(rec.stop, st));

@@ -13,11 +13,16 @@
 
 namespace cce {
 
-constexpr int P_NSTAGE = 6;
-constexpr int P_A_BYTES = BM * BK * 2;         // 128 rows of E
-constexpr int P_B_BYTES = (BN / 2) * BK * 2;   // 128 of the tile's 256 classifier rows
-constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
-constexpr int PAIR_SMEM = P_NSTAGE * P_STAGE_BYTES + 1024 + 256;
+// KSUB = 64-element K sub-blocks per ring stage (1: 32 KB stages, 2: 64 KB stages), NST = ring depth
+constexpr int P_SUB_BYTES = BM * BK * 2;  // one operand, 128 rows x 64 K elements (one swizzle atom column)
+template <int KSUB>
+struct PairCfg {
+    static constexpr int NST = 6 / KSUB;
+    static constexpr int A_BYTES = KSUB * P_SUB_BYTES;
+    static constexpr int STAGE_BYTES = 2 * A_BYTES;
+    static constexpr int SMEM = NST * STAGE_BYTES + 1024 + 256;
+};
+constexpr int PAIR_SMEM = PairCfg<1>::SMEM;
 
 struct PairIter {
     const EngineParams& p;
@@ -61,27 +66,33 @@ struct PairSmem {
     int* abort_flag;
 };
 
+template <int KSUB>
 __device__ void pair_producer(const CUtensorMap* tmA, const CUtensorMap* tmB, const EngineParams& p,
                               const PairSmem& s, uint32_t rank) {
+    using C = PairCfg<KSUB>;
     if ((threadIdx.x & 31) != 0) return;  // one lane runs the whole loop
     int stage = 0;
     uint32_t phase = 0;
     long long waited = 0;
     PairIter it(p);
+    const int n_step = (p.n_kblk + KSUB - 1) / KSUB;
     while (it.next()) {
         const int a_row = (it.rb2 * 2 + int(rank)) * BM;
         const int b_row = it.nblk * BN + int(rank) * (BN / 2);
-        for (int kb = 0; kb < p.n_kblk; ++kb) {
+        for (int ks = 0; ks < n_step; ++ks) {
             const long long t0 = (kTrace && p.wait_cycles) ? clock64() : 0;
             if (!mbar_wait(smem_u32(&s.empty[stage]), phase ^ 1u, s.abort_flag, p.status, ERR_WAIT_SMEM_EMPTY)) return;
             if (kTrace && p.wait_cycles) waited += clock64() - t0;
             const uint32_t bar_local = smem_u32(&s.full[stage]);
             const uint32_t bar_leader = map_to_cta(bar_local, 0);
-            const uint32_t sa = smem_u32(s.stages + stage * P_STAGE_BYTES);
-            if (rank == 0) mbar_expect_tx(bar_local, 2 * P_STAGE_BYTES);  // bytes of both CTAs
-            tma_load_2d_pair(sa, tmA, bar_leader, kb * BK, a_row);
-            tma_load_2d_pair(sa + P_A_BYTES, tmB, bar_leader, kb * BK, b_row);
-            if (++stage == P_NSTAGE) {
+            const uint32_t sa = smem_u32(s.stages + stage * C::STAGE_BYTES);
+            if (rank == 0) mbar_expect_tx(bar_local, 2 * C::STAGE_BYTES);  // bytes of both CTAs
+#pragma unroll
+            for (int j = 0; j < KSUB; ++j) {  // columns past K are zero-filled by the tensor map
+                tma_load_2d_pair(sa + j * P_SUB_BYTES, tmA, bar_leader, (ks * KSUB + j) * BK, a_row);
+                tma_load_2d_pair(sa + C::A_BYTES + j * P_SUB_BYTES, tmB, bar_leader, (ks * KSUB + j) * BK, b_row);
+            }
+            if (++stage == C::NST) {
                 stage = 0;
                 phase ^= 1u;
             }
@@ -90,8 +101,11 @@ __device__ void pair_producer(const CUtensorMap* tmA, const CUtensorMap* tmB, co
     if (kTrace && p.wait_cycles) atomicAdd(p.wait_cycles + 0, (unsigned long long)waited);
 }
 
-// leader CTA only; one lane runs the whole loop
-__device__ void pair_mma(const EngineParams& p, const PairSmem& s, uint32_t tmem_base) {
+// leader CTA only; one lane runs the whole loop.  mc_commit: one multicast commit per event instead
+// of one commit per CTA of the pair.
+template <int KSUB>
+__device__ void pair_mma(const EngineParams& p, const PairSmem& s, uint32_t tmem_base, bool mc_commit) {
+    using C = PairCfg<KSUB>;
     if ((threadIdx.x & 31) != 0) return;
     int stage = 0;
     uint32_t phase = 0;
@@ -99,13 +113,13 @@ __device__ void pair_mma(const EngineParams& p, const PairSmem& s, uint32_t tmem
     uint32_t acc_phase = 0;
     long long waited_full = 0, waited_acc = 0;
     // per-stage descriptors and barrier addresses (own CTA and peer), built once
-    uint64_t adesc[P_NSTAGE], bdesc[P_NSTAGE];
-    uint32_t full_bar[P_NSTAGE], empty_bar[P_NSTAGE], empty_peer[P_NSTAGE];
+    uint64_t adesc[C::NST], bdesc[C::NST];
+    uint32_t full_bar[C::NST], empty_bar[C::NST], empty_peer[C::NST];
 #pragma unroll
-    for (int i = 0; i < P_NSTAGE; ++i) {
-        const uint32_t sa = smem_u32(s.stages + i * P_STAGE_BYTES);
+    for (int i = 0; i < C::NST; ++i) {
+        const uint32_t sa = smem_u32(s.stages + i * C::STAGE_BYTES);
         adesc[i] = make_smem_desc(sa, 16, 1024);
-        bdesc[i] = make_smem_desc(sa + P_A_BYTES, 16, 1024);
+        bdesc[i] = make_smem_desc(sa + C::A_BYTES, 16, 1024);
         full_bar[i] = smem_u32(&s.full[i]);
         empty_bar[i] = smem_u32(&s.empty[i]);
         empty_peer[i] = map_to_cta(empty_bar[i], 1);
@@ -113,6 +127,7 @@ __device__ void pair_mma(const EngineParams& p, const PairSmem& s, uint32_t tmem
     const uint32_t tfull_bar[2] = {smem_u32(&s.tfull[0]), smem_u32(&s.tfull[1])};
     const uint32_t tfull_peer[2] = {map_to_cta(tfull_bar[0], 1), map_to_cta(tfull_bar[1], 1)};
     PairIter it(p);
+    const int n_step = (p.n_kblk + KSUB - 1) / KSUB;
     while (it.next()) {
         {
             const long long t0 = (kTrace && p.wait_cycles) ? clock64() : 0;
@@ -122,11 +137,11 @@ __device__ void pair_mma(const EngineParams& p, const PairSmem& s, uint32_t tmem
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < p.n_kblk; ++kb) {
+        for (int ks = 0; ks < n_step; ++ks) {
             uint64_t ad = 0, bd = 0;
             uint32_t fb = 0, eb = 0, ep = 0;
 #pragma unroll
-            for (int i = 0; i < P_NSTAGE; ++i) {  // select without dynamic register indexing
+            for (int i = 0; i < C::NST; ++i) {  // select without dynamic register indexing
                 if (i == stage) {
                     ad = adesc[i];
                     bd = bdesc[i];
@@ -140,18 +155,30 @@ __device__ void pair_mma(const EngineParams& p, const PairSmem& s, uint32_t tmem
             if (kTrace && p.wait_cycles) waited_full += clock64() - t0;
             tc_fence_after();
 #pragma unroll
-            for (int k = 0; k < BK / UMMA_K; ++k)
-                tc_mma_f16_pair(d_tmem, ad + k * 2, bd + k * 2, p.idesc, (kb | k) ? 1u : 0u);  // +32 B per K step
+            for (int j = 0; j < KSUB; ++j) {
+                const uint64_t off = uint64_t(j) * (P_SUB_BYTES >> 4);  // next 64-element K sub-block of the stage
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k)  // +32 B per K step inside a swizzle row
+                    tc_mma_f16_pair(d_tmem, ad + off + k * 2, bd + off + k * 2, p.idesc, (ks | j | k) ? 1u : 0u);
+            }
             // the stage is free in both CTAs once these MMAs have read it
-            tc_commit_pair(eb);
-            tc_commit_pair(ep);
-            if (++stage == P_NSTAGE) {
+            if (mc_commit) {
+                tc_commit_pair_mc(eb, 3);
+            } else {
+                tc_commit_pair(eb);
+                tc_commit_pair(ep);
+            }
+            if (++stage == C::NST) {
                 stage = 0;
                 phase ^= 1u;
             }
         }
-        tc_commit_pair(acc ? tfull_bar[1] : tfull_bar[0]);
-        tc_commit_pair(acc ? tfull_peer[1] : tfull_peer[0]);
+        if (mc_commit) {
+            tc_commit_pair_mc(acc ? tfull_bar[1] : tfull_bar[0], 3);
+        } else {
+            tc_commit_pair(acc ? tfull_bar[1] : tfull_bar[0]);
+            tc_commit_pair(acc ? tfull_peer[1] : tfull_peer[0]);
+        }
         if (++acc == 2) {
             acc = 0;
             acc_phase ^= 1u;
@@ -243,9 +270,13 @@ __device__ void pair_epilogue(const EngineParams& p, const PairSmem& s, uint32_t
     if (kTrace && p.wait_cycles && lane == 0) atomicAdd(p.wait_cycles + 3, (unsigned long long)(waited_epi / 4));
 }
 
+template <int KSUB>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(ENGINE_THREADS, 1)
 lse_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                const EngineParams p) {
+                const EngineParams p, const int mc_commit) {
+    using C = PairCfg<KSUB>;
+    constexpr int P_NSTAGE = C::NST;
+    constexpr int P_STAGE_BYTES = C::STAGE_BYTES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     PairSmem s;
@@ -262,6 +293,10 @@ lse_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
     const long long t_start = (kTrace && p.wait_cycles) ? clock64() : 0;
+    if (p.clk_words && blockIdx.x == 0 && threadIdx.x == 0) {
+        p.clk_words[0] = (unsigned long long)clock64();
+        p.clk_words[1] = global_timer_ns();
+    }
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < P_NSTAGE; ++i) {
@@ -292,9 +327,9 @@ lse_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(s.tmem_base);
 
     if (warp == 0) {
-        pair_producer(&tmA, &tmB, p, s, rank);
+        pair_producer<KSUB>(&tmA, &tmB, p, s, rank);
     } else if (warp == 1) {
-        if (rank == 0) pair_mma(p, s, tmem_base);
+        if (rank == 0) pair_mma<KSUB>(p, s, tmem_base, mc_commit != 0);
     } else {
         pair_epilogue(p, s, tmem_base, rank);
     }
@@ -315,6 +350,10 @@ lse_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    }
+    if (p.clk_words && blockIdx.x == 0 && threadIdx.x == 0) {
+        p.clk_words[2] = (unsigned long long)clock64();
+        p.clk_words[3] = global_timer_ns();
     }
     if (kTrace && p.wait_cycles && threadIdx.x == 0) {
         atomicAdd(p.wait_cycles + 4, (unsigned long long)(clock64() - t_start));

@@ -54,6 +54,14 @@ __device__ __forceinline__ void tc_commit_pair(uint32_t bar_cluster_addr) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr)
                  : "memory");
 }
+// the same, arriving on the barrier at the same shared-memory offset in every CTA of `cta_mask`
+__device__ __forceinline__ void tc_commit_pair_mc(uint32_t bar_cluster_addr, uint16_t cta_mask) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+            bar_cluster_addr),
+        "h"(cta_mask)
+        : "memory");
+}
 // D[tmem of both CTAs] (+)= A * B with M = 256 (128 rows per CTA) and each CTA supplying half of B's rows
 __device__ __forceinline__ void tc_mma_f16_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                                 uint32_t accumulate) {

@@ -16,7 +16,7 @@ PKG_DIR = Path(__file__).resolve().parent
 CSRC_DIR = PKG_DIR.parent / "csrc"
 LIB_PATH = PKG_DIR / "libcce_b200.so"
 SOURCES = ["api.cu"]
-HEADERS = ["engine.cuh", "engine_pair.cuh", "ptx.cuh", "ptx_pair.cuh", "small_kernels.cuh", "../../include/cce_b200.h"]
+HEADERS = ["engine.cuh", "engine_pair.cuh", "ptx.cuh", "ptx_pair.cuh", "small_kernels.cuh", "../../include/cce_b200.h", "../../include/cce_b200_testing.h"]
 
 
 def _nvcc() -> str:

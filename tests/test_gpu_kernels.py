@@ -205,13 +205,14 @@ def test_two_cta_forward_kernel_matches_the_default_one():
 
     with tempfile.TemporaryDirectory() as tmp:
         results = []
-        for flag in ("0", "1"):
+        for flag in ("0", "1", "3", "5", "7"):  # off; on; + multicast commit; + 128-element K stages; both
             path = os.path.join(tmp, f"lse_{flag}.pt")
             env = dict(os.environ, CCE_B200_LSE_PAIR=flag, CCE_B200_DEBUG="1")
             subprocess.run([sys.executable, "-c", code, path], check=True, env=env, timeout=300)
             results.append(torch.load(path))
-    for a, b in zip(*results):
-        torch.testing.assert_close(a, b, rtol=0, atol=1e-5)
+    for other in results[1:]:
+        for a, b in zip(results[0], other):
+            torch.testing.assert_close(a, b, rtol=0, atol=1e-5)
 
 
 @pytest.mark.parametrize("shape", [(4, 32), (1, 1), (3, 2047), (7, 3001), (64, 1024), (2, 3, 500)])
