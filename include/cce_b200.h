@@ -94,6 +94,12 @@ int cce_b200_lse_forward(const cce_b200_operands* op, float* lse /* [n_rows] */,
  * softmax value is provably below filter_eps and no label falls.  (The reference keeps a
  * different by-product for its filter, the mean logit per column, cce_lse_forward.py:95-97.) */
 size_t cce_b200_tile_max_elems(const cce_b200_operands* op);
+/* Where cce_b200_lse_forward leaves its staged copy of e (the listed rows gathered into a dense
+ * [n_rows][pitch] 16-bit matrix, zero padded; made when `valids` is given or TMA cannot address e
+ * as it is): returns 1 and the byte offset inside the workspace and the row pitch in elements, 0 if
+ * the call stages nothing, negative on bad arguments.  A caller that keeps the forward's workspace
+ * alive can hand the copy to cce_b200_backward (e_packed), which then skips making its own. */
+int cce_b200_lse_packed_e(const cce_b200_operands* op, size_t* offset, int64_t* pitch);
 /* cce_b200_lse_forward with one more optional by-product: col_max_key [V] int32, the largest logit
  * (log2 units) of every vocabulary entry over all rows, stored as an order-preserving integer key
  * (a float f >= 0 as its bit pattern, f < 0 as its bit pattern with the low 31 bits inverted), so
@@ -217,6 +223,10 @@ typedef struct cce_b200_backward_args {
      * reordered copy of c in the workspace.  Both NULL: natural vocabulary order. */
     const int32_t* vocab_order;
     const int32_t* col_max_key;
+    /* Optional: the staged copy of e that cce_b200_lse_forward left in its workspace for the same
+     * operands (see cce_b200_lse_packed_e), with its row pitch in elements; NULL: staged here if needed. */
+    const void* e_packed;
+    int64_t e_packed_ld;
 } cce_b200_backward_args;
 
 /* Gradient of sum_i d_out_i * grad_scale * (lse_i - logit_i[t_i]) + sum_i d_lse_i * lse_i

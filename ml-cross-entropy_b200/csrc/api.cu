@@ -217,13 +217,14 @@ inline bool is_split(const cce_b200_operands* op) { return op->dtype == CCE_DT_F
 inline int compute_dtype(const cce_b200_operands* op) { return is_split(op) ? CCE_DT_BF16 : op->dtype; }
 
 struct OperandPlan {
-    bool pack_e, pad_c, bias32, split;
+    bool pack_e, pad_c, bias32, split, own_e;
     long long Dp;    // length (elements) of one padded block of columns, multiple of 8
     long long Drow;  // row length of the staged copies: Dp, or 3*Dp for split fp32 operands
     size_t off_e, off_c, off_bias, end;
 };
 
-OperandPlan plan_operands(const cce_b200_operands* op, size_t start) {
+// have_packed_e: the caller hands over the staged copy of e (the forward's), so none is made here
+OperandPlan plan_operands(const cce_b200_operands* op, size_t start, bool have_packed_e = false) {
     OperandPlan pl;
     pl.Dp = (op->D + 7) / 8 * 8;
     const bool d_ok = (op->D % 8 == 0);
@@ -232,10 +233,11 @@ OperandPlan plan_operands(const cce_b200_operands* op, size_t start) {
     pl.bias32 = op->bias && op->bias_dtype != CCE_DT_F32;
     pl.split = is_split(op);
     if (pl.split) pl.pack_e = pl.pad_c = true;
+    pl.own_e = pl.pack_e && !have_packed_e;  // this call makes the staged copy itself
     pl.Drow = pl.split ? 3 * pl.Dp : pl.Dp;
     size_t off = align_up(start, 256);
     pl.off_e = off;
-    if (pl.pack_e) off = align_up(off + (size_t)op->n_rows * pl.Drow * 2, 256);
+    if (pl.own_e) off = align_up(off + (size_t)op->n_rows * pl.Drow * 2, 256);
     pl.off_c = off;
     if (pl.pad_c) off = align_up(off + (size_t)op->V * pl.Drow * 2, 256);
     pl.off_bias = off;
@@ -255,14 +257,15 @@ struct Staged {
     long long blk;  // distance between the column blocks of a split row (Dp), 0 otherwise
 };
 
-int stage_operands(const cce_b200_operands* op, const OperandPlan& pl, char* ws, cudaStream_t st, Staged* out) {
+int stage_operands(const cce_b200_operands* op, const OperandPlan& pl, char* ws, cudaStream_t st, Staged* out,
+                   const void* e_packed = nullptr) {
     const long long* ndev = reinterpret_cast<const long long*>(op->n_rows_dev);
     out->Dk = out->Dmn = op->D;
     out->blk = 0;
     if (pl.split) {
         out->Dk = out->Dmn = pl.Drow;
         out->blk = pl.Dp;
-        if (op->n_rows > 0) {
+        if (op->n_rows > 0 && pl.own_e) {
             split_rows_kernel<<<(unsigned)op->n_rows, 128, 0, st>>>(
                 reinterpret_cast<const float*>(op->e), op->lde, op->valids, op->valids_dtype == CCE_IDX_I64,
                 reinterpret_cast<__nv_bfloat16*>(ws + pl.off_e), pl.Dp, op->D, op->n_rows, 0, ndev);
@@ -272,17 +275,17 @@ int stage_operands(const cce_b200_operands* op, const OperandPlan& pl, char* ws,
                                                           reinterpret_cast<__nv_bfloat16*>(ws + pl.off_c), pl.Dp,
                                                           op->D, op->V, 1, nullptr);
         CCE_LAUNCH_CHECK();
-        out->e = ws + pl.off_e;
+        out->e = pl.own_e ? ws + pl.off_e : e_packed;
         out->c = ws + pl.off_c;
         out->lde = out->ldc = pl.Drow;
     } else if (pl.pack_e) {
-        if (op->n_rows > 0) {
+        if (op->n_rows > 0 && pl.own_e) {
             pack_rows_kernel<<<(unsigned)op->n_rows, 128, 0, st>>>(
                 reinterpret_cast<const uint16_t*>(op->e), op->lde, op->valids, op->valids_dtype == CCE_IDX_I64,
                 reinterpret_cast<uint16_t*>(ws + pl.off_e), pl.Dp, op->D, op->n_rows, ndev);
             CCE_LAUNCH_CHECK();
         }
-        out->e = ws + pl.off_e;
+        out->e = pl.own_e ? ws + pl.off_e : e_packed;
         out->lde = pl.Dp;
     } else {
         out->e = op->e;
@@ -459,7 +462,7 @@ BwdPlan plan_bwd(const cce_b200_backward_args* a) {
     const cce_b200_operands* op = &a->op;
     BwdPlan pl;
     memset(&pl, 0, sizeof(pl));
-    pl.ops = plan_operands(op, kStatusBytes);
+    pl.ops = plan_operands(op, kStatusBytes, a->e_packed != nullptr);
     pl.n_rb = int(cdiv(op->n_rows, BM));
     pl.n_vt = int(cdiv(op->V, BN));
     size_t off = pl.ops.end;
@@ -652,6 +655,15 @@ int cce_b200_profile_read(double* ms, int64_t* launches) {
 size_t cce_b200_lse_workspace_bytes(const cce_b200_operands* op) {
     if (check_operands(op) != CCE_OK) return 0;
     return plan_lse(op).total;
+}
+
+int cce_b200_lse_packed_e(const cce_b200_operands* op, size_t* offset, int64_t* pitch) {
+    if (check_operands(op) != CCE_OK || !offset || !pitch) return CCE_ERR_ARG;
+    const LsePlan pl = plan_lse(op);
+    if (!pl.ops.pack_e) return 0;
+    *offset = pl.ops.off_e;
+    *pitch = pl.ops.Drow;
+    return 1;
 }
 
 size_t cce_b200_tile_max_elems(const cce_b200_operands* op) {
@@ -928,8 +940,11 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
         return CCE_OK;
     }
 
+    if (a->e_packed && pl.ops.pack_e &&
+        (a->e_packed_ld != pl.ops.Drow || (reinterpret_cast<uintptr_t>(a->e_packed) & 15)))
+        return CCE_ERR_ARG;  // not the staged copy cce_b200_lse_packed_e describes
     Staged sg;
-    rc = stage_operands(op, pl.ops, ws, st, &sg);
+    rc = stage_operands(op, pl.ops, ws, st, &sg, a->e_packed);
     if (rc != CCE_OK) return rc;
 
     // A vocabulary order (block-list form only): the products and the recomputation read a copy of the
@@ -1068,9 +1083,9 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
         rc = make_tmap_mn(&tmP_mn, g_buf, cdt, BN, (long long)pl.capacity * BM, BN, BM / 64, tma3_enabled(), &p_is3);
         if (rc != CCE_OK) return rc;
 
+        CCE_CUDA(cudaMemsetAsync(sflag_e, 0, (size_t)pl.capacity * 8, st));  // later passes: cleared by their reader
         for (int ps = 0; ps < pl.max_pass; ++ps) {
             const int* pinfo = pass_info + 4 * ps;
-            CCE_CUDA(cudaMemsetAsync(sflag_e, 0, (size_t)pl.capacity * 8, st));
             {
                 EngineParams p = pg;
                 p.sparse = 1;

@@ -482,13 +482,13 @@ __global__ void tile_index_kernel(const uint8_t* __restrict__ act, int n_rb, int
 }
 
 // After phase 1 of a pass: turn the slot flags into ordered K-block lists for the two products
-// (one warp per list).  Warps 0..n_rb-1 build the dE list of a row block: its slots that belong to
+// (one warp per list), clearing every flag it reads so that the next pass starts from zeros.  Warps 0..n_rb-1 build the dE list of a row block: its slots that belong to
 // the pass, vt ascending, 4 column groups each.  The next 2*n_vt warps build the dC list of a
 // (vt, 128-column half): its slots, rb ascending, 2 row halves each.  Layout: see EngineParams.
 __global__ void klist_build_kernel(const int* __restrict__ pass_info, const int* __restrict__ row_ptr,
                                    const int* __restrict__ row_slots, const int* __restrict__ col_ptr,
                                    const int* __restrict__ slot_tile, int n_rb, int n_vt,
-                                   const uint8_t* __restrict__ sflag_e, const uint8_t* __restrict__ sflag_c,
+                                   uint8_t* __restrict__ sflag_e, uint8_t* __restrict__ sflag_c,
                                    int2* __restrict__ de_list, int* __restrict__ de_cnt,
                                    int2* __restrict__ dc_list, int* __restrict__ dc_cnt) {
     const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -512,6 +512,7 @@ __global__ void klist_build_kernel(const int* __restrict__ pass_info, const int*
                 if (slot >= s_lo && slot < s_hi) {
                     const int sl = slot - s_lo, kb = c & 3;
                     on = sflag_e[sl * 4 + kb] != 0;
+                    if (on) sflag_e[sl * 4 + kb] = 0;  // each flag has one reader: leave it clear for the next pass
                     ent = make_int2(sl * 4 + kb, slot_tile[slot] % n_vt);
                 }
             }
@@ -533,6 +534,7 @@ __global__ void klist_build_kernel(const int* __restrict__ pass_info, const int*
                 if (c < n) {
                     const int slot = c0s + (c >> 1), sl = slot - s_lo, kb = c & 1;
                     on = sflag_c[sl * 4 + h * 2 + kb] != 0;
+                    if (on) sflag_c[sl * 4 + h * 2 + kb] = 0;
                     ent = make_int2(sl * 2 + kb, slot_tile[slot] / n_vt);
                 }
                 const uint32_t m = __ballot_sync(0xffffffffu, on);

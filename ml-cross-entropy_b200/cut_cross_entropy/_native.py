@@ -25,6 +25,7 @@ EXPORTS = (
     "cce_b200_lse_workspace_bytes",
     "cce_b200_lse_forward",
     "cce_b200_tile_max_elems",
+    "cce_b200_lse_packed_e",
     "cce_b200_lse_forward_ex",
     "cce_b200_logit_avg_workspace_bytes",
     "cce_b200_logit_avg",
@@ -95,6 +96,8 @@ class BackwardArgs(Structure):
         ("tile_max", c_void_p),
         ("vocab_order", c_void_p),
         ("col_max_key", c_void_p),
+        ("e_packed", c_void_p),
+        ("e_packed_ld", c_int64),
     ]
 
 
@@ -127,6 +130,8 @@ def lib() -> ctypes.CDLL:
     L.cce_b200_logit_avg_workspace_bytes.argtypes = [POINTER(Operands)]
     L.cce_b200_logit_avg.restype = c_int32
     L.cce_b200_logit_avg.argtypes = [POINTER(Operands), c_void_p, c_void_p, c_size_t, c_void_p]
+    L.cce_b200_lse_packed_e.restype = c_int32
+    L.cce_b200_lse_packed_e.argtypes = [POINTER(Operands), POINTER(c_size_t), POINTER(c_int64)]
     L.cce_b200_tile_max_elems.restype = c_size_t
     L.cce_b200_tile_max_elems.argtypes = [POINTER(Operands)]
     L.cce_b200_lse_forward_static.restype = c_int32

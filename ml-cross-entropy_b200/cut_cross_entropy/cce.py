@@ -142,6 +142,9 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
             params.valids, params.n_rows_dev = pending.rows, pending.count_dev
             pending = None
         n_dev = params.n_rows_dev
+        # the backward reads the same gathered rows of e: keep the forward's staged copy for it
+        # (only when e itself is what the backward will be given, i.e. no autocast cast happened)
+        want_packed_e = e_info.requires_grad or c_info.requires_grad or (bias_info is not None and bias_info.requires_grad)
         ret = cce_lse_forward_kernel(
             e=e,
             c=c,
@@ -153,6 +156,7 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
             return_logit_avg=order_mode == "mean",
             return_col_max=order_mode != "off",
             n_rows_dev=n_dev,
+            return_packed_e=want_packed_e,
         )
         if pending is not None:
             params.valids = pending.resolve()
@@ -161,6 +165,7 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
         logit_avg = ret.pop(0) if order_mode == "mean" else None
         tile_max = ret.pop(0) if want_tile_max else None
         col_max = ret.pop(0) if order_mode != "off" else None
+        packed_e = ret.pop(0) if want_packed_e else None
         order_key = logit_avg if order_mode == "mean" else col_max
         assert isinstance(lse, torch.Tensor)
         n_rows = lse.numel()
@@ -201,7 +206,7 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
         else:
             lse = stats[0, 0]
 
-        ctx.save_for_backward(e, c, bias, lse, params.targets, params.valids, tile_max, col_max, order_key, n_dev)
+        ctx.save_for_backward(e, c, bias, lse, params.targets, params.valids, tile_max, col_max, order_key, n_dev, packed_e)
         ctx.params = params
         ctx.e_info, ctx.c_info, ctx.bias_info = e_info, c_info, bias_info
         return loss, lse_out
@@ -211,7 +216,7 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
     def backward(
         ctx, grad_out: torch.Tensor, grad_lse_out: torch.Tensor | None
     ) -> tuple[torch.Tensor | None, torch.Tensor | None, torch.Tensor | None, None]:
-        e, c, bias, lse, targets, valids, tile_max, col_max, order_key, n_dev = ctx.saved_tensors
+        e, c, bias, lse, targets, valids, tile_max, col_max, order_key, n_dev, packed_e = ctx.saved_tensors
         # integer keys (column maxima) and float keys (mean logits) both sort with the hottest entry first
         vocab_ordering = sort_logit_avg(order_key) if order_key is not None else None
         params = cast(CCEParams, ctx.params)
@@ -257,6 +262,7 @@ class LinearCrossEntropyFunction(torch.autograd.Function):
             col_max=col_max,
             n_rows_dev=n_dev,
             scale_by_inv_rows=n_dev is not None and params.reduction == "mean",
+            packed_e=packed_e,
         )
         return de, dc, dbias, None
 

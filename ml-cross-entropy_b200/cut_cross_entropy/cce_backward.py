@@ -18,7 +18,7 @@ from .vocab_parallel.utils import vp_reduce_e_grad_
 
 def _launch(do, dlse, e, c, bias, lse, valids, softcap, filter_eps, targets, shift, grad_scale,
             filter_e, filter_c, vocab_start, de, dc, dbias, tile_max=None, vocab_ordering=None, col_max=None,
-            n_rows_dev=None, scale_by_inv_rows=False) -> None:
+            n_rows_dev=None, scale_by_inv_rows=False, packed_e=None) -> None:
     """Fill the (pre-allocated, possibly ``None``) outputs ``de``/``dc``/``dbias`` through the C ABI."""
     dev = e.device
     a = _native.BackwardArgs()
@@ -32,6 +32,8 @@ def _launch(do, dlse, e, c, bias, lse, valids, softcap, filter_eps, targets, shi
     a.d_lse = _native._ptr(dlse)
     a.grad_scale = grad_scale
     a.grad_scale_by_inv_rows = int(scale_by_inv_rows)
+    if packed_e is not None:
+        a.e_packed, a.e_packed_ld = packed_e.data_ptr(), packed_e.stride(0)
     a.has_filter = int(filter_eps is not None)
     a.filter_eps = float(filter_eps) if filter_eps is not None else 0.0
     a.filter_e = int(filter_e)
@@ -80,6 +82,7 @@ def cce_backward_kernel(
     col_max: torch.Tensor | None = None,
     n_rows_dev: torch.Tensor | None = None,
     scale_by_inv_rows: bool = False,
+    packed_e: torch.Tensor | None = None,
 ) -> tuple[torch.Tensor | None, torch.Tensor | None, torch.Tensor | None]:
     """Returns ``(de, dc, dbias)``, each ``None`` unless its ``*_info.requires_grad``.
 
@@ -96,6 +99,8 @@ def cce_backward_kernel(
     ``n_rows_dev`` (one int64 on the device) is the number of valid rows when the host never read
     it (``valids`` and ``lse`` are then sized for all rows); ``scale_by_inv_rows`` divides
     ``grad_scale`` by that number on the device (``reduction="mean"``).
+    ``packed_e`` is the staged copy of ``e`` from ``cce_lse_forward_kernel(return_packed_e=True)``
+    for the same ``e`` and ``valids``.
     ``tile_max`` / ``col_max`` are the optional by-products of
     ``cce_lse_forward_kernel(return_tile_max=True, return_col_max=True)``.
     """
@@ -138,7 +143,7 @@ def cce_backward_kernel(
     if want_de or want_dc or want_dbias:
         _launch(do, dlse, e, c, bias, lse, valids, softcap, filter_eps, targets, int(shift), float(grad_scale),
                 bool(filter_e_grad), bool(filter_c_grad), int(vocab_start), de, dc, dbias, tile_max,
-                vocab_ordering, col_max, n_rows_dev, bool(scale_by_inv_rows))
+                vocab_ordering, col_max, n_rows_dev, bool(scale_by_inv_rows), packed_e)
 
     if de_f32:
         assert de is not None

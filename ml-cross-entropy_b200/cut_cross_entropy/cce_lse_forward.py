@@ -24,6 +24,7 @@ def cce_lse_forward_kernel(
     stats_flat: torch.Tensor | None = None,
     return_col_max: bool = False,
     n_rows_dev: torch.Tensor | None = None,
+    return_packed_e: bool = False,
 ) -> tuple[torch.Tensor, ...] | torch.Tensor:
     """``lse[i] = logsumexp_v(softcap(e[valids[i]] @ c[v] + bias[v]))`` as float32 ``[B]``.
 
@@ -51,7 +52,12 @@ def cce_lse_forward_kernel(
     ``valids`` is then the whole list buffer, the result has one slot per entry of that buffer and
     only the first ``n_rows_dev`` are written.
 
-    Returns ``lse`` alone, or a tuple ``(lse[, logit_avg][, tile_max][, col_max])`` of what was asked for.
+    ``return_packed_e`` adds the staged copy of ``e`` the kernel made in its workspace (the valid
+    rows gathered into a dense matrix; ``None`` when it read ``e`` in place), which the backward
+    launcher accepts so that it need not gather the same rows again.
+
+    Returns ``lse`` alone, or a tuple ``(lse[, logit_avg][, tile_max][, col_max][, packed_e])`` of what
+    was asked for.
     """
     assert e.shape[1] == c.shape[1], "Incompatible dimensions"
     assert e.is_contiguous(), "Matrix A must be contiguous"
@@ -102,5 +108,14 @@ def cce_lse_forward_kernel(
             rc = L.cce_b200_logit_avg(op, logit_avg.data_ptr(), ws2.data_ptr(), ws2.numel(), stream)
             _native.check(rc, "cce_b200_logit_avg")
     _native.finish(ws, "cce_b200_lse_forward")
-    extras = [x for x, want in ((logit_avg, return_logit_avg), (tile_max, return_tile_max), (col_max, return_col_max)) if want]
+    packed_e = None
+    if return_packed_e:
+        import ctypes
+
+        off, pitch = ctypes.c_size_t(0), ctypes.c_int64(0)
+        if L.cce_b200_lse_packed_e(op, ctypes.byref(off), ctypes.byref(pitch)) == 1 and op.n_rows > 0:
+            nbytes = op.n_rows * pitch.value * 2
+            packed_e = ws[off.value : off.value + nbytes].view(torch.int16).view(op.n_rows, pitch.value)
+    extras = [x for x, want in ((logit_avg, return_logit_avg), (tile_max, return_tile_max),
+                                (col_max, return_col_max), (packed_e, return_packed_e)) if want]  # fmt: skip
     return (lse, *extras) if extras else lse

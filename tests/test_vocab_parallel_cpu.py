@@ -63,9 +63,10 @@ def _install_cpu_stand_ins():
     import cut_cross_entropy.cce_backward as bwd_mod
 
     def lse_kernel(e, c, bias=None, valids=None, softcap=None, return_logit_avg=False, return_tile_max=False,
-                   stats_flat=None, return_col_max=False, n_rows_dev=None):
+                   stats_flat=None, return_col_max=False, n_rows_dev=None, return_packed_e=False):
         assert not return_tile_max and not return_col_max and not return_logit_avg
-        return O.lse_forward(e, c, bias, valids, softcap).float()
+        lse = O.lse_forward(e, c, bias, valids, softcap).float()
+        return (lse, None) if return_packed_e else lse  # no staged copy of e on this stand-in
 
     def dot_kernel(e, c, inds, bias=None, shift=0, valids=None, softcap=None, out_dtype=None, vocab_start=0,
                    out=None, n_rows_dev=None):
@@ -89,7 +90,7 @@ def _install_cpu_stand_ins():
 
     def launch(do, dlse, e, c, bias, lse, valids, softcap, filter_eps, targets, shift, grad_scale,
                filter_e, filter_c, vocab_start, de, dc, dbias, tile_max=None, vocab_ordering=None, col_max=None,
-               n_rows_dev=None, scale_by_inv_rows=False):
+               n_rows_dev=None, scale_by_inv_rows=False, packed_e=None):
         # restates one rank of cce_backward.py:182-310 with the global lse
         n = e.size(0)
         rows = torch.arange(n) if valids is None else valids.long()
