@@ -76,16 +76,14 @@ EncodeTiledFn get_encode() {
     return fn;
 }
 
-// CCE_B200_LSE_PAIR=<n> selects the two-CTA (cta_group::2) forward kernel; read once.
-// bit 0: on; bit 1: one multicast commit per event instead of one commit per CTA; bit 2: 128 K elements per stage.
-int cta_pair_mode() {
-    static const int mode = [] {
-        const char* env = getenv("CCE_B200_LSE_PAIR");
-        return env ? atoi(env) : 0;
+// The dense launches run on CTA pairs (engine_pair.cuh) unless CCE_B200_PAIR=0; read once.
+bool pair_enabled() {
+    static const bool on = [] {
+        const char* env = getenv("CCE_B200_PAIR");
+        return !(env && env[0] == '0');
     }();
-    return mode;
+    return on;
 }
-bool use_cta_pairs() { return (cta_pair_mode() & 1) != 0; }
 
 struct DeviceInfo {
     int sms = 0;
@@ -114,8 +112,12 @@ int device_info(DeviceInfo** out) {
                                       ENGINE_SMEM));
         CCE_CUDA(cudaFuncSetAttribute(engine_kernel<MODE_GEMM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       ENGINE_SMEM));
-        CCE_CUDA(cudaFuncSetAttribute(lse_pair_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg<1>::SMEM));
-        CCE_CUDA(cudaFuncSetAttribute(lse_pair_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg<2>::SMEM));
+        CCE_CUDA(cudaFuncSetAttribute(pair_engine_kernel<MODE_LSE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      PAIR_SMEM));
+        CCE_CUDA(cudaFuncSetAttribute(pair_engine_kernel<MODE_PGRAD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      PAIR_SMEM));
+        CCE_CUDA(cudaFuncSetAttribute(pair_engine_kernel<MODE_GEMM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      PAIR_SMEM));
         d.attr_set = true;
     }
     *out = &d;
@@ -344,15 +346,19 @@ LsePlan plan_lse(const cce_b200_operands* op) {
     return pl;
 }
 
+// pair: run on CTA pairs (dense launches only; the B-side tensor map then has boxes of 128 rows, not 256)
 template <int MODE>
-int launch_engine(const CUtensorMap& a, const CUtensorMap& b, const EngineParams& p, int sms, cudaStream_t st) {
+int launch_engine(const CUtensorMap& a, const CUtensorMap& b, const EngineParams& p, int sms, cudaStream_t st,
+                  bool pair = false) {
+    const long long m_units = pair ? cdiv(p.n_mblk, 2) : p.n_mblk;
     long long items;
     if (MODE == MODE_LSE)
-        items = cdiv(p.n_nblk, p.band_len) * p.n_mblk;
+        items = cdiv(p.n_nblk, p.band_len) * m_units;
     else
-        items = (long long)p.n_mblk * p.n_nblk;
+        items = m_units * p.n_nblk;
     if (items <= 0) return CCE_OK;
-    const unsigned grid = (unsigned)(items < sms ? items : sms);
+    const long long units = pair ? sms / 2 : sms;
+    const unsigned grid = (unsigned)(items < units ? items : units) * (pair ? 2u : 1u);
     ProfRecord rec{nullptr, nullptr, MODE};
     bool prof = false;
     EngineParams pp = p;
@@ -367,7 +373,12 @@ int launch_engine(const CUtensorMap& a, const CUtensorMap& b, const EngineParams
         CCE_CUDA(cudaEventCreate(&rec.stop));
         CCE_CUDA(cudaEventRecord(rec.start, st));
     }
-    engine_kernel<MODE><<<grid, ENGINE_THREADS, ENGINE_SMEM, st>>>(a, b, pp);
+    if (pair) {
+        pp.idesc = (pp.idesc & ~(0x1fu << 24)) | ((uint32_t(2 * BM) >> 4) << 24);  // M = 256 over the pair
+        pair_engine_kernel<MODE><<<grid, ENGINE_THREADS, PAIR_SMEM, st>>>(a, b, pp);
+    } else {
+        engine_kernel<MODE><<<grid, ENGINE_THREADS, ENGINE_SMEM, st>>>(a, b, pp);
+    }
     CCE_LAUNCH_CHECK();
     if (prof) {
         CCE_CUDA(cudaEventRecord(rec.stop, st));
@@ -715,47 +726,14 @@ int cce_b200_lse_forward_ex(const cce_b200_operands* op, float* lse, float* tile
     p.tile_max = tile_max;
     p.col_max_key = col_max_key;
     p.m_dev = reinterpret_cast<const long long*>(op->n_rows_dev);
-    if (use_cta_pairs() && !col_max_key && !p.m_dev) {
-        // two-CTA form: each CTA of a pair stages 128 rows of each operand, the MMA is M = 256
+    // CTA pairs need two row blocks to share a tile
+    const bool pair = pair_enabled() && p.n_mblk >= 2 && dev->sms >= 2;
+    if (pair) {  // each CTA of a pair stages 128 of the tile's 256 classifier rows
         rc = make_tmap(&tmB, sg.c, cdt, sg.Dk, op->V, sg.ldc, BK, BN / 2);
         if (rc != CCE_OK) return rc;
-        p.idesc = make_idesc(cdt == CCE_DT_BF16 ? 1u : 0u, 0, 0, 2 * BM, BN);
-        const long long items = cdiv(p.n_nblk, p.band_len) * cdiv(p.n_mblk, 2);
-        const long long pairs = std::min<long long>(items, dev->sms / 2);
-        ProfRecord rec{nullptr, nullptr, MODE_LSE};
-        bool prof = false;
-        {
-            std::lock_guard<std::mutex> lock(g_prof_mu);
-            prof = g_prof_on;
-        }
-        if (prof) {
-            CCE_CUDA(cudaEventCreate(&rec.start));
-            CCE_CUDA(cudaEventCreate(&rec.stop));
-            CCE_CUDA(cudaEventRecord(rec.start, st));
-        }
-        {
-            std::lock_guard<std::mutex> lock(g_prof_mu);
-            if (g_wait_counters) p.wait_cycles = g_wait_counters;
-        }
-        {
-            std::lock_guard<std::mutex> lock(g_prof_mu);
-            if (g_clk_words) p.clk_words = g_clk_words;
-        }
-        const int mc = (cta_pair_mode() >> 1) & 1;
-        if (cta_pair_mode() & 4)
-            lse_pair_kernel<2><<<(unsigned)(2 * pairs), ENGINE_THREADS, PairCfg<2>::SMEM, st>>>(tmA, tmB, p, mc);
-        else
-            lse_pair_kernel<1><<<(unsigned)(2 * pairs), ENGINE_THREADS, PairCfg<1>::SMEM, st>>>(tmA, tmB, p, mc);
-        CCE_LAUNCH_CHECK();
-        if (prof) {
-            CCE_CUDA(cudaEventRecord(rec.stop, st));
-            std::lock_guard<std::mutex> lock(g_prof_mu);
-            g_prof.push_back(rec);
-        }
-    } else {
-        rc = launch_engine<MODE_LSE>(tmA, tmB, p, dev->sms, st);
-        if (rc != CCE_OK) return rc;
     }
+    rc = launch_engine<MODE_LSE>(tmA, tmB, p, dev->sms, st, pair);
+    if (rc != CCE_OK) return rc;
 
     lse_combine_kernel<<<(unsigned)cdiv(op->n_rows, 256), 256, 0, st>>>(p.partial, pl.n_band, op->n_rows, lse,
                                                                         reinterpret_cast<const int*>(ws), p.m_dev);
@@ -989,24 +967,45 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
     rc = make_tmap_mn(&tmC_mn, sg.c, cdt, sg.Dmn, V, sg.ldc, BN / 64, mn3, &c_is3);
     if (rc != CCE_OK) return rc;
 
+    // Dense launches that take every K block run on CTA pairs: each CTA stages 128 of the B side's 256 rows
+    const bool can_pair = pair_enabled() && !pl.sparse && dev->sms >= 2;
+    CUtensorMap tmC_k_h, tmE_mn_h, tmC_mn_h;
+    if (can_pair) {
+        int is3 = 0;
+        rc = make_tmap(&tmC_k_h, sg.c, cdt, sg.Dk, V, sg.ldc, BK, BN / 2);
+        if (rc != CCE_OK) return rc;
+        if (e_is3) rc = make_tmap_mn(&tmE_mn_h, sg.e, cdt, sg.Dmn, B, sg.lde, BN / 128, true, &is3);
+        if (rc != CCE_OK) return rc;
+        if (c_is3) rc = make_tmap_mn(&tmC_mn_h, sg.c, cdt, sg.Dmn, V, sg.ldc, BN / 128, true, &is3);
+        if (rc != CCE_OK) return rc;
+    }
+    // a product runs on pairs when nothing is skipped, both MN-major operands have 3-D maps, and two row blocks exist
+    auto pair_ok = [&](const EngineParams& p, int b_is3) {
+        return can_pair && !p.kflags && !p.sparse && p.n_mblk >= 2 && b_is3 && (!p.a_mn_major || p.a_tma3);
+    };
+
     // The two products.  With split fp32 operands the staged rows hold three column blocks
     // ([hi|hi|lo] for e, [hi|lo|hi] for c): dC = G^T e_hi + G^T e_lo and dE = G c_hi + G c_lo, i.e. the
     // same launch run twice on different column blocks of the B operand, the second adding in fp32.
     auto run_dc = [&](EngineParams p, const CUtensorMap& tmA) -> int {
         p.b_tma3 = e_is3;
-        int r = launch_engine<MODE_GEMM>(tmA, tmE_mn, p, dev->sms, st);
+        const bool pair = pair_ok(p, e_is3);
+        const CUtensorMap& tmB = pair ? tmE_mn_h : tmE_mn;
+        int r = launch_engine<MODE_GEMM>(tmA, tmB, p, dev->sms, st, pair);
         if (r != CCE_OK || !split) return r;
         p.b_mn_off = int(2 * sg.blk);
         p.accumulate = 2;
-        return launch_engine<MODE_GEMM>(tmA, tmE_mn, p, dev->sms, st);
+        return launch_engine<MODE_GEMM>(tmA, tmB, p, dev->sms, st, pair);
     };
     auto run_de = [&](EngineParams p, const CUtensorMap& tmA) -> int {
         p.b_tma3 = c_is3;
-        int r = launch_engine<MODE_GEMM>(tmA, tmC_mn, p, dev->sms, st);
+        const bool pair = pair_ok(p, c_is3);
+        const CUtensorMap& tmB = pair ? tmC_mn_h : tmC_mn;
+        int r = launch_engine<MODE_GEMM>(tmA, tmB, p, dev->sms, st, pair);
         if (r != CCE_OK || !split) return r;
         p.b_mn_off = int(sg.blk);
         p.accumulate = 2;
-        return launch_engine<MODE_GEMM>(tmA, tmC_mn, p, dev->sms, st);
+        return launch_engine<MODE_GEMM>(tmA, tmB, p, dev->sms, st, pair);
     };
 
     // phase-1 parameters shared by both shapes
@@ -1159,7 +1158,8 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
                 p.ld_flag_e = pl.ld_flag_e;
                 p.flag_c = flag_c;
                 p.ld_flag_c = pl.ld_flag_c;
-                rc = launch_engine<MODE_PGRAD>(tmE_k, tmC_k, p, dev->sms, st);
+                const bool pair = can_pair && p.n_mblk >= 2;
+                rc = launch_engine<MODE_PGRAD>(tmE_k, pair ? tmC_k_h : tmC_k, p, dev->sms, st, pair);
                 if (rc != CCE_OK) return rc;
             }
 
@@ -1275,11 +1275,16 @@ int cce_b200_gemm(const void* A, const void* Bm, void* out, int64_t M, int64_t N
     else
         rc = make_tmap_mn(&tmA, A, dtype, M, K, lda, BM / 64, tma3_enabled() && M % 64 == 0, &a_is3);
     if (rc != CCE_OK) return rc;
+    // CTA pairs when nothing is skipped, two row blocks exist and MN-major operands have 3-D maps
+    const bool pair = pair_enabled() && !kflags && M > BM && dev->sms >= 2 && (!a_mn || a_is3) &&
+                      (!b_mn || (tma3_enabled() && N % 64 == 0));
+    const int b_rows = pair ? BN / 2 : BN;  // rows of the B side each CTA stages
     if (!b_mn)
-        rc = make_tmap(&tmB, Bm, dtype, K, N, ldb, BK, BN);
+        rc = make_tmap(&tmB, Bm, dtype, K, N, ldb, BK, b_rows);
     else
-        rc = make_tmap_mn(&tmB, Bm, dtype, N, K, ldb, BN / 64, tma3_enabled() && N % 64 == 0, &b_is3);
+        rc = make_tmap_mn(&tmB, Bm, dtype, N, K, ldb, b_rows / 64, tma3_enabled() && N % 64 == 0, &b_is3);
     if (rc != CCE_OK) return rc;
+    if (pair && b_mn && !b_is3) return CCE_ERR_CUDA;  // the 3-D map the pair form needs was refused
     if (status) CCE_CUDA(cudaMemsetAsync(status, 0, 4, st));
     EngineParams p;
     base_params(&p, M, N, K, dtype, a_mn, b_mn, status);
@@ -1291,7 +1296,7 @@ int cce_b200_gemm(const void* A, const void* Bm, void* out, int64_t M, int64_t N
     p.ld_kflags = int(cdiv(K, BK));
     p.a_tma3 = a_is3;
     p.b_tma3 = b_is3;
-    return launch_engine<MODE_GEMM>(tmA, tmB, p, dev->sms, st);
+    return launch_engine<MODE_GEMM>(tmA, tmB, p, dev->sms, st, pair);
 }
 
 }  // extern "C"

@@ -628,8 +628,12 @@ __device__ __forceinline__ void gemm_store_chunk(const EngineParams& p, int row,
     }
 }
 
-template <int MODE>
-__device__ void epilogue_loop(const EngineParams& p, const EngineSmem& s, uint32_t tmem_base) {
+// The epilogue warps' loop.  `it` walks this CTA's tiles (TileIter, or the pair form's iterator);
+// tempty_bar[a] is the (shared::cluster) address of the barrier that hands accumulator a back to the
+// MMA issuer, which in the two-CTA form lives in the pair's leader CTA.
+template <int MODE, class Iter>
+__device__ void epilogue_loop(const EngineParams& p, const EngineSmem& s, uint32_t tmem_base, Iter& it,
+                              const Dyn& dyn, const uint32_t (&tempty_bar)[2]) {
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int q = warp & 3;  // TMEM lane quarter this warp may read
@@ -641,9 +645,6 @@ __device__ void epilogue_loop(const EngineParams& p, const EngineSmem& s, uint32
     float run_m = -INFINITY, run_s = 0.0f;
     long long waited_epi = 0;
 
-    const PassInfo pass = load_pass(p);
-    const Dyn dyn = load_dyn(p);
-    TileIter<MODE> it(p, pass, dyn);
     while (it.next()) {
         const int row = it.mblk * BM + q * 32 + lane;
         const bool row_ok = row < dyn.M;
@@ -682,8 +683,8 @@ __device__ void epilogue_loop(const EngineParams& p, const EngineSmem& s, uint32
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) return;
         tc_fence_after();
-        const bool acc_is_empty =
-            (MODE == MODE_GEMM) ? (reinterpret_cast<volatile int*>(s.acc_empty)[acc] != 0) : false;
+        const bool acc_is_empty =  // every K block skipped, or a reduction of length zero
+            (MODE == MODE_GEMM) ? (reinterpret_cast<volatile int*>(s.acc_empty)[acc] != 0 || dyn.n_kblk == 0) : false;
         const uint32_t taddr = tmem_base + acc * BN + (uint32_t(q * 32) << 16);
 
         float tile_rowmax = -INFINITY;  // MODE_LSE: max logit (log2 units) of this row within the tile
@@ -835,9 +836,9 @@ __device__ void epilogue_loop(const EngineParams& p, const EngineSmem& s, uint32
         // accumulator consumed: hand it back to the MMA warp
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&s.tempty[acc]));
+        if (lane == 0) mbar_arrive_cluster(tempty_bar[acc]);
         if (MODE == MODE_LSE) {
-            if (p.tile_max) {
+            if (p.tile_max && it.mblk < dyn.n_mblk) {
                 float m = row_ok ? tile_rowmax : -INFINITY;
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
@@ -921,7 +922,11 @@ engine_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
     } else if (warp == 1) {
         mma_loop<MODE>(p, s, tmem_base);
     } else {
-        epilogue_loop<MODE>(p, s, tmem_base);
+        const PassInfo pass = load_pass(p);
+        const Dyn dyn = load_dyn(p);
+        TileIter<MODE> it(p, pass, dyn);
+        const uint32_t tempty_bar[2] = {smem_u32(&s.tempty[0]), smem_u32(&s.tempty[1])};  // this CTA's own
+        epilogue_loop<MODE>(p, s, tmem_base, it, dyn, tempty_bar);
     }
 
     // tear-down: wait (bounded) for every MMA this CTA issued, then release TMEM

@@ -180,9 +180,11 @@ def test_workspace_too_small_and_bad_arguments_are_reported():
         _native.check(rc, "lse")
 
 
-def test_two_cta_forward_kernel_matches_the_default_one():
-    """CCE_B200_LSE_PAIR=1 selects the cta_group::2 forward kernel (a cluster of two CTAs per
-    256x256 tile).  The switch is read once per process, so the comparison runs in a child."""
+def test_single_cta_pipeline_matches_the_cta_pair_one():
+    """Dense launches run on CTA pairs (tcgen05 cta_group::2, a cluster of two CTAs per 256x256 tile)
+    by default; CCE_B200_PAIR=0 keeps every launch on the single-CTA pipeline.  The switch is read
+    once per process, so both run in children: forward by-products, exact gradients and the GEMM
+    hook must agree (same products, same fp32 accumulation order within a tile)."""
     import os
     import subprocess
     import sys
@@ -193,26 +195,35 @@ def test_two_cta_forward_kernel_matches_the_default_one():
         "import sys, torch\n"
         f"sys.path[:0] = [r'{root / 'ml-cross-entropy_b200'}', r'{root / 'tests'}', r'{root}']\n"
         "from conftest import planted_inputs\n"
+        "from cut_cross_entropy import linear_cross_entropy\n"
         "from cut_cross_entropy.cce_lse_forward import cce_lse_forward_kernel\n"
         "out = []\n"
-        "for n, v, d, sc in ((1000, 5000, 256, None), (255, 507, 123, 20.0), (385, 1300, 512, None)):\n"
-        "    e, c, b, _ = planted_inputs(n, v, d, torch.bfloat16, 'cuda', seed=n, bias=True)\n"
-        "    lse, tm = cce_lse_forward_kernel(e, c, b.float(), softcap=sc, return_tile_max=True)\n"
-        "    out += [lse.cpu(), tm.cpu()]\n"
+        "for n, v, d, sc in ((1000, 5000, 256, None), (255, 507, 123, 20.0), (385, 1300, 512, None), (700, 2500, 192, 25.0)):\n"
+        "    e, c, b, t = planted_inputs(n, v, d, torch.bfloat16, 'cuda', seed=n, bias=True, ignored=0.1)\n"
+        "    lse, tm, cm = cce_lse_forward_kernel(e, c, b.float(), softcap=sc, return_tile_max=True, return_col_max=True)\n"
+        "    out += [lse.cpu(), tm.cpu(), cm.cpu()]\n"
+        "    e.requires_grad_(True); c.requires_grad_(True); bf = b.float().requires_grad_(True)\n"
+        "    for impl in ('cce_exact', 'cce_kahan_full_c'):\n"
+        "        e.grad = c.grad = bf.grad = None\n"
+        "        linear_cross_entropy(e, c, t, bias=bf, softcap=sc, impl=impl).backward()\n"
+        "        out += [e.grad.float().cpu(), c.grad.float().cpu(), bf.grad.cpu()]\n"
         "torch.save(out, sys.argv[1])\n"
     )
     import tempfile
 
     with tempfile.TemporaryDirectory() as tmp:
         results = []
-        for flag in ("0", "1", "3", "5", "7"):  # off; on; + multicast commit; + 128-element K stages; both
-            path = os.path.join(tmp, f"lse_{flag}.pt")
-            env = dict(os.environ, CCE_B200_LSE_PAIR=flag, CCE_B200_DEBUG="1")
+        for flag in ("0", "1"):
+            path = os.path.join(tmp, f"out_{flag}.pt")
+            env = dict(os.environ, CCE_B200_PAIR=flag, CCE_B200_DEBUG="1", CCE_B200_GBUF_MB="1")
             subprocess.run([sys.executable, "-c", code, path], check=True, env=env, timeout=300)
             results.append(torch.load(path))
-    for other in results[1:]:
-        for a, b in zip(results[0], other):
-            torch.testing.assert_close(a, b, rtol=0, atol=1e-5)
+    assert len(results[0]) == len(results[1]) and len(results[0]) > 0
+    for a, b in zip(*results):
+        if a.dtype == torch.int32:
+            assert torch.equal(a, b)
+        else:
+            torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-6 * max(1.0, float(a.abs().max())))
 
 
 @pytest.mark.parametrize("shape", [(4, 32), (1, 1), (3, 2047), (7, 3001), (64, 1024), (2, 3, 500)])
