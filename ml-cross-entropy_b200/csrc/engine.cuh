@@ -806,9 +806,10 @@ __device__ void epilogue_loop(const EngineParams& p, const EngineSmem& s, uint32
                         char* dst = reinterpret_cast<char*>(p.g_out) +
                                     (((size_t)it.slot * BM + q * 32 + lane) * BN + c * 32) * 2;
                         store_g16(dst, g, p.g_is_bf16 != 0);
-                    } else {
-                        // rows past the count (within a visited block of 128) are stored as zeros, so
-                        // that the products never meet stale values there
+                    } else if (row < p.n_mblk * BM) {
+                        // rows past the count (within the buffer's blocks of 128) are stored as zeros,
+                        // so that the products never meet stale values there; a CTA pair's second
+                        // block may lie past the buffer altogether
                         char* dst = reinterpret_cast<char*>(p.g_out) + ((size_t)row * p.ldg + col0) * 2;
                         store_g16(dst, g, p.g_is_bf16 != 0);
                     }
