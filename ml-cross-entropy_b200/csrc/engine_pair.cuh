@@ -85,29 +85,28 @@ struct PairTileIter {
 
 // Walks the K blocks of a tile in ascending order and hands them to `stage_fn(kbs, n)` in groups of
 // up to P_KSUB (one ring stage each).  The producers of both CTAs and the MMA issuer call this with
-// the same arguments and so see the same sequence of stages.  stage_fn runs on lane 0 and returns 0
-// to abandon the walk; the warp gets the outcome.
+// the same arguments and so see the same sequence of stages.  Called by one thread; stage_fn
+// returns 0 to abandon the walk, and so does this.
 template <class F>
 __device__ __forceinline__ bool pair_walk_k(const Dyn& dyn, F&& stage_fn) {
-    int ok = 1;
-    if ((threadIdx.x & 31) == 0) {
-        int kbs[P_KSUB];
-        int pend = 0;
-        for (int kb = 0; kb < dyn.n_kblk && ok; ++kb) {
-            kbs[pend++] = kb;
-            if (pend == P_KSUB) {
-                ok = stage_fn(kbs, pend);
-                pend = 0;
-            }
-        }
-        if (ok && pend) ok = stage_fn(kbs, pend);
+    int kbs[P_KSUB];
+    int kb = 0;
+    for (; kb + P_KSUB <= dyn.n_kblk; kb += P_KSUB) {
+#pragma unroll
+        for (int j = 0; j < P_KSUB; ++j) kbs[j] = kb + j;
+        if (!stage_fn(kbs, P_KSUB)) return false;
     }
-    return __shfl_sync(0xffffffffu, ok, 0) != 0;
+    if (kb < dyn.n_kblk) {
+        kbs[0] = kb;
+        if (!stage_fn(kbs, 1)) return false;
+    }
+    return true;
 }
 
 template <int MODE>
 __device__ void pair_producer(const CUtensorMap* tmA, const CUtensorMap* tmB, const EngineParams& p,
                               const EngineSmem& s, const Dyn& dyn, uint32_t rank) {
+    if ((threadIdx.x & 31) != 0) return;  // one lane runs the whole loop
     int stage = 0;
     uint32_t phase = 0;
     PairTileIter<MODE> it(p, dyn, int(rank));
@@ -120,7 +119,9 @@ __device__ void pair_producer(const CUtensorMap* tmA, const CUtensorMap* tmB, co
             const uint32_t bar_leader = map_to_cta(bar_local, 0);
             const uint32_t sa = smem_u32(s.stages + stage * P_STAGE_BYTES);
             if (rank == 0) mbar_expect_tx(bar_local, uint32_t(n) * 4u * P_SUB_BYTES);  // both operands, both CTAs
-            for (int j = 0; j < n; ++j) {
+#pragma unroll
+            for (int j = 0; j < P_KSUB; ++j) {
+                if (j >= n) break;
                 const int a_k = p.a_k_off + kbs[j] * BK, b_k = p.b_k_off + kbs[j] * BK;
                 const uint32_t da = sa + j * P_SUB_BYTES, db = sa + P_OPER_BYTES + j * P_SUB_BYTES;
                 if (!p.a_mn_major)
@@ -142,10 +143,10 @@ __device__ void pair_producer(const CUtensorMap* tmA, const CUtensorMap* tmB, co
     }
 }
 
-// leader CTA only
+// leader CTA only; one lane runs the whole loop
 template <int MODE>
 __device__ void pair_mma(const EngineParams& p, const EngineSmem& s, const Dyn& dyn, uint32_t tmem_base) {
-    const int lane = threadIdx.x & 31;
+    if ((threadIdx.x & 31) != 0) return;
     int stage = 0;
     uint32_t phase = 0;
     int acc = 0;
@@ -169,10 +170,7 @@ __device__ void pair_mma(const EngineParams& p, const EngineSmem& s, const Dyn& 
     const uint32_t tfull_peer[2] = {map_to_cta(tfull_bar[0], 1), map_to_cta(tfull_bar[1], 1)};
     PairTileIter<MODE> it(p, dyn, 0);
     while (it.next()) {
-        int ok = 1;
-        if (lane == 0)
-            ok = mbar_wait(smem_u32(&s.tempty[acc]), acc_phase ^ 1u, s.abort_flag, p.status, ERR_WAIT_TMEM_EMPTY);
-        if (!__shfl_sync(0xffffffffu, ok, 0)) return;
+        if (!mbar_wait(smem_u32(&s.tempty[acc]), acc_phase ^ 1u, s.abort_flag, p.status, ERR_WAIT_TMEM_EMPTY)) return;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         int n_issued = 0;
@@ -191,7 +189,9 @@ __device__ void pair_mma(const EngineParams& p, const EngineSmem& s, const Dyn& 
             }
             if (!mbar_wait(fb, phase, s.abort_flag, p.status, ERR_WAIT_SMEM_FULL)) return 0;
             tc_fence_after();
-            for (int j = 0; j < n; ++j) {
+#pragma unroll
+            for (int j = 0; j < P_KSUB; ++j) {
+                if (j >= n) break;
                 const uint64_t off = uint64_t(j) * (P_SUB_BYTES >> 4);  // next K sub-block of the stage
 #pragma unroll
                 for (int k = 0; k < BK / UMMA_K; ++k)
@@ -209,16 +209,13 @@ __device__ void pair_mma(const EngineParams& p, const EngineSmem& s, const Dyn& 
             return 1;
         });
         if (!walked) return;
-        if (lane == 0) {
-            if (n_issued) {  // arrives in both CTAs when the accumulator is complete
-                tc_commit_pair(tfull_bar[acc]);
-                tc_commit_pair(tfull_peer[acc]);
-            } else {  // a reduction of length zero: nothing was issued, the epilogues store zeros
-                mbar_arrive_cluster(tfull_bar[acc]);
-                mbar_arrive_cluster(tfull_peer[acc]);
-            }
+        if (n_issued) {  // arrives in both CTAs when the accumulator is complete
+            tc_commit_pair(tfull_bar[acc]);
+            tc_commit_pair(tfull_peer[acc]);
+        } else {  // a reduction of length zero: nothing was issued, the epilogues store zeros
+            mbar_arrive_cluster(tfull_bar[acc]);
+            mbar_arrive_cluster(tfull_peer[acc]);
         }
-        __syncwarp();
         if (++acc == 2) {
             acc = 0;
             acc_phase ^= 1u;
