@@ -287,11 +287,10 @@ __device__ __forceinline__ KTile ktile_setup(const EngineParams& p, const Dyn& d
     return kt;
 }
 
-// Is candidate `cand` of this tile taken, and where are its operands?
+// Where are the operands of candidate `cand` of this tile?
 template <int MODE>
-__device__ __forceinline__ bool kcand_eval(const EngineParams& p, const KTile& kt, int mblk, int nblk,
-                                           int cand, KCoord& kc) {
-    if (cand >= kt.n_cand) return false;
+__device__ __forceinline__ void kcand_coords(const EngineParams& p, const KTile& kt, int mblk, int nblk, int cand,
+                                             KCoord& kc) {
     if (MODE == MODE_GEMM && p.sparse == 1) {  // A = pool tile (K-major), B = classifier rows (MN-major)
         const int2 ent = p.klist[kt.e0 + cand];
         const int sl = ent.x >> 2, kb = ent.x & 3;
@@ -299,7 +298,7 @@ __device__ __forceinline__ bool kcand_eval(const EngineParams& p, const KTile& k
         kc.a_k = kb * BK;
         kc.b_mn = p.b_mn_off + nblk * BN;
         kc.b_k = ent.y * BN + kb * BK;
-        return true;
+        return;
     }
     if (MODE == MODE_GEMM && p.sparse == 2) {  // A = pool tile (MN-major), B = embedding rows (MN-major)
         const int2 ent = p.klist[kt.e0 + cand];
@@ -308,14 +307,50 @@ __device__ __forceinline__ bool kcand_eval(const EngineParams& p, const KTile& k
         kc.a_k = sl * BM + kb * BK;
         kc.b_mn = p.b_mn_off + nblk * BN;
         kc.b_k = ent.y * BM + kb * BK;
-        return true;
+        return;
     }
-    if (MODE == MODE_GEMM && p.kflags && !p.kflags[(size_t)mblk * p.ld_kflags + cand]) return false;
     kc.a_mn = p.a_mn_off + mblk * BM;
     kc.a_k = p.a_k_off + cand * BK;
     kc.b_mn = p.b_mn_off + nblk * BN;
     kc.b_k = p.b_k_off + cand * BK;
-    return true;
+}
+
+// One thread walks the candidates a tile takes, in order, and calls fn(cand) for each; fn returns
+// false to abandon the walk.  Block-list forms take every list entry; dense flagged forms read the
+// skip flags of the tile's row block four at a time.  Returns the number taken, or -1 if abandoned.
+// (A warp-collective walk with ballots was slower: lanes parked at a shuffle slow the one that
+// issues the loads or the MMAs.)
+template <int MODE, class F>
+__device__ __forceinline__ int walk_taken(const EngineParams& p, const KTile& kt, int mblk, F&& fn) {
+    int n = 0;
+    if (MODE == MODE_GEMM && !p.sparse && p.kflags) {
+        const uint8_t* f = p.kflags + (size_t)mblk * p.ld_kflags;
+        int c = 0;
+        if ((reinterpret_cast<uintptr_t>(f) & 3) == 0) {
+            for (; c + 4 <= kt.n_cand; c += 4) {
+                uint32_t w = *reinterpret_cast<const uint32_t*>(f + c);
+#pragma unroll
+                for (int j = 0; j < 4; ++j, w >>= 8) {
+                    if (w & 0xffu) {
+                        if (!fn(c + j)) return -1;
+                        ++n;
+                    }
+                }
+            }
+        }
+        for (; c < kt.n_cand; ++c) {
+            if (f[c]) {
+                if (!fn(c)) return -1;
+                ++n;
+            }
+        }
+        return n;
+    }
+    for (int c = 0; c < kt.n_cand; ++c) {
+        if (!fn(c)) return -1;
+        ++n;
+    }
+    return n;
 }
 
 // Operand loads of one ring stage (issued by one thread).
@@ -375,43 +410,29 @@ __device__ void producer_loop(const CUtensorMap* tmA, const CUtensorMap* tmB, co
         }
         return;
     }
-    if constexpr (MODE == MODE_GEMM) {  // only the products have sparse or flagged reductions
-    while (it.next()) {
-        const KTile kt = ktile_setup<MODE>(p, dyn, it.mblk);
-        for (int base = 0; base < kt.n_cand; base += 32) {
-            KCoord kc{0, 0, 0, 0};
-            const bool take = kcand_eval<MODE>(p, kt, it.mblk, it.nblk, base + lane, kc);
-            uint32_t mask = __ballot_sync(0xffffffffu, take);
-            while (mask) {
-                const int src = __ffs(mask) - 1;
-                mask &= mask - 1;
-                const int a_mn = __shfl_sync(0xffffffffu, kc.a_mn, src);
-                const int a_k = __shfl_sync(0xffffffffu, kc.a_k, src);
-                const int b_mn = __shfl_sync(0xffffffffu, kc.b_mn, src);
-                const int b_k = __shfl_sync(0xffffffffu, kc.b_k, src);
-                int ok = 1;
-                if (lane == 0) {
-                    const long long t0 = (kTrace && p.wait_cycles) ? clock64() : 0;
-                    ok = mbar_wait(smem_u32(&s.empty[stage]), phase ^ 1u, s.abort_flag, p.status,
-                                   ERR_WAIT_SMEM_EMPTY);
-                    if (kTrace && p.wait_cycles) waited += clock64() - t0;
-                    if (ok) {
-                        const uint32_t bar = smem_u32(&s.full[stage]);
-                        const uint32_t sa = smem_u32(s.stages + stage * STAGE_BYTES);
-                        const uint32_t sb = sa + A_BYTES;
-                        mbar_expect_tx(bar, STAGE_BYTES);
-                        load_stage(p, tmA, tmB, sa, sb, bar, a_mn, a_k, b_mn, b_k);
-                    }
-                }
-                ok = __shfl_sync(0xffffffffu, ok, 0);
-                if (!ok) return;
+    if constexpr (MODE == MODE_GEMM) {  // only the products have block-list or flagged reductions
+        if (lane != 0) return;
+        while (it.next()) {
+            const KTile kt = ktile_setup<MODE>(p, dyn, it.mblk);
+            const int taken = walk_taken<MODE>(p, kt, it.mblk, [&](int cand) -> bool {
+                KCoord kc{0, 0, 0, 0};
+                kcand_coords<MODE>(p, kt, it.mblk, it.nblk, cand, kc);
+                const long long t0 = (kTrace && p.wait_cycles) ? clock64() : 0;
+                if (!mbar_wait(smem_u32(&s.empty[stage]), phase ^ 1u, s.abort_flag, p.status, ERR_WAIT_SMEM_EMPTY))
+                    return false;
+                if (kTrace && p.wait_cycles) waited += clock64() - t0;
+                const uint32_t bar = smem_u32(&s.full[stage]);
+                const uint32_t sa = smem_u32(s.stages + stage * STAGE_BYTES);
+                mbar_expect_tx(bar, STAGE_BYTES);
+                load_stage(p, tmA, tmB, sa, sa + A_BYTES, bar, kc.a_mn, kc.a_k, kc.b_mn, kc.b_k);
                 if (++stage == NSTAGE) {
                     stage = 0;
                     phase ^= 1u;
                 }
-            }
+                return true;
+            });
+            if (taken < 0) return;
         }
-    }
     }
     if (kTrace && p.wait_cycles && lane == 0) atomicAdd(p.wait_cycles + 0, (unsigned long long)waited);
 }
@@ -481,68 +502,65 @@ __device__ void mma_loop(const EngineParams& p, const EngineSmem& s, uint32_t tm
         }
         return;
     }
-    if constexpr (MODE == MODE_GEMM) {  // only the products have sparse or flagged reductions
-    while (it.next()) {
-        int ok = 1;
-        if (lane == 0) {
-            const long long t0 = (kTrace && p.wait_cycles) ? clock64() : 0;
-            ok = mbar_wait(smem_u32(&s.tempty[acc]), acc_phase ^ 1u, s.abort_flag, p.status,
-                           ERR_WAIT_TMEM_EMPTY);
-            if (kTrace && p.wait_cycles) waited_acc += clock64() - t0;
-        }
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) return;
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BN;
-        int n_issued = 0;
-        const KTile kt = ktile_setup<MODE>(p, dyn, it.mblk);
-        for (int base = 0; base < kt.n_cand; base += 32) {
-            KCoord kc{0, 0, 0, 0};
-            const bool take = kcand_eval<MODE>(p, kt, it.mblk, it.nblk, base + lane, kc);
-            uint32_t mask = __ballot_sync(0xffffffffu, take);
-            while (mask) {
-                mask &= mask - 1;
-                if (lane == 0) {
-                    const long long t0 = (kTrace && p.wait_cycles) ? clock64() : 0;
-                    ok = mbar_wait(smem_u32(&s.full[stage]), phase, s.abort_flag, p.status,
-                                   ERR_WAIT_SMEM_FULL);
-                    if (kTrace && p.wait_cycles) waited_full += clock64() - t0;
-                    if (ok) {
-                        tc_fence_after();
-                        const uint32_t sa = smem_u32(s.stages + stage * STAGE_BYTES);
-                        const uint32_t sb = sa + A_BYTES;
+    if constexpr (MODE == MODE_GEMM) {  // only the products have block-list or flagged reductions
+        if (lane != 0) return;
+        // descriptors of the ring stages, built once; a K step adds to the address field
+        uint64_t adesc[NSTAGE], bdesc[NSTAGE];
 #pragma unroll
-                        for (int k = 0; k < BK / UMMA_K; ++k) {
-                            const uint64_t ad = make_smem_desc(sa + k * a_kstep, a_lbo, 1024);
-                            const uint64_t bd = make_smem_desc(sb + k * b_kstep, b_lbo, 1024);
-                            tc_mma_f16(d_tmem, ad, bd, p.idesc, (n_issued | k) ? 1u : 0u);
-                        }
-                        tc_commit(smem_u32(&s.empty[stage]));  // frees the stage once the MMAs have read it
+        for (int i = 0; i < NSTAGE; ++i) {
+            const uint32_t sa = smem_u32(s.stages + i * STAGE_BYTES);
+            adesc[i] = make_smem_desc(sa, a_lbo, 1024);
+            bdesc[i] = make_smem_desc(sa + A_BYTES, b_lbo, 1024);
+        }
+        const uint64_t a_inc = a_kstep >> 4, b_inc = b_kstep >> 4;
+        while (it.next()) {
+            {
+                const long long t0 = (kTrace && p.wait_cycles) ? clock64() : 0;
+                if (!mbar_wait(smem_u32(&s.tempty[acc]), acc_phase ^ 1u, s.abort_flag, p.status, ERR_WAIT_TMEM_EMPTY))
+                    return;
+                if (kTrace && p.wait_cycles) waited_acc += clock64() - t0;
+            }
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + acc * BN;
+            int n_issued = 0;
+            const KTile kt = ktile_setup<MODE>(p, dyn, it.mblk);
+            const int taken = walk_taken<MODE>(p, kt, it.mblk, [&](int) -> bool {
+                const long long t0 = (kTrace && p.wait_cycles) ? clock64() : 0;
+                if (!mbar_wait(smem_u32(&s.full[stage]), phase, s.abort_flag, p.status, ERR_WAIT_SMEM_FULL))
+                    return false;
+                if (kTrace && p.wait_cycles) waited_full += clock64() - t0;
+                tc_fence_after();
+                uint64_t ad = 0, bd = 0;
+#pragma unroll
+                for (int i = 0; i < NSTAGE; ++i) {  // select without dynamic register indexing
+                    if (i == stage) {
+                        ad = adesc[i];
+                        bd = bdesc[i];
                     }
                 }
-                ok = __shfl_sync(0xffffffffu, ok, 0);
-                if (!ok) return;
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k)
+                    tc_mma_f16(d_tmem, ad + k * a_inc, bd + k * b_inc, p.idesc, (n_issued | k) ? 1u : 0u);
+                tc_commit(smem_u32(&s.empty[stage]));  // frees the stage once the MMAs have read it
                 ++n_issued;
                 if (++stage == NSTAGE) {
                     stage = 0;
                     phase ^= 1u;
                 }
-            }
-        }
-        if (lane == 0) {
+                return true;
+            });
+            if (taken < 0) return;
             s.acc_empty[acc] = (n_issued == 0);
             __threadfence_block();
             if (n_issued)
                 tc_commit(smem_u32(&s.tfull[acc]));  // arrives when the accumulator is complete
             else
                 mbar_arrive(smem_u32(&s.tfull[acc]));
+            if (++acc == 2) {
+                acc = 0;
+                acc_phase ^= 1u;
+            }
         }
-        __syncwarp();
-        if (++acc == 2) {
-            acc = 0;
-            acc_phase ^= 1u;
-        }
-    }
     }
     if (kTrace && p.wait_cycles && lane == 0) {
         atomicAdd(p.wait_cycles + 1, (unsigned long long)waited_full);
