@@ -193,9 +193,10 @@ class ClockSampler:
 
 
 # DRAM bytes of ONE launch of the forward kernel at the default workload (dram__bytes_read.sum +
-# dram__bytes_write.sum of one ncu capture of engine_kernel<0>; profiles/ holds the summary), or None
-# while no such capture exists; then `traffic` is an estimate scaled from the small profiling case.
-FORWARD_DRAM_BYTES_MEASURED = {"gemma2-2b-head": None}
+# dram__bytes_write.sum of one ncu capture of the full-size launch, summarised in
+# profiles/forward_dram_traffic_gemma2-2b-head_full-size.md).  Other workloads get an estimate
+# scaled from the small profiling case by algorithmic bytes, and say so.
+FORWARD_DRAM_BYTES_MEASURED = {"gemma2-2b-head": 2412335360 + 8159744}
 FORWARD_DRAM_TRAFFIC_RATIO_SMALL_CASE = 1.031
 
 
