@@ -227,6 +227,11 @@ typedef struct cce_b200_backward_args {
      * operands (see cce_b200_lse_packed_e), with its row pitch in elements; NULL: staged here if needed. */
     const void* e_packed;
     int64_t e_packed_ld;
+    /* Optional cudaEvent_t (as void*): recorded on `stream` as soon as d_e is complete.  The call then
+     * computes the last dE product before the last dC product, so a caller that sums d_e across ranks
+     * (vocab parallelism) can wait for this event on another stream and run the reduction while the
+     * rest of dC is computed.  NULL: no event, dC before dE throughout. */
+    void* de_ready_event;
 } cce_b200_backward_args;
 
 /* Gradient of sum_i d_out_i * grad_scale * (lse_i - logit_i[t_i]) + sum_i d_lse_i * lse_i

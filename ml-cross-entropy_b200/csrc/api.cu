@@ -1033,6 +1033,29 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
     pg.g_is_bf16 = cdt == CCE_DT_BF16;
     pg.inv_order = inv_order;
 
+    // The last step of dE: fp32 scratch -> the caller's rows.  Run once, either at the end or, when the
+    // caller asked to be told (de_ready_event), right after the last dE product and before the last dC
+    // product, so that a cross-rank reduction of dE can overlap that product.
+    const bool early_de = a->d_e && a->de_ready_event != nullptr;
+    bool de_finished = false;
+    auto finish_de = [&]() -> int {
+        if (de_finished || !a->d_e) return CCE_OK;
+        de_finished = true;
+        if (a->d_e_f32 || split)
+            scatter_cast_kernel<float><<<(unsigned)B, 128, 0, st>>>(
+                de32, D, op->valids, op->valids_dtype == CCE_IDX_I64, reinterpret_cast<float*>(a->d_e), D, D, B, status, ndev);
+        else if (cdt == CCE_DT_BF16)
+            scatter_cast_kernel<__nv_bfloat16><<<(unsigned)B, 128, 0, st>>>(
+                de32, D, op->valids, op->valids_dtype == CCE_IDX_I64, reinterpret_cast<__nv_bfloat16*>(a->d_e), D, D, B,
+                status, ndev);
+        else
+            scatter_cast_kernel<__half><<<(unsigned)B, 128, 0, st>>>(
+                de32, D, op->valids, op->valids_dtype == CCE_IDX_I64, reinterpret_cast<__half*>(a->d_e), D, D, B, status, ndev);
+        CCE_LAUNCH_CHECK();
+        if (a->de_ready_event) CCE_CUDA(cudaEventRecord(reinterpret_cast<cudaEvent_t>(a->de_ready_event), st));
+        return CCE_OK;
+    };
+
     if (pl.sparse) {
         // ---- index of the tiles worth recomputing
         const int n_groups = pl.n_rb * 4;
@@ -1103,7 +1126,8 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
                 pinfo, row_ptr, row_slots, col_ptr, slot_tile, pl.n_rb, pl.n_vt, sflag_e, sflag_c, de_list, de_cnt,
                 dc_list, dc_cnt);
             CCE_LAUNCH_CHECK();
-            if (a->d_c) {  // dC[vt] = sum over the slots of column vt of G^T E
+            auto pass_dc = [&]() -> int {  // dC[vt] = sum over the slots of column vt of G^T E
+                if (!a->d_c) return CCE_OK;
                 EngineParams p;
                 base_params(&p, V, D, B, cdt, 1, 1, status);
                 p.out = a->d_c;
@@ -1119,10 +1143,10 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
                 p.kcount = dc_cnt;
                 p.a_tma3 = p_is3;
                 p.row_map = inv_order ? a->vocab_order : nullptr;
-                rc = run_dc(p, tmP_mn);
-                if (rc != CCE_OK) return rc;
-            }
-            if (a->d_e) {  // dE[rb] += sum over the slots of row rb (in this pass) of G C
+                return run_dc(p, tmP_mn);
+            };
+            auto pass_de = [&]() -> int {  // dE[rb] += sum over the slots of row rb (in this pass) of G C
+                if (!a->d_e) return CCE_OK;
                 EngineParams p;
                 base_params(&p, B, D, V, cdt, 0, 1, status);
                 p.out = de32;
@@ -1137,9 +1161,18 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
                 p.klist = de_list;
                 p.kcount = de_cnt;
                 p.m_dev = ndev;
-                rc = run_de(p, tmP_k);
+                return run_de(p, tmP_k);
+            };
+            // in the last pass dE goes first when the caller wants to start reducing it early
+            const bool de_first = early_de && ps == pl.max_pass - 1;
+            rc = de_first ? pass_de() : pass_dc();
+            if (rc != CCE_OK) return rc;
+            if (de_first) {
+                rc = finish_de();
                 if (rc != CCE_OK) return rc;
             }
+            rc = de_first ? pass_dc() : pass_de();
+            if (rc != CCE_OK) return rc;
         }
     } else {
         uint8_t* flag_e = reinterpret_cast<uint8_t*>(ws + pl.off_flag_e);
@@ -1167,7 +1200,8 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
             }
 
             // phase 2: dC[v0 : v0 + Vw, :] = G^T E   (M = Vw, N = D, K = B; both operands MN-major)
-            if (a->d_c) {
+            auto chunk_dc = [&]() -> int {
+                if (!a->d_c) return CCE_OK;
                 CUtensorMap tmG_mn;
                 int g_is3 = 0;  // the chunk's pitch (a multiple of 256) covers the last group of 64 columns
                 rc = make_tmap_mn(&tmG_mn, g_buf, cdt, Vw, B, pl.Vc, BM / 64, tma3_enabled(), &g_is3);
@@ -1184,12 +1218,12 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
                     p.kflags = flag_c;
                     p.ld_kflags = pl.ld_flag_c;
                 }
-                rc = run_dc(p, tmG_mn);
-                if (rc != CCE_OK) return rc;
-            }
+                return run_dc(p, tmG_mn);
+            };
 
             // phase 3: dE += G C[v0 : v0 + Vw, :]    (M = B, N = D, K = Vw; A K-major, B MN-major)
-            if (a->d_e) {
+            auto chunk_de = [&]() -> int {
+                if (!a->d_e) return CCE_OK;
                 CUtensorMap tmG_k;
                 rc = make_tmap(&tmG_k, g_buf, cdt, Vw, B, pl.Vc, BK, BM);
                 if (rc != CCE_OK) return rc;
@@ -1205,9 +1239,17 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
                     p.kflags = flag_e;
                     p.ld_kflags = pl.ld_flag_e;
                 }
-                rc = run_de(p, tmG_k);
+                return run_de(p, tmG_k);
+            };
+            const bool de_first = early_de && ch == pl.n_chunk - 1;
+            rc = de_first ? chunk_de() : chunk_dc();
+            if (rc != CCE_OK) return rc;
+            if (de_first) {
+                rc = finish_de();
                 if (rc != CCE_OK) return rc;
             }
+            rc = de_first ? chunk_dc() : chunk_de();
+            if (rc != CCE_OK) return rc;
 
             // bias gradient: column sums of G, partial sums per row block then a fixed-order finish
             if (a->d_bias) {
@@ -1228,19 +1270,8 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
         }
     }
 
-    if (a->d_e) {
-        if (a->d_e_f32 || split)
-            scatter_cast_kernel<float><<<(unsigned)B, 128, 0, st>>>(
-                de32, D, op->valids, op->valids_dtype == CCE_IDX_I64, reinterpret_cast<float*>(a->d_e), D, D, B, status, ndev);
-        else if (cdt == CCE_DT_BF16)
-            scatter_cast_kernel<__nv_bfloat16><<<(unsigned)B, 128, 0, st>>>(
-                de32, D, op->valids, op->valids_dtype == CCE_IDX_I64, reinterpret_cast<__nv_bfloat16*>(a->d_e), D, D, B,
-                status, ndev);
-        else
-            scatter_cast_kernel<__half><<<(unsigned)B, 128, 0, st>>>(
-                de32, D, op->valids, op->valids_dtype == CCE_IDX_I64, reinterpret_cast<__half*>(a->d_e), D, D, B, status, ndev);
-        CCE_LAUNCH_CHECK();
-    }
+    rc = finish_de();
+    if (rc != CCE_OK) return rc;
     return CCE_OK;
 }
 

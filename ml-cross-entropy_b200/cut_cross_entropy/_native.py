@@ -98,6 +98,7 @@ class BackwardArgs(Structure):
         ("col_max_key", c_void_p),
         ("e_packed", c_void_p),
         ("e_packed_ld", c_int64),
+        ("de_ready_event", c_void_p),
     ]
 
 

@@ -16,9 +16,20 @@ from .utils import TensorInfo
 from .vocab_parallel.utils import vp_reduce_e_grad_
 
 
+_REDUCE_STREAMS: dict = {}
+
+
+def _reduce_stream(dev: torch.device) -> "torch.cuda.Stream":
+    """One side stream per device for the cross-rank sum of dE."""
+    key = (dev.type, dev.index if dev.index is not None else torch.cuda.current_device())
+    if key not in _REDUCE_STREAMS:
+        _REDUCE_STREAMS[key] = torch.cuda.Stream(device=dev)
+    return _REDUCE_STREAMS[key]
+
+
 def _launch(do, dlse, e, c, bias, lse, valids, softcap, filter_eps, targets, shift, grad_scale,
             filter_e, filter_c, vocab_start, de, dc, dbias, tile_max=None, vocab_ordering=None, col_max=None,
-            n_rows_dev=None, scale_by_inv_rows=False, packed_e=None) -> None:
+            n_rows_dev=None, scale_by_inv_rows=False, packed_e=None, de_ready=None) -> None:
     """Fill the (pre-allocated, possibly ``None``) outputs ``de``/``dc``/``dbias`` through the C ABI."""
     dev = e.device
     a = _native.BackwardArgs()
@@ -34,6 +45,8 @@ def _launch(do, dlse, e, c, bias, lse, valids, softcap, filter_eps, targets, shi
     a.grad_scale_by_inv_rows = int(scale_by_inv_rows)
     if packed_e is not None:
         a.e_packed, a.e_packed_ld = packed_e.data_ptr(), packed_e.stride(0)
+    if de_ready is not None:
+        a.de_ready_event = de_ready.cuda_event
     a.has_filter = int(filter_eps is not None)
     a.filter_eps = float(filter_eps) if filter_eps is not None else 0.0
     a.filter_e = int(filter_e)
@@ -140,14 +153,29 @@ def cce_backward_kernel(
     dc = torch.empty((c.size(0), c.size(1)), dtype=c.dtype, device=dev) if want_dc else None
     dbias = torch.empty((c.size(0),), dtype=torch.float32, device=dev) if want_dbias else None
 
+    # With a cross-rank sum of dE to do, the library is asked to finish dE before the last dC product
+    # and to record an event there: the all-reduce then runs on a side stream beside that product.
+    overlap = de_f32 and dev.type == "cuda"
+    de_ready = None
+    if overlap:
+        de_ready = torch.cuda.Event()
+        de_ready.record(torch.cuda.current_stream(dev))  # creates the handle; the library records it again
     if want_de or want_dc or want_dbias:
         _launch(do, dlse, e, c, bias, lse, valids, softcap, filter_eps, targets, int(shift), float(grad_scale),
                 bool(filter_e_grad), bool(filter_c_grad), int(vocab_start), de, dc, dbias, tile_max,
-                vocab_ordering, col_max, n_rows_dev, bool(scale_by_inv_rows), packed_e)
+                vocab_ordering, col_max, n_rows_dev, bool(scale_by_inv_rows), packed_e, de_ready)
 
     if de_f32:
         assert de is not None
-        vp_reduce_e_grad_(de, pg)
+        if overlap:
+            main, side = torch.cuda.current_stream(dev), _reduce_stream(dev)
+            side.wait_event(de_ready)
+            with torch.cuda.stream(side):
+                vp_reduce_e_grad_(de, pg)
+            de.record_stream(side)
+            main.wait_stream(side)  # enqueued after the last dC product, which therefore overlaps the reduction
+        else:
+            vp_reduce_e_grad_(de, pg)
 
     if dbias is not None:
         assert bias_info is not None
