@@ -49,6 +49,17 @@ class PendingValidRows:
         self.count_dev = count_dev
         self._resolved: torch.Tensor | None | object = _UNRESOLVED
 
+    def __del__(self):
+        # The length is written by a kernel into pinned host memory that PyTorch's host allocator
+        # knows nothing about being in use: if this object goes away before the kernel has run (an
+        # exception between the launch and resolve()), wait for it, so that the block cannot be
+        # handed to somebody else and then overwritten.
+        try:
+            if self.count_dev is None and self.done is not None and self._resolved is _UNRESOLVED:
+                self.done.synchronize()
+        except Exception:
+            pass
+
     def resolve(self) -> torch.Tensor | None:
         if self._resolved is _UNRESOLVED and self.count_dev is not None:
             n = int(self.count_dev.item())  # synchronises; the sync-free path never calls this
