@@ -968,14 +968,12 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
     if (rc != CCE_OK) return rc;
 
     // Dense launches that take every K block run on CTA pairs: each CTA stages 128 of the B side's 256 rows
-    const bool can_pair = pair_enabled() && dev->sms >= 2;
+    const bool can_pair = pair_enabled() && !pl.sparse && dev->sms >= 2;
     CUtensorMap tmC_k_h, tmE_mn_h, tmC_mn_h;
     if (can_pair) {
+        int is3 = 0;
         rc = make_tmap(&tmC_k_h, sg.c, cdt, sg.Dk, V, sg.ldc, BK, BN / 2);
         if (rc != CCE_OK) return rc;
-    }
-    if (can_pair && !pl.sparse) {
-        int is3 = 0;
         if (e_is3) rc = make_tmap_mn(&tmE_mn_h, sg.e, cdt, sg.Dmn, B, sg.lde, BN / 128, true, &is3);
         if (rc != CCE_OK) return rc;
         if (c_is3) rc = make_tmap_mn(&tmC_mn_h, sg.c, cdt, sg.Dmn, V, sg.ldc, BN / 128, true, &is3);
@@ -1118,8 +1116,7 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
                 p.n_vt = pl.n_vt;
                 p.sflag_e = sflag_e;
                 p.sflag_c = sflag_c;
-                // slots two at a time on CTA pairs (the number of slots is known on the device only)
-                rc = launch_engine<MODE_PGRAD>(tmE_k, can_pair ? tmC_k_h : tmC_k, p, dev->sms, st, can_pair);
+                rc = launch_engine<MODE_PGRAD>(tmE_k, tmC_k, p, dev->sms, st);
                 if (rc != CCE_OK) return rc;
             }
             klist_build_kernel<<<(unsigned)cdiv(pl.n_rb + 2 * pl.n_vt, 8), 256, 0, st>>>(

@@ -194,7 +194,6 @@ struct TileIter {
     int item, n_items, sub, sub_end;
     int mblk, nblk, band, slot;
     bool first, last;
-    static constexpr bool phantom = false;  // (the pair form's iterator can hand a CTA a tile that is not there)
     __device__ TileIter(const EngineParams& p_, const PassInfo& pass_, const Dyn& dyn)
         : p(p_), pass(pass_), n_mblk(dyn.n_mblk) {
         item = int(blockIdx.x) - int(gridDim.x);
@@ -666,7 +665,7 @@ __device__ void epilogue_loop(const EngineParams& p, const EngineSmem& s, uint32
 
     while (it.next()) {
         const int row = it.mblk * BM + q * 32 + lane;
-        const bool row_ok = row < dyn.M && !it.phantom;
+        const bool row_ok = row < dyn.M;
 
         // per-row constants (loaded before the wait so the latency overlaps the MMAs)
         float row_l2 = 0.0f, row_g = 0.0f, row_dl = 0.0f;
@@ -822,11 +821,9 @@ __device__ void epilogue_loop(const EngineParams& p, const EngineSmem& s, uint32
                     }
                     if (p.sparse) {
                         // pool slot: a dense 128x256 tile; rows past M are written as zeros
-                        if (!it.phantom) {
-                            char* dst = reinterpret_cast<char*>(p.g_out) +
-                                        (((size_t)it.slot * BM + q * 32 + lane) * BN + c * 32) * 2;
-                            store_g16(dst, g, p.g_is_bf16 != 0);
-                        }
+                        char* dst = reinterpret_cast<char*>(p.g_out) +
+                                    (((size_t)it.slot * BM + q * 32 + lane) * BN + c * 32) * 2;
+                        store_g16(dst, g, p.g_is_bf16 != 0);
                     } else if (row < p.n_mblk * BM) {
                         // rows past the count (within the buffer's blocks of 128) are stored as zeros,
                         // so that the products never meet stale values there; a CTA pair's second

@@ -12,8 +12,8 @@
 // Roles per CTA as in engine.cuh: warp 0 TMA producer (both CTAs; loads are per-CTA tiled loads
 // whose bytes are credited to the leader's barrier, no cluster-wide broadcast), warp 1 MMA issuer
 // (leader only) and TMEM owner, warps 2..5 epilogue (engine.cuh's epilogue_loop, unchanged).
-// Serves the launches that take every K block: MODE_LSE, MODE_PGRAD (dense, and over the slots of
-// a block-list pass) and MODE_GEMM without block lists and without skip flags (a filtered product keeps the single-CTA pipeline, where a K
+// Serves the dense launches that take every K block: MODE_LSE, MODE_PGRAD and MODE_GEMM without
+// block lists and without skip flags (a filtered product keeps the single-CTA pipeline, where a K
 // block is skipped exactly when its own 128-row block has nothing above the threshold).
 #pragma once
 #include "engine.cuh"
@@ -29,32 +29,21 @@ constexpr int P_STAGE_BYTES = 2 * P_OPER_BYTES;
 constexpr int PAIR_SMEM = P_NST * P_STAGE_BYTES + 1024 + 256;
 
 // Tiles of this pair: as TileIter, with pairs of 128-row blocks in place of single ones.
-// Block-list recompute (MODE_PGRAD, sparse): the slots of the pass are taken two at a time; slots
-// are numbered column by column, so two neighbours usually lie in the same vocabulary tile and
-// share the B side.  Where they do not (a column boundary, or an odd slot at the end) each is
-// computed in a step of its own with the pair's second CTA idle (`phantom`): it still stages its
-// half of the B side, computes on a copy of the first CTA's rows and stores nothing.
 template <int MODE>
 struct PairTileIter {
     const EngineParams& p;
-    const PassInfo& pass;
     const int n_mblk2;  // pairs of row blocks
     const int rank;
     int item, n_items, stride, sub, sub_end;
     int mblk, mblk2, nblk, band, slot;
-    int second_slot;  // block list: the slot still to do on its own after a split pair, or -1
-    bool first, last, phantom;
-    __device__ PairTileIter(const EngineParams& p_, const PassInfo& pass_, const Dyn& dyn, int rank_)
-        : p(p_), pass(pass_), n_mblk2((dyn.n_mblk + 1) >> 1), rank(rank_) {
+    bool first, last;
+    __device__ PairTileIter(const EngineParams& p_, const Dyn& dyn, int rank_)
+        : p(p_), n_mblk2((dyn.n_mblk + 1) >> 1), rank(rank_) {
         stride = int(gridDim.x >> 1);
         item = int(blockIdx.x >> 1) - stride;
         sub = sub_end = 0;
         slot = 0;
-        second_slot = -1;
-        phantom = false;
-        if (MODE == MODE_PGRAD && p.sparse) {
-            n_items = (pass.slot_hi - pass.slot_lo + 1) >> 1;
-        } else if (MODE == MODE_LSE) {
+        if (MODE == MODE_LSE) {
             const int n_band = (p.n_nblk + p.band_len - 1) / p.band_len;
             n_items = n_band * n_mblk2;
         } else {
@@ -76,33 +65,6 @@ struct PairTileIter {
             nblk = sub;
             first = (sub == band * p.band_len);
             last = (sub + 1 == sub_end);
-        } else if (MODE == MODE_PGRAD && p.sparse) {
-            first = last = true;
-            band = 0;
-            int s0;  // the slot CTA 0 computes in this step
-            bool paired = false;
-            if (second_slot >= 0) {
-                s0 = second_slot;
-                second_slot = -1;
-            } else {
-                item += stride;
-                if (item >= n_items) return false;
-                s0 = pass.slot_lo + 2 * item;
-                if (s0 + 1 < pass.slot_hi) {
-                    if (p.slot_tile[s0 + 1] % p.n_vt == p.slot_tile[s0] % p.n_vt)
-                        paired = true;
-                    else
-                        second_slot = s0 + 1;
-                }
-            }
-            const int my_slot = paired ? s0 + rank : s0;
-            const int t = p.slot_tile[my_slot];
-            mblk = t / p.n_vt;
-            nblk = t % p.n_vt;
-            mblk2 = mblk >> 1;
-            slot = my_slot - pass.slot_lo;
-            phantom = !paired && rank == 1;
-            return true;
         } else {
             item += stride;
             if (item >= n_items) return false;
@@ -143,11 +105,11 @@ __device__ __forceinline__ bool pair_walk_k(const Dyn& dyn, F&& stage_fn) {
 
 template <int MODE>
 __device__ void pair_producer(const CUtensorMap* tmA, const CUtensorMap* tmB, const EngineParams& p,
-                              const EngineSmem& s, const Dyn& dyn, const PassInfo& pass, uint32_t rank) {
+                              const EngineSmem& s, const Dyn& dyn, uint32_t rank) {
     if ((threadIdx.x & 31) != 0) return;  // one lane runs the whole loop
     int stage = 0;
     uint32_t phase = 0;
-    PairTileIter<MODE> it(p, pass, dyn, int(rank));
+    PairTileIter<MODE> it(p, dyn, int(rank));
     while (it.next()) {
         const int a_mn = p.a_mn_off + it.mblk * BM;
         const int b_mn = p.b_mn_off + it.nblk * BN + int(rank) * (BN / 2);
@@ -183,8 +145,7 @@ __device__ void pair_producer(const CUtensorMap* tmA, const CUtensorMap* tmB, co
 
 // leader CTA only; one lane runs the whole loop
 template <int MODE>
-__device__ void pair_mma(const EngineParams& p, const EngineSmem& s, const Dyn& dyn, const PassInfo& pass,
-                         uint32_t tmem_base) {
+__device__ void pair_mma(const EngineParams& p, const EngineSmem& s, const Dyn& dyn, uint32_t tmem_base) {
     if ((threadIdx.x & 31) != 0) return;
     int stage = 0;
     uint32_t phase = 0;
@@ -207,7 +168,7 @@ __device__ void pair_mma(const EngineParams& p, const EngineSmem& s, const Dyn& 
     }
     const uint32_t tfull_bar[2] = {smem_u32(&s.tfull[0]), smem_u32(&s.tfull[1])};
     const uint32_t tfull_peer[2] = {map_to_cta(tfull_bar[0], 1), map_to_cta(tfull_bar[1], 1)};
-    PairTileIter<MODE> it(p, pass, dyn, 0);
+    PairTileIter<MODE> it(p, dyn, 0);
     while (it.next()) {
         if (!mbar_wait(smem_u32(&s.tempty[acc]), acc_phase ^ 1u, s.abort_flag, p.status, ERR_WAIT_TMEM_EMPTY)) return;
         tc_fence_after();
@@ -283,10 +244,9 @@ pair_engine_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
     const Dyn dyn = load_dyn(p);
-    const PassInfo pass = load_pass(p);
 
     {   // a pair without a first item leaves before it sets up anything; uniform over the pair
-        const PairTileIter<MODE> probe(p, pass, dyn, 0);
+        const PairTileIter<MODE> probe(p, dyn, 0);
         if (int(blockIdx.x >> 1) >= probe.n_items) return;
     }
     if (p.clk_words && blockIdx.x == 0 && threadIdx.x == 0) {
@@ -324,11 +284,11 @@ pair_engine_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(s.tmem_base);
 
     if (warp == 0) {
-        pair_producer<MODE>(&tmA, &tmB, p, s, dyn, pass, rank);
+        pair_producer<MODE>(&tmA, &tmB, p, s, dyn, rank);
     } else if (warp == 1) {
-        if (rank == 0) pair_mma<MODE>(p, s, dyn, pass, tmem_base);
+        if (rank == 0) pair_mma<MODE>(p, s, dyn, tmem_base);
     } else {
-        PairTileIter<MODE> it(p, pass, dyn, int(rank));
+        PairTileIter<MODE> it(p, dyn, int(rank));
         const uint32_t tempty_bar[2] = {map_to_cta(smem_u32(&s.tempty[0]), 0), map_to_cta(smem_u32(&s.tempty[1]), 0)};
         epilogue_loop<MODE>(p, s, tmem_base, it, dyn, tempty_bar);
     }
