@@ -109,12 +109,15 @@ __device__ void pair_producer(const CUtensorMap* tmA, const CUtensorMap* tmB, co
     if ((threadIdx.x & 31) != 0) return;  // one lane runs the whole loop
     int stage = 0;
     uint32_t phase = 0;
+    long long waited = 0;
     PairTileIter<MODE> it(p, dyn, int(rank));
     while (it.next()) {
         const int a_mn = p.a_mn_off + it.mblk * BM;
         const int b_mn = p.b_mn_off + it.nblk * BN + int(rank) * (BN / 2);
         const bool ok = pair_walk_k(dyn, [&](const int* kbs, int n) -> int {
+            const long long t0 = (kTrace && p.wait_cycles) ? clock64() : 0;
             if (!mbar_wait(smem_u32(&s.empty[stage]), phase ^ 1u, s.abort_flag, p.status, ERR_WAIT_SMEM_EMPTY)) return 0;
+            if (kTrace && p.wait_cycles) waited += clock64() - t0;
             const uint32_t bar_local = smem_u32(&s.full[stage]);
             const uint32_t bar_leader = map_to_cta(bar_local, 0);
             const uint32_t sa = smem_u32(s.stages + stage * P_STAGE_BYTES);
@@ -141,6 +144,7 @@ __device__ void pair_producer(const CUtensorMap* tmA, const CUtensorMap* tmB, co
         });
         if (!ok) return;
     }
+    if (kTrace && p.wait_cycles) atomicAdd(p.wait_cycles + 0, (unsigned long long)waited);
 }
 
 // leader CTA only; one lane runs the whole loop
@@ -151,6 +155,7 @@ __device__ void pair_mma(const EngineParams& p, const EngineSmem& s, const Dyn& 
     uint32_t phase = 0;
     int acc = 0;
     uint32_t acc_phase = 0;
+    long long waited_full = 0, waited_acc = 0;
     const uint32_t a_lbo = p.a_mn_major ? ATOM_BYTES : 16, b_lbo = p.b_mn_major ? ATOM_BYTES : 16;
     const uint64_t a_inc = (p.a_mn_major ? (UMMA_K / 8) * 1024 : UMMA_K * 2) >> 4;  // descriptor units per UMMA_K
     const uint64_t b_inc = (p.b_mn_major ? (UMMA_K / 8) * 1024 : UMMA_K * 2) >> 4;
@@ -170,7 +175,12 @@ __device__ void pair_mma(const EngineParams& p, const EngineSmem& s, const Dyn& 
     const uint32_t tfull_peer[2] = {map_to_cta(tfull_bar[0], 1), map_to_cta(tfull_bar[1], 1)};
     PairTileIter<MODE> it(p, dyn, 0);
     while (it.next()) {
-        if (!mbar_wait(smem_u32(&s.tempty[acc]), acc_phase ^ 1u, s.abort_flag, p.status, ERR_WAIT_TMEM_EMPTY)) return;
+        {
+            const long long t0 = (kTrace && p.wait_cycles) ? clock64() : 0;
+            if (!mbar_wait(smem_u32(&s.tempty[acc]), acc_phase ^ 1u, s.abort_flag, p.status, ERR_WAIT_TMEM_EMPTY))
+                return;
+            if (kTrace && p.wait_cycles) waited_acc += clock64() - t0;
+        }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         int n_issued = 0;
@@ -187,7 +197,9 @@ __device__ void pair_mma(const EngineParams& p, const EngineSmem& s, const Dyn& 
                     ep = empty_peer[i];
                 }
             }
+            const long long t0 = (kTrace && p.wait_cycles) ? clock64() : 0;
             if (!mbar_wait(fb, phase, s.abort_flag, p.status, ERR_WAIT_SMEM_FULL)) return 0;
+            if (kTrace && p.wait_cycles) waited_full += clock64() - t0;
             tc_fence_after();
 #pragma unroll
             for (int j = 0; j < P_KSUB; ++j) {
@@ -221,6 +233,10 @@ __device__ void pair_mma(const EngineParams& p, const EngineSmem& s, const Dyn& 
             acc_phase ^= 1u;
         }
     }
+    if (kTrace && p.wait_cycles) {
+        atomicAdd(p.wait_cycles + 1, (unsigned long long)waited_full);
+        atomicAdd(p.wait_cycles + 2, (unsigned long long)waited_acc);
+    }
 }
 
 template <int MODE>
@@ -244,6 +260,7 @@ pair_engine_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
     const Dyn dyn = load_dyn(p);
+    const long long t_start = (kTrace && p.wait_cycles) ? clock64() : 0;
 
     {   // a pair without a first item leaves before it sets up anything; uniform over the pair
         const PairTileIter<MODE> probe(p, dyn, 0);
@@ -313,6 +330,10 @@ pair_engine_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     if (p.clk_words && blockIdx.x == 0 && threadIdx.x == 0) {
         p.clk_words[2] = (unsigned long long)clock64();
         p.clk_words[3] = global_timer_ns();
+    }
+    if (kTrace && p.wait_cycles && threadIdx.x == 0) {
+        atomicAdd(p.wait_cycles + 4, (unsigned long long)(clock64() - t_start));
+        atomicAdd(p.wait_cycles + 5, 1ull);
     }
 }
 
