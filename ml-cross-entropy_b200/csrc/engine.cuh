@@ -36,11 +36,7 @@ enum { MODE_LSE = 0, MODE_PGRAD = 1, MODE_GEMM = 2 };
 #define CCE_TRACE 0
 #endif
 constexpr bool kTrace = CCE_TRACE != 0;
-// Epilogue of the forward and of the recompute: issue the tensor-memory load of the next 32-column
-// chunk before the math of the current one (1), or load, wait, compute (0).
-#ifndef CCE_EPI_PREFETCH
-#define CCE_EPI_PREFETCH 0
-#endif
+
 
 struct EngineParams {
     // extents of this launch
@@ -737,26 +733,16 @@ __device__ void epilogue_loop(const EngineParams& p, const EngineSmem& s, uint32
             }
         } else {
             uint32_t flag_bits = 0;  // MODE_PGRAD: activity of the current 64-column group
-            // one 32-column load from TMEM per step; the math of a step hides little of the next
-            // load's latency, yet deeper buffering measured slower here (register pressure)
+            // one 32-column load from TMEM per step; issuing the next chunk's load before the math of
+            // this one measured +1.5 % on the recompute and -1.3 % on the forward (250 / 155 registers):
+            // no gain under the power cap, so the simple form stays
             const bool from_tmem = true;
-#if CCE_EPI_PREFETCH
-            uint32_t rn[32];
-            tmem_ld32(taddr, rn);
-#endif
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
                 const int col0 = it.nblk * BN + c * 32;  // column within this launch
                 // warp-uniform; a pool slot is written in full (zeros past N) so no stale data stays in it
                 if (col0 >= p.N && !(MODE == MODE_PGRAD && p.sparse)) break;
                 float x[32];
-#if CCE_EPI_PREFETCH
-                // the load of this chunk was issued one step ago; the next one goes out before the math
-                tmem_ld_wait();
-#pragma unroll
-                for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(rn[j]);
-                if (c + 1 < BN / 32) tmem_ld32(taddr + (c + 1) * 32, rn);
-#else
                 uint32_t r[32];
                 if (from_tmem) {
                     tmem_ld32(taddr + c * 32, r);
@@ -764,7 +750,6 @@ __device__ void epilogue_loop(const EngineParams& p, const EngineSmem& s, uint32
                 }
 #pragma unroll
                 for (int j = 0; j < 32; ++j) x[j] = from_tmem ? __uint_as_float(r[j]) : 0.0f;
-#endif
 
                 if (MODE == MODE_LSE || MODE == MODE_PGRAD) {
                     if (p.bias) {
@@ -869,9 +854,6 @@ __device__ void epilogue_loop(const EngineParams& p, const EngineSmem& s, uint32
             }
         }
 
-#if CCE_EPI_PREFETCH
-        if (MODE != MODE_GEMM) tmem_ld_wait();  // a load issued ahead of a chunk that was not reached
-#endif
         // accumulator consumed: hand it back to the MMA warp
         tc_fence_before();
         __syncwarp();
