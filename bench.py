@@ -831,9 +831,13 @@ def main() -> None:
         peaks = measured_peaks()
         names = ["lse_forward", "logit_grad_recompute", "dE_dC_products"]
         per_kernel = {}
+        all_words = clk_words.tolist()
         for i, nm in enumerate(names):
             if k_n[i]:
                 per_kernel[nm] = {"launches_per_step": k_n[i] / args.steps, "ms_per_step": k_ms[i] / args.steps}
+                wk = all_words[4 * i: 4 * i + 4]  # block 0 of the last launch: cycles / nanoseconds
+                if wk[3] > wk[1] and wk[2] > wk[0]:
+                    per_kernel[nm]["sm_mhz_in_kernel"] = 1e3 * (wk[2] - wk[0]) / (wk[3] - wk[1])
         # dominant kernel: one forward launch does 2*B*D*V_local algorithmic FLOP (B = rows that enter the loss)
         dom = max(range(3), key=lambda i: k_ms[i])
         alg_per_launch = {0: 2.0 * n_valid * D * v_local,

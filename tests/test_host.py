@@ -309,3 +309,18 @@ def test_reference_and_this_package_import_side_by_side():
     assert "baseline/_ref" in ref.__file__ and "ml-cross-entropy_b200" in ours.__file__
     assert sys.modules["cce_reference"] is ref and "cce_reference.utils" in sys.modules
     assert hasattr(ref, "linear_cross_entropy") and ref.linear_cross_entropy is not ours.linear_cross_entropy
+
+
+def test_mode_switches_of_the_python_layer():
+    """set_sync_free / set_vocab_ordering return the previous setting and reject unknown modes."""
+    from cut_cross_entropy import cce
+
+    prev = cce.set_sync_free(False)
+    assert cce.set_sync_free(True) is False and cce.set_sync_free(prev) is True
+    prev = cce.set_vocab_ordering("mean")
+    assert cce.set_vocab_ordering(True) == "mean" and cce.set_vocab_ordering(False) == "max"
+    assert cce.set_vocab_ordering(prev) == "off"
+    with pytest.raises(ValueError):
+        cce.set_vocab_ordering("alphabetical")
+    k = torch.tensor([0.5, 3.0, -1.0, 2.0])
+    assert cce.sort_logit_avg(k).tolist() == [1, 3, 0, 2] and cce.sort_logit_avg(k).dtype == torch.int32
