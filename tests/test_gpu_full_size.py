@@ -170,8 +170,8 @@ def test_full_size_against_float32(cfg_name):
 
 def test_full_size_properties():
     """Size-independent checks at the Gemma-2-2B head size: linearity in the upstream gradient,
-    mean = sum / count, independence of the chunking of the vocabulary, agreement of the filtered
-    variants with the exact one."""
+    mean = sum / count, independence of the chunking of the vocabulary, agreement of the unfiltered
+    products of the half-filtered variants with the exact one."""
     from cut_cross_entropy import linear_cross_entropy
 
     cfg = bench.CONFIGS["gemma2-2b-head"]
@@ -205,19 +205,17 @@ def test_full_size_properties():
     torch.testing.assert_close(dc3, dc1, rtol=0, atol=0)
     _check_grad(de3, de1, "dE under a different chunking")
 
-    # Filtered variants against the exact one.  On this synthetic data every non-label probability
-    # (~1/V) is below the threshold, so the filter removes the whole softmax part of dE — about
-    # sigma_c^2 * |e| / |c_label| ~ 2 % of the largest entry — which any implementation of the
-    # reference's filter rule does; hence the looser numbers here.  An unfiltered product of a
-    # half-filtered variant must still match the exact one tightly.
-    for impl in ("cce", "cce_kahan_full_c", "cce_kahan_full_e"):
+    # Half-filtered variants: the product that is NOT filtered must match the exact one at the stated
+    # tolerances.  (What a filtered product may differ by is bounded by the reference's own filter on
+    # the same GPU and tensors in tests/test_gpu_reference.py, and by the element-wise droppable mass
+    # in test_full_size_against_float32.)
+    for impl in ("cce_kahan_full_c", "cce_kahan_full_e"):
         lf, def_, dcf = grads(impl)
         torch.testing.assert_close(lf, l1, rtol=0, atol=0)
-        e_filtered, c_filtered = impl != "cce_kahan_full_e", impl != "cce_kahan_full_c"
-        _check_grad(def_, de1, f"dE {impl} vs exact", rel=5e-2 if e_filtered else 1e-2,
-                    min_cos=0.999 if e_filtered else 0.9999)
-        _check_grad(dcf, dc1, f"dC {impl} vs exact", rel=5e-2 if c_filtered else 1e-2,
-                    min_cos=0.999 if c_filtered else 0.9999)
+        if impl == "cce_kahan_full_e":
+            _check_grad(def_, de1, f"dE {impl} vs exact")
+        else:
+            _check_grad(dcf, dc1, f"dC {impl} vs exact")
     # the fully filtered variant must give identical results with a tile pool too small for one pass
     lf, de_a, dc_a = grads("cce")
     os.environ["CCE_B200_GBUF_MB"] = "64"
