@@ -489,3 +489,54 @@ def test_row_count_on_the_device_gives_the_same_bits_as_reading_it_back(impl, re
             assert b is None
         else:
             torch.testing.assert_close(a, b, rtol=0, atol=0, equal_nan=True)
+
+
+@pytest.mark.parametrize("impl", ["cce", "cce_exact"])
+def test_forward_and_backward_can_be_captured_in_a_cuda_graph(impl):
+    """With the row count kept on the device nothing in forward or backward waits for the GPU, so a
+    whole step can be captured once and replayed: the replay gives the bits of the eager step, also
+    after the inputs were overwritten in place."""
+    from cut_cross_entropy import cce as cce_mod
+    from cut_cross_entropy import linear_cross_entropy
+
+    prev = cce_mod.set_sync_free(True)
+    try:
+        e, c, _, t = planted_inputs(512, 4096, 256, torch.bfloat16, DEV, seed=5, ignored=0.2)
+        e.requires_grad_(True)
+        c.requires_grad_(True)
+
+        def step():
+            loss = linear_cross_entropy(e, c, t, impl=impl, softcap=30.0)
+            loss.backward()
+            return loss
+
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):  # warm-up off the default stream, as graph capture wants
+            for _ in range(3):
+                e.grad = c.grad = None
+                step()
+        torch.cuda.current_stream().wait_stream(side)
+        e.grad = c.grad = None
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            loss_g = step()
+        de_g, dc_g = e.grad, c.grad  # static tensors the replay writes into
+
+        for seed in (5, 6):  # the captured inputs, then new values written into the same tensors
+            e2, c2, _, t2 = planted_inputs(512, 4096, 256, torch.bfloat16, DEV, seed=seed, ignored=0.2)
+            with torch.no_grad():
+                e.copy_(e2)
+                c.copy_(c2)
+                t.copy_(t2)
+            graph.replay()
+            torch.cuda.synchronize()
+            got = (loss_g.detach().clone(), de_g.clone(), dc_g.clone())
+            ee, cc = e.detach().clone().requires_grad_(True), c.detach().clone().requires_grad_(True)
+            want_loss = linear_cross_entropy(ee, cc, t, impl=impl, softcap=30.0)
+            want_loss.backward()
+            torch.testing.assert_close(got[0], want_loss.detach(), rtol=0, atol=0)
+            torch.testing.assert_close(got[1], ee.grad, rtol=0, atol=0)
+            torch.testing.assert_close(got[2], cc.grad, rtol=0, atol=0)
+    finally:
+        cce_mod.set_sync_free(prev)
