@@ -13,7 +13,7 @@ import torch
 
 from . import _native
 from .utils import TensorInfo
-from .vocab_parallel.utils import vp_reduce_e_grad_
+from .vocab_parallel.utils import vp_reduce_e_grad_, vp_reduce_e_grad_cast
 
 
 _REDUCE_STREAMS: dict = {}
@@ -171,7 +171,14 @@ def cce_backward_kernel(
             main, side = torch.cuda.current_stream(dev), _reduce_stream(dev)
             side.wait_event(de_ready)
             with torch.cuda.stream(side):
-                vp_reduce_e_grad_(de, pg)
+                if e_info.dtype in (torch.float16, torch.bfloat16):
+                    # fp32 reduce-scatter, cast, 16-bit all-gather: the fp32 sum of the reference with less traffic
+                    reduced = vp_reduce_e_grad_cast(de, e_info.dtype, pg)
+                    de.record_stream(side)
+                    de = reduced
+                else:
+                    vp_reduce_e_grad_(de, pg)
+            de.record_stream(main)
             de.record_stream(side)
             main.wait_stream(side)  # enqueued after the last dC product, which therefore overlaps the reduction
         else:

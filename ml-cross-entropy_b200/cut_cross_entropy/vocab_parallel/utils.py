@@ -80,6 +80,31 @@ def vp_merge_forward(
     return lse, neg_dot
 
 
+def vp_reduce_e_grad_cast(
+    e_grad_f32: torch.Tensor, out_dtype: torch.dtype, pg: "dist.ProcessGroup | None"
+) -> torch.Tensor:
+    """Sum of the partial ``dE`` over the group in fp32, returned in ``out_dtype``: a reduce-scatter
+    of the fp32 partial sums, a cast of this rank's slice, and an all-gather of the 16-bit slices.
+    Same arithmetic as an fp32 all-reduce followed by the cast (reference
+    ``vocab_parallel/utils.py:68-76``) with a quarter less traffic, since the second half of the
+    exchange moves 2-byte values."""
+    assert e_grad_f32.dtype == torch.float32 and e_grad_f32.is_contiguous()
+    world = dist.get_world_size(pg)
+    flat = e_grad_f32.view(-1)
+    n = flat.numel()
+    per = -(-n // world)
+    if per * world != n:  # pad to a multiple of the group size
+        padded = flat.new_zeros(per * world)
+        padded[:n] = flat
+        flat = padded
+    mine = flat.new_empty(per)
+    dist.reduce_scatter_tensor(mine, flat, group=pg)
+    mine_lp = mine.to(out_dtype)
+    out = mine_lp.new_empty(per * world)
+    dist.all_gather_into_tensor(out, mine_lp, group=pg)
+    return out[:n].view(e_grad_f32.shape)
+
+
 def vp_reduce_e_grad_(e_grad_f32: torch.Tensor, pg: "dist.ProcessGroup | None") -> torch.Tensor:
     """In-place fp32 sum of the partial ``dE`` over the group."""
     assert e_grad_f32.dtype == torch.float32
