@@ -647,6 +647,7 @@ def main() -> None:
     L.cce_b200_profile_enable(0)
     L.cce_b200_profile_clock_words(None)
     L.cce_b200_profile_tile_counts(None)
+    tile_counts_main = tile_counts.tolist()  # of the timed steps (the array is reused further down)
     k_ms = (ctypes.c_double * 3)()
     k_n = (ctypes.c_int64 * 3)()
     L.cce_b200_profile_read(k_ms, k_n)
@@ -857,7 +858,7 @@ def main() -> None:
         peak = peaks["burst"] if use_burst else peaks["sustained"]
         traffic_meas = FORWARD_DRAM_BYTES_MEASURED.get(args.config) if (dom == 0 and world == 1) else None
         traffic_est = FORWARD_DRAM_TRAFFIC_RATIO_SMALL_CASE * 2.0 * (n_valid * D + v_local * D) if dom == 0 else None
-        tc = tile_counts.tolist()
+        tc = tile_counts_main
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",

@@ -1095,7 +1095,7 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
             tile_counts = g_tile_counts;
         }
         tile_index_kernel<<<1, 1024, sm_bytes, st>>>(act, pl.n_rb, pl.n_vt, pl.capacity, pl.max_pass, col_ptr, slot_tile,
-                                                    slot_of, row_ptr, row_slots, pass_info, tile_counts);
+                                                    slot_of, row_ptr, row_slots, pass_info, tile_counts, B, ndev);
         CCE_LAUNCH_CHECK();
 
         CUtensorMap tmP_k, tmP_mn;  // the pool seen as a [capacity*128][256] matrix

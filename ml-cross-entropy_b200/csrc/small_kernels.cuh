@@ -330,7 +330,7 @@ __global__ void tile_index_kernel(const uint8_t* __restrict__ act, int n_rb, int
                                   int max_pass, int* __restrict__ col_ptr, int* __restrict__ slot_tile,
                                   int* __restrict__ slot_of, int* __restrict__ row_ptr,
                                   int* __restrict__ row_slots, int* __restrict__ pass_info,
-                                  int* __restrict__ counts_out) {
+                                  int* __restrict__ counts_out, long long n_rows, const long long* __restrict__ n_dev) {
     extern __shared__ int sm[];
     int* col_s = sm;              // [n_vt + 1] column counts, then column starts
     int* row_s = sm + n_vt + 1;   // [n_rb + 1] row counts, then row starts
@@ -417,7 +417,7 @@ __global__ void tile_index_kernel(const uint8_t* __restrict__ act, int n_rb, int
         }
         if (counts_out) {  // optional report: {active tiles, all tiles, passes that hold tiles}
             counts_out[0] = total;
-            counts_out[1] = n_rb * n_vt;
+            counts_out[1] = int((actual_rows(n_rows, n_dev) + 127) / 128) * n_vt;  // row blocks that hold rows
             counts_out[2] = total > 0 ? pass + 1 : 0;
         }
         for (int q = pass + 1; q < max_pass; ++q) {
