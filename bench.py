@@ -566,6 +566,9 @@ def main() -> None:
     ap.add_argument("--no-extras", action="store_true",
                     help="skip phases/op-memory, cce_exact, sustained, reference-on-GPU, peaked and cfg5 extras")
     ap.add_argument("--no-ref-gpu", action="store_true", help="skip timing the reference's implementations")
+    ap.add_argument("--wait-trace", action="store_true",
+                    help="add `wait_shares`: where each role of the pipeline kernels waits (needs the library built "
+                         "with `python -m cut_cross_entropy._build --trace`, selected with CCE_B200_LIB)")
     ap.add_argument("--profile-mode", action="store_true",
                     help="for runs under a profiler: honour --warmup below 3, skip everything but the timed steps")
     args = ap.parse_args()
@@ -683,6 +686,25 @@ def main() -> None:
         extras["sustained"] = {"tokens_per_s": n_tok / (ms_long / n_long * 1e-3), "ms_per_step": ms_long / n_long,
                                "steps": n_long, "seconds": ms_long * 1e-3, "sm_mhz_median": (clocks2 or {}).get("sm_mhz"),
                                "power_w_max": (clocks2 or {}).get("power_w_max"), "reasons": (clocks2 or {}).get("reasons")}
+
+    if args.wait_trace:
+        # one more step with the pipeline's wait counters on (tracing build only)
+        cnt = torch.zeros(24, dtype=torch.int64, device=dev)
+        if L.cce_b200_profile_wait_counters(cnt.data_ptr()) == 0:
+            step(*tensors)
+            torch.cuda.synchronize()
+            L.cce_b200_profile_wait_counters(None)
+            shares = {}
+            for nm, r in zip(("lse_forward", "logit_grad_recompute", "dE_dC_products"), cnt.view(3, 8).tolist()):
+                life, ctas = max(r[4], 1), max(r[5], 1)
+                shares[nm] = {"ctas": r[5], "mcycles_per_cta": r[4] / ctas / 1e6,
+                              "producer_waits_for_free_stage": r[0] / life, "mma_waits_for_filled_stage": r[1] / life,
+                              "mma_waits_for_free_accumulator": r[2] / life, "epilogue_waits_for_accumulator": r[3] / life}
+            extras["wait_shares"] = {"per_kernel": shares,
+                                     "note": "shares of the summed CTA lifetimes; in the CTA-pair form only the leader of a "
+                                             "pair issues MMAs, so its two mma_* shares are to be doubled"}
+        else:
+            extras["wait_shares"] = {"unavailable": "this build of the library has no wait counters (build with --trace)"}
 
     if world > 1:
         # ---- gradient parity of the sharded run: this rank recomputes the UNSHARDED exact gradients
