@@ -405,18 +405,30 @@ void base_params(EngineParams* p, long long M, long long N, long long K, int fmt
 }
 
 // ---- backward planning
-long long gbuf_cap_bytes() {
+long long gbuf_cap_bytes(bool* from_env = nullptr) {
     long long cap_bytes = 512LL << 20;
+    if (from_env) *from_env = false;
     if (const char* env = getenv("CCE_B200_GBUF_MB")) {
         long long mb = atoll(env);
-        if (mb >= 1) cap_bytes = mb << 20;
+        if (mb >= 1) {
+            cap_bytes = mb << 20;
+            if (from_env) *from_env = true;
+        }
     }
     return cap_bytes;
 }
 
 long long pick_chunk(long long n_rows, long long V, long long D) {
     const long long v_round = cdiv(V, BN) * BN;
-    long long cap = gbuf_cap_bytes() / (2 * (n_rows > 0 ? n_rows : 1)) / BN * BN;
+    bool from_env = false;
+    long long cap_bytes = gbuf_cap_bytes(&from_env);
+    if (!from_env) {
+        // Every vocabulary chunk costs a read-modify-write pass over the fp32 dE scratch and a round
+        // of launches: a long batch gets a larger buffer (up to 2 GB) so that it needs at most 16 chunks.
+        const long long for_16 = cdiv(2 * (n_rows > 0 ? n_rows : 1) * v_round, 16);
+        cap_bytes = std::max(cap_bytes, std::min(for_16, 2048LL << 20));
+    }
+    long long cap = cap_bytes / (2 * (n_rows > 0 ? n_rows : 1)) / BN * BN;
     if (cap < BN) cap = BN;
     if (cap >= v_round) return v_round;
     // among widths within [cap/2, cap] prefer the one whose dC product fills whole waves of CTAs
