@@ -540,3 +540,66 @@ def test_forward_and_backward_can_be_captured_in_a_cuda_graph(impl):
             torch.testing.assert_close(got[2], cc.grad, rtol=0, atol=0)
     finally:
         cce_mod.set_sync_free(prev)
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_random_shapes_against_float32(seed):
+    """Random (rows, vocabulary, hidden) sizes, odd ones included: ragged last row block and
+    vocabulary tile, reduction tails, one or many row blocks (single-CTA and CTA-pair pipelines),
+    hidden sizes TMA cannot address directly.  Exact variant at the stated tolerances, and the
+    filtered default against the exact one within the filter bound."""
+    from cut_cross_entropy import linear_cross_entropy
+
+    g = torch.Generator().manual_seed(1000 + seed)
+    N = int(torch.randint(1, 900, (1,), generator=g))
+    V = int(torch.randint(2, 3000, (1,), generator=g))
+    D = int(torch.randint(1, 700, (1,), generator=g))
+    if seed % 3 == 0:
+        D = (D + 63) // 64 * 64  # the common case: whole swizzle rows
+    softcap = 25.0 if seed % 2 else None
+    e, c, bias, t = planted_inputs(N, V, D, torch.bfloat16, DEV, seed=seed, bias=seed % 4 == 1, ignored=0.15)
+    if bias is not None:
+        bias = bias.float().requires_grad_(True)
+    e.requires_grad_(True)
+    c.requires_grad_(True)
+    keep = t != IGNORE
+    if not bool(keep.any()):
+        t[0] = 0
+        keep = t != IGNORE
+    x = e.detach().float()[keep] @ c.detach().float().T
+    if bias is not None:
+        x = x + bias.detach()
+    if softcap is not None:
+        x = torch.tanh(x / softcap) * softcap
+    want_lse = torch.logsumexp(x, -1)
+    ee = e.detach().float().requires_grad_(True)
+    cc = c.detach().float().requires_grad_(True)
+    bb = None if bias is None else bias.detach().clone().requires_grad_(True)
+    y = ee[keep] @ cc.T
+    if bb is not None:
+        y = y + bb
+    if softcap is not None:
+        y = torch.tanh(y / softcap) * softcap
+    want_loss = torch.nn.functional.cross_entropy(y, t[keep])
+    want_loss.backward()
+    grads = {}
+    for impl in ("cce_exact", "cce"):
+        e.grad = c.grad = None
+        if bias is not None:
+            bias.grad = None
+        loss, lse = linear_cross_entropy(e, c, t, bias=bias, softcap=softcap, impl=impl, return_lse=True)
+        loss.backward()
+        assert abs(loss.item() - want_loss.item()) <= 1e-3 * abs(want_loss.item()) + 1e-5, (N, V, D)
+        assert (lse[keep] - want_lse).abs().max().item() <= 2e-3, (N, V, D)
+        grads[impl] = (e.grad.float().clone(), c.grad.float().clone())
+    for got, want, what in ((grads["cce_exact"][0], ee.grad, "dE"), (grads["cce_exact"][1], cc.grad, "dC")):
+        scale = want.abs().max().item()
+        assert (got - want).abs().max().item() <= 1e-2 * scale + 1e-7, (what, N, V, D)
+    # the filter drops entries below eps only: per element at most eps * (sum of |operand| over the reduction)
+    eps = 2.0**-12 / max(int(keep.sum()), 1)
+    bound_e = eps * c.detach().float().abs().sum(0)  # per hidden column
+    bound_c = eps * e.detach().float()[keep].abs().sum(0)
+    de_x, dc_x = grads["cce_exact"]
+    de_f, dc_f = grads["cce"]
+    assert ((de_f - de_x).abs() <= bound_e + 1e-2 * de_x.abs().max() + 1e-7).all(), (N, V, D)
+    assert ((dc_f - dc_x).abs() <= bound_c + 1e-2 * dc_x.abs().max() + 1e-7).all(), (N, V, D)
