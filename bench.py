@@ -794,8 +794,15 @@ def main() -> None:
             for _ in range(2):
                 step_x(*tensors)
             L.cce_b200_profile_enable(1)
+            clk_x = torch.zeros(12, dtype=torch.int64, device=dev)
+            L.cce_b200_profile_clock_words(clk_x.data_ptr())
             ms_x, _ = time_steps(step_x, tensors, 5, barrier)
+            L.cce_b200_profile_clock_words(None)
             L.cce_b200_profile_enable(0)
+            wx = clk_x.tolist()
+            mhz_x = [1e3 * (wx[4 * i + 2] - wx[4 * i]) / (wx[4 * i + 3] - wx[4 * i + 1])
+                     if wx[4 * i + 3] > wx[4 * i + 1] else None for i in range(3)]
+            n_sm_x = torch.cuda.get_device_properties(dev).multi_processor_count
             x_ms = (ctypes.c_double * 3)()
             x_n = (ctypes.c_int64 * 3)()
             L.cce_b200_profile_read(x_ms, x_n)
@@ -805,6 +812,14 @@ def main() -> None:
                 "executed_tflops": 8.0 * n_valid * D * cfg["V"] / (ms_x * 1e-3) / 1e12,
                 "tflops_6NDV": 6.0 * n_tok * D * cfg["V"] / (ms_x * 1e-3) / 1e12,
                 "kernels_ms": {"lse_forward": x_ms[0] / 5, "logit_grad_recompute": x_ms[1] / 5, "dE_dC_products": x_ms[2] / 5},
+                "sm_mhz_in_kernel": {"lse_forward": mhz_x[0], "logit_grad_recompute": mhz_x[1], "dE_dC_products": mhz_x[2]},
+                # executed FLOP of each kernel (2, 2 and 4 B*D*V) over its time, as a share of the tensor
+                # pipe's peak (SMs x 8192 FLOP per cycle) at the clock it ran at
+                "frac_of_pipe_peak_at_kernel_clock": {
+                    nm: (mult * n_valid * D * cfg["V"] / (x_ms[i] / 5 * 1e-3)) / (n_sm_x * 8192 * mhz_x[i] * 1e6)
+                    if (mhz_x[i] and x_ms[i]) else None
+                    for i, (nm, mult) in enumerate((("lse_forward", 2.0), ("logit_grad_recompute", 2.0),
+                                                    ("dE_dC_products", 4.0)))},
                 "what": "nothing filtered: forward + recompute + both products = 8*B*D*V executed FLOP "
                         "(B = rows in the loss); tflops_6NDV uses the nominal row count"}}
         # ---- a peaked softmax, natural order against vocabulary ordering
