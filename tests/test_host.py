@@ -209,6 +209,14 @@ def test_backward_planning_respects_the_logit_gradient_buffer_cap(monkeypatch):
     assert tiny < 2 << 20
     # without a gradient for e there is no fp32 dE scratch
     assert need(8192, 256000, 2304, True) - need(8192, 256000, 2304, True, d_e=None) >= de32
+    # a long batch (chunked form): the buffer grows so that 16 chunks suffice, up to 2 GB; an explicit cap is kept
+    g16 = 2 * 65536 * 152064 / 16
+    long_batch = need(65536, 152064, 3584, False)
+    # (the chunk width is then rounded down to whole waves of CTAs, to no less than half of it)
+    assert g16 / 2 - (64 << 20) < long_batch - 65536 * 3584 * 4 < g16 + (64 << 20), long_batch
+    assert long_batch > need(65536, 152064, 3584, False, mb=512)
+    assert need(65536, 152064, 3584, False, mb=512) - 65536 * 3584 * 4 < (512 << 20) + (64 << 20)
+    assert need(400000, 152064, 3584, False) - 400000 * 3584 * 4 < (2048 << 20) + (256 << 20)
     # refused descriptions
     assert L.cce_b200_backward_workspace_bytes(None) == 0
 
