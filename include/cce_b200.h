@@ -232,7 +232,24 @@ typedef struct cce_b200_backward_args {
      * (vocab parallelism) can wait for this event on another stream and run the reduction while the
      * rest of dC is computed.  NULL: no event, dC before dE throughout. */
     void* de_ready_event;
+    /* Optional: the cross-rank sum of dE (vocabulary parallelism) fused into the dE product.  With
+     * de_peer_world > 1, de_peer_acc[r] is rank r's accumulator (cce_b200_peer_buffer_create on rank r,
+     * cce_b200_peer_buffer_open here; this rank's own entry is its local pointer), each
+     * [cce_b200_de_peer_rows(op.n_rows, world)][D] fp32 and all zeros.  Every rank must run the same
+     * rows (same valids) with the same op.n_rows.  The product kernels then add each 128-row block of
+     * this rank's partial dE into the accumulator of rank (block % world) with red.add over NVLink
+     * instead of writing it locally; d_e is only cleared (rows outside valids), de_ready_event is
+     * recorded after the last dE product, and the caller finishes with a barrier over the ranks,
+     * cce_b200_de_peer_collect, an all-gather of the slices and cce_b200_de_peer_scatter.  At most
+     * CCE_B200_MAX_PEERS ranks.  0 or 1: dE is written to d_e as described above. */
+    int32_t de_peer_world;
+    /* With de_ready_event: SMs the dC product launched after that event leaves free, so that the
+     * caller's exchange of dE (collective kernels on another stream) can run beside it; the product
+     * is a persistent kernel that otherwise holds every SM until it ends.  0: none. */
+    int32_t exchange_sms;
+    float* de_peer_acc[8];
 } cce_b200_backward_args;
+#define CCE_B200_MAX_PEERS 8
 
 /* Gradient of sum_i d_out_i * grad_scale * (lse_i - logit_i[t_i]) + sum_i d_lse_i * lse_i
  * with respect to e, c and bias.  Accumulation is fp32 throughout.
@@ -240,6 +257,35 @@ typedef struct cce_b200_backward_args {
 size_t cce_b200_backward_workspace_bytes(const cce_b200_backward_args* a);
 int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t workspace_bytes,
                       void* stream);
+
+/* ---- Peer-shared buffers and the tail of the fused dE reduction (one process per GPU on one node).
+ * The reference sums dE over the ranks with an all-reduce after the kernel
+ * (cut_cross_entropy/vocab_parallel/utils.py:68-76, called from cce_backward.py:508-509); here the
+ * product kernel adds its tiles straight into the owning rank's memory.
+ *
+ * create: cudaMalloc of `bytes` on the current device, cleared, with the 64-byte inter-process
+ *         handle of the allocation written to handle_out (host).
+ * open:   maps another process's buffer from its handle (peer access is enabled on first use).
+ * close / destroy: unmap a buffer opened here / free a buffer created here. */
+#define CCE_B200_PEER_HANDLE_BYTES 64
+int cce_b200_peer_buffer_create(size_t bytes, void** ptr_out, void* handle_out);
+int cce_b200_peer_buffer_open(const void* handle, void** ptr_out);
+int cce_b200_peer_buffer_close(void* ptr);
+int cce_b200_peer_buffer_destroy(void* ptr);
+/* Rows of one rank's accumulator for n_rows rows over `world` ranks: whole 128-row blocks, dealt
+ * round-robin. */
+int64_t cce_b200_de_peer_rows(int64_t n_rows, int32_t world);
+/* After a barrier over the ranks that follows every rank's cce_b200_backward: writes this rank's
+ * accumulator [acc_rows][D] to slice_out in `dtype` (CCE_DT_*) and clears the accumulator.
+ * status_workspace: the workspace of that cce_b200_backward call (its status word turns the slice
+ * into NaN when a kernel of this rank abandoned a wait), or NULL. */
+int cce_b200_de_peer_collect(float* acc, int64_t acc_rows, int64_t D, void* slice_out, int32_t dtype,
+                             const void* status_workspace, void* stream);
+/* gathered: the ranks' slices in rank order [world][acc_rows][D]; copies row i of the reduced dE to
+ * d_e[rows[i]] (rows NULL: d_e[i]); rows the list does not name are left as cce_b200_backward cleared them. */
+int cce_b200_de_peer_scatter(const void* gathered, int32_t world, int64_t acc_rows, int64_t D, int32_t dtype,
+                             const void* rows, int32_t rows_dtype, int64_t n_rows, const int64_t* n_rows_dev,
+                             void* d_e, void* stream);
 
 /* Synchronises `stream` and returns CCE_OK or CCE_ERR_KERNEL_WAIT; the raw word goes to *word.
  * Without this read an abandoned wait still shows: the log-sum-exp (hence the loss) and dE of that

@@ -111,13 +111,13 @@ int device_info(DeviceInfo** out) {
         CCE_CUDA(cudaFuncSetAttribute(engine_kernel<MODE_PGRAD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       ENGINE_SMEM));
         CCE_CUDA(cudaFuncSetAttribute(engine_kernel<MODE_GEMM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      ENGINE_SMEM));
+                                      ENGINE_SMEM + PEER_STAGE_BYTES));
         CCE_CUDA(cudaFuncSetAttribute(pair_engine_kernel<MODE_LSE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       PAIR_SMEM));
         CCE_CUDA(cudaFuncSetAttribute(pair_engine_kernel<MODE_PGRAD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       PAIR_SMEM));
         CCE_CUDA(cudaFuncSetAttribute(pair_engine_kernel<MODE_GEMM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      PAIR_SMEM));
+                                      PAIR_SMEM + PEER_STAGE_BYTES));
         d.attr_set = true;
     }
     *out = &d;
@@ -373,11 +373,12 @@ int launch_engine(const CUtensorMap& a, const CUtensorMap& b, const EngineParams
         CCE_CUDA(cudaEventCreate(&rec.stop));
         CCE_CUDA(cudaEventRecord(rec.start, st));
     }
+    const size_t stage_extra = (MODE == MODE_GEMM && pp.peer_world > 0) ? PEER_STAGE_BYTES : 0;
     if (pair) {
         pp.idesc = (pp.idesc & ~(0x1fu << 24)) | ((uint32_t(2 * BM) >> 4) << 24);  // M = 256 over the pair
-        pair_engine_kernel<MODE><<<grid, ENGINE_THREADS, PAIR_SMEM, st>>>(a, b, pp);
+        pair_engine_kernel<MODE><<<grid, ENGINE_THREADS, PAIR_SMEM + stage_extra, st>>>(a, b, pp);
     } else {
-        engine_kernel<MODE><<<grid, ENGINE_THREADS, ENGINE_SMEM, st>>>(a, b, pp);
+        engine_kernel<MODE><<<grid, ENGINE_THREADS, ENGINE_SMEM + stage_extra, st>>>(a, b, pp);
     }
     CCE_LAUNCH_CHECK();
     if (prof) {
@@ -621,6 +622,97 @@ int cce_b200_read_status(const void* workspace, void* stream, int32_t* word) {
     return w == 0 ? CCE_OK : CCE_ERR_KERNEL_WAIT;
 }
 
+// ---- peer-shared buffers and the tail of the fused dE reduction
+int cce_b200_peer_buffer_create(size_t bytes, void** ptr_out, void* handle_out) {
+    if (!ptr_out || !handle_out || bytes == 0) return CCE_ERR_ARG;
+    static_assert(sizeof(cudaIpcMemHandle_t) == CCE_B200_PEER_HANDLE_BYTES, "handle size");
+    void* p = nullptr;
+    CCE_CUDA(cudaMalloc(&p, bytes));
+    cudaError_t e = cudaMemset(p, 0, bytes);
+    cudaIpcMemHandle_t h;
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+    if (e != cudaSuccess) {
+        cudaFree(p);
+        CCE_CUDA(e);
+    }
+    memcpy(handle_out, &h, sizeof(h));
+    *ptr_out = p;
+    return CCE_OK;
+}
+
+int cce_b200_peer_buffer_open(const void* handle, void** ptr_out) {
+    if (!handle || !ptr_out) return CCE_ERR_ARG;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof(h));
+    void* p = nullptr;
+    CCE_CUDA(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+    *ptr_out = p;
+    return CCE_OK;
+}
+
+int cce_b200_peer_buffer_close(void* ptr) {
+    if (!ptr) return CCE_ERR_ARG;
+    CCE_CUDA(cudaIpcCloseMemHandle(ptr));
+    return CCE_OK;
+}
+
+int cce_b200_peer_buffer_destroy(void* ptr) {
+    if (!ptr) return CCE_ERR_ARG;
+    CCE_CUDA(cudaFree(ptr));
+    return CCE_OK;
+}
+
+int64_t cce_b200_de_peer_rows(int64_t n_rows, int32_t world) {
+    if (n_rows < 0 || world < 1) return 0;
+    return cdiv(cdiv(n_rows, BM), world) * BM;
+}
+
+int cce_b200_de_peer_collect(float* acc, int64_t acc_rows, int64_t D, void* slice_out, int32_t dtype,
+                             const void* status_workspace, void* stream) {
+    if (!acc || !slice_out || acc_rows < 0 || D <= 0 || acc_rows % BM != 0) return CCE_ERR_ARG;
+    if ((reinterpret_cast<uintptr_t>(acc) | reinterpret_cast<uintptr_t>(slice_out)) & 15) return CCE_ERR_ALIGN;
+    DeviceInfo* dev = nullptr;
+    int rc = device_info(&dev);
+    if (rc != CCE_OK) return rc;
+    const long long n = acc_rows * D;
+    if (n == 0) return CCE_OK;
+    const unsigned grid = (unsigned)std::min<long long>(cdiv(n / 4, 256), (long long)dev->sms * 8);
+    const int* status = reinterpret_cast<const int*>(status_workspace);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == CCE_DT_F32)
+        peer_collect_kernel<float><<<grid, 256, 0, st>>>(acc, n, reinterpret_cast<float*>(slice_out), status);
+    else if (dtype == CCE_DT_BF16)
+        peer_collect_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(acc, n, reinterpret_cast<__nv_bfloat16*>(slice_out), status);
+    else if (dtype == CCE_DT_F16)
+        peer_collect_kernel<__half><<<grid, 256, 0, st>>>(acc, n, reinterpret_cast<__half*>(slice_out), status);
+    else
+        return CCE_ERR_ARG;
+    CCE_LAUNCH_CHECK();
+    return CCE_OK;
+}
+
+int cce_b200_de_peer_scatter(const void* gathered, int32_t world, int64_t acc_rows, int64_t D, int32_t dtype,
+                             const void* rows, int32_t rows_dtype, int64_t n_rows, const int64_t* n_rows_dev,
+                             void* d_e, void* stream) {
+    if (!gathered || !d_e || world < 1 || acc_rows < 0 || D <= 0 || n_rows < 0) return CCE_ERR_ARG;
+    if (n_rows > acc_rows * world) return CCE_ERR_ARG;
+    if (n_rows == 0) return CCE_OK;
+    if (n_rows > 0x7fffffffLL) return CCE_ERR_TOO_LARGE;
+    cudaStream_t st = (cudaStream_t)stream;
+    const long long* ndev = reinterpret_cast<const long long*>(n_rows_dev);
+    const int i64 = rows_dtype == CCE_IDX_I64;
+    if (dtype == CCE_DT_F32)
+        peer_scatter_kernel<float><<<(unsigned)n_rows, 128, 0, st>>>(reinterpret_cast<const float*>(gathered), world, acc_rows, D,
+                                                                    rows, i64, reinterpret_cast<float*>(d_e), n_rows, ndev);
+    else if (dtype == CCE_DT_BF16 || dtype == CCE_DT_F16)
+        peer_scatter_kernel<uint16_t><<<(unsigned)n_rows, 128, 0, st>>>(reinterpret_cast<const uint16_t*>(gathered), world, acc_rows,
+                                                                       D, rows, i64, reinterpret_cast<uint16_t*>(d_e), n_rows, ndev);
+    else
+        return CCE_ERR_ARG;
+    CCE_LAUNCH_CHECK();
+    return CCE_OK;
+}
+
 int cce_b200_profile_enable(int on) {
     std::lock_guard<std::mutex> lock(g_prof_mu);
     g_prof_on = on != 0;
@@ -851,7 +943,7 @@ int cce_b200_loss_tail(const float* stats, int32_t world, int64_t n_rows, const 
         if (lse_scatter) CCE_CUDA(cudaMemsetAsync(lse_scatter, 0, (size_t)n_total * sizeof(float), st));
     }
     if (n_rows == 0 && reduction == 2) return CCE_OK;  // (an upper bound of 0 leaves nothing to scatter either)
-    loss_tail_kernel<<<1, TAIL_THREADS, 0, st>>>(stats, world, n_rows, rows, rows_dtype == CCE_IDX_I64, shift, reduction,
+    loss_tail_kernel<<<TAIL_CTAS, TAIL_THREADS, 0, st>>>(stats, world, n_rows, rows, rows_dtype == CCE_IDX_I64, shift, reduction,
                                                  lse_rows, loss_out, lse_scatter,
                                                  reinterpret_cast<const int*>(status_workspace),
                                                  reinterpret_cast<const long long*>(n_rows_dev));
@@ -908,6 +1000,12 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
     if (a->d_bias && !op->bias) return CCE_ERR_ARG;
     if (a->has_filter && !(a->filter_eps >= 0.0f)) return CCE_ERR_ARG;
     if (reinterpret_cast<uintptr_t>(workspace) & 255) return CCE_ERR_ALIGN;
+    const int peer_world = a->de_peer_world > 1 ? a->de_peer_world : 0;  // dE added into the ranks' accumulators
+    if (peer_world) {
+        if (peer_world > kMaxPeers || !a->d_e) return CCE_ERR_ARG;
+        for (int r = 0; r < peer_world; ++r)
+            if (!a->de_peer_acc[r] || (reinterpret_cast<uintptr_t>(a->de_peer_acc[r]) & 15)) return CCE_ERR_ARG;
+    }
     const BwdPlan pl = plan_bwd(a);
     if (workspace_bytes < pl.total) return CCE_ERR_WORKSPACE;
     DeviceInfo* dev = nullptr;
@@ -999,15 +1097,18 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
     // The two products.  With split fp32 operands the staged rows hold three column blocks
     // ([hi|hi|lo] for e, [hi|lo|hi] for c): dC = G^T e_hi + G^T e_lo and dE = G c_hi + G c_lo, i.e. the
     // same launch run twice on different column blocks of the B operand, the second adding in fp32.
+    // SMs the dC product may use: all of them, except after dE has been handed to the caller's
+    // exchange (finish_de), which needs SMs of its own to run beside the product
+    int sms_dc = dev->sms;
     auto run_dc = [&](EngineParams p, const CUtensorMap& tmA) -> int {
         p.b_tma3 = e_is3;
         const bool pair = pair_ok(p, e_is3);
         const CUtensorMap& tmB = pair ? tmE_mn_h : tmE_mn;
-        int r = launch_engine<MODE_GEMM>(tmA, tmB, p, dev->sms, st, pair);
+        int r = launch_engine<MODE_GEMM>(tmA, tmB, p, sms_dc, st, pair);
         if (r != CCE_OK || !split) return r;
         p.b_mn_off = int(2 * sg.blk);
         p.accumulate = 2;
-        return launch_engine<MODE_GEMM>(tmA, tmB, p, dev->sms, st, pair);
+        return launch_engine<MODE_GEMM>(tmA, tmB, p, sms_dc, st, pair);
     };
     auto run_de = [&](EngineParams p, const CUtensorMap& tmA) -> int {
         p.b_tma3 = c_is3;
@@ -1046,11 +1147,23 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
     // The last step of dE: fp32 scratch -> the caller's rows.  Run once, either at the end or, when the
     // caller asked to be told (de_ready_event), right after the last dE product and before the last dC
     // product, so that a cross-rank reduction of dE can overlap that product.
-    const bool early_de = a->d_e && a->de_ready_event != nullptr;
+    const bool early_de = a->d_e && (a->de_ready_event != nullptr || peer_world);
     bool de_finished = false;
+    auto set_peers = [&](EngineParams& p) {  // the dE product adds into the owners' accumulators
+        if (!peer_world) return;
+        p.peer_world = peer_world;
+        for (int r = 0; r < peer_world; ++r) p.peer_out[r] = a->de_peer_acc[r];
+        p.accumulate = 2;
+    };
     auto finish_de = [&]() -> int {
         if (de_finished || !a->d_e) return CCE_OK;
         de_finished = true;
+        if (a->de_ready_event && a->exchange_sms > 0)
+            sms_dc = std::max(dev->sms / 2, dev->sms - a->exchange_sms) & ~1;  // even: CTA pairs
+        if (peer_world) {  // the sums sit in the ranks' accumulators: the caller collects them
+            if (a->de_ready_event) CCE_CUDA(cudaEventRecord(reinterpret_cast<cudaEvent_t>(a->de_ready_event), st));
+            return CCE_OK;
+        }
         if (a->d_e_f32 || split)
             scatter_cast_kernel<float><<<(unsigned)B, 128, 0, st>>>(
                 de32, D, op->valids, op->valids_dtype == CCE_IDX_I64, reinterpret_cast<float*>(a->d_e), D, D, B, status, ndev);
@@ -1170,6 +1283,7 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
                 p.klist = de_list;
                 p.kcount = de_cnt;
                 p.m_dev = ndev;
+                set_peers(p);
                 return run_de(p, tmP_k);
             };
             // in the last pass dE goes first when the caller wants to start reducing it early
@@ -1248,6 +1362,7 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
                     p.kflags = flag_e;
                     p.ld_kflags = pl.ld_flag_e;
                 }
+                set_peers(p);
                 return run_de(p, tmG_k);
             };
             const bool de_first = early_de && ch == pl.n_chunk - 1;

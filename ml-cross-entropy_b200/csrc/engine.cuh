@@ -27,6 +27,11 @@ constexpr int ATOM_BYTES = 64 * 128;  // one MN-major swizzle atom column: 64 K 
 constexpr int ENGINE_THREADS = 192;
 constexpr int TMEM_COLS = 512;
 constexpr int ENGINE_SMEM = NSTAGE * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+// Staging for the epilogue's bulk adds into peer memory (EngineParams::peer_world): one row of 32
+// fp32 values per epilogue thread; the 144-byte pitch keeps the 16-byte stores of neighbouring
+// threads in different banks.  Requested only by launches that add into peers.
+constexpr int PEER_ROW_PITCH = 144;
+constexpr int PEER_STAGE_BYTES = 4 * 32 * PEER_ROW_PITCH;
 
 enum { MODE_LSE = 0, MODE_PGRAD = 1, MODE_GEMM = 2 };
 
@@ -37,6 +42,8 @@ enum { MODE_LSE = 0, MODE_PGRAD = 1, MODE_GEMM = 2 };
 #endif
 constexpr bool kTrace = CCE_TRACE != 0;
 
+
+constexpr int kMaxPeers = 8;  // ranks whose memory one launch can add into
 
 struct EngineParams {
     // extents of this launch
@@ -129,6 +136,13 @@ struct EngineParams {
     int accumulate;  // fp32 out only: 0 store, 1 read-add-store, 2 vector red.add (out pre-zeroed)
     const uint8_t* kflags;  // null or [n_mblk][ld_kflags]
     int ld_kflags;
+    // Cross-rank sum fused into the store (dE under vocabulary parallelism): with peer_world > 0 the
+    // tile of row block m is added (red.add, fp32) into the accumulator of rank m % peer_world, a
+    // buffer of that rank's memory mapped into this process, at rows (m / peer_world) * 128 + r with
+    // row pitch ldo.  Every rank runs the same row blocks, so each accumulator ends up with the sum
+    // over ranks of the row blocks it owns.  `out` is not written.
+    int peer_world;
+    float* peer_out[kMaxPeers];
 };
 
 // Order-preserving map from float to int32 (and back): a < b  <=>  key(a) < key(b).
@@ -153,6 +167,7 @@ struct EngineSmem {
     uint32_t* tmem_base;
     int* abort_flag;
     int* acc_empty;  // [2] accumulator holds no product (all K blocks skipped)
+    uint8_t* peer_stage;  // null, or PEER_STAGE_BYTES behind the barriers
 };
 
 struct PassInfo {
@@ -598,12 +613,24 @@ __device__ __forceinline__ void store_g16(void* dst, const float (&v)[32], bool 
 
 // One row's 32 consecutive columns of a product tile (fp32 accumulator bits in r) to the output:
 // store, read-add-store (accumulate == 1) or red.add (accumulate == 2); fp32 or 16-bit output.
-__device__ __forceinline__ void gemm_store_chunk(const EngineParams& p, int row, int col0, const uint32_t (&r)[32]) {
+// `peer` (null, or another rank's accumulator): the values are added there with red.add instead.
+__device__ __forceinline__ void gemm_store_chunk(const EngineParams& p, int row, int col0, const uint32_t (&r)[32],
+                                                 float* peer = nullptr) {
     float x[32];
 #pragma unroll
     for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(r[j]);
     const int ncol = min(32, p.N - col0);
-    if (p.out_dtype == 2) {
+    if (peer) {
+        float* dst = peer + (size_t)row * p.ldo + col0;
+        if ((ncol == 32) && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) red_add_v4(dst + 4 * j, x[4 * j], x[4 * j + 1], x[4 * j + 2], x[4 * j + 3]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (j < ncol) atomicAdd(dst + j, x[j]);
+        }
+    } else if (p.out_dtype == 2) {
         float* dst = reinterpret_cast<float*>(p.out) + (size_t)row * p.ldo + col0;
         const bool vec = (ncol == 32) && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
         if (vec && p.accumulate == 2) {
@@ -700,7 +727,10 @@ __device__ void epilogue_loop(const EngineParams& p, const EngineSmem& s, uint32
                            ERR_WAIT_TMEM_FULL);
         if (kTrace && p.wait_cycles) waited_epi += clock64() - t0w;
         ok = __all_sync(0xffffffffu, ok);
-        if (!ok) return;
+        if (!ok) {
+            if (MODE == MODE_GEMM && p.peer_world > 0) bulk_wait_all();
+            return;
+        }
         tc_fence_after();
         const bool acc_is_empty =  // every K block skipped, or a reduction of length zero
             (MODE == MODE_GEMM) ? (reinterpret_cast<volatile int*>(s.acc_empty)[acc] != 0 || dyn.n_kblk == 0) : false;
@@ -712,6 +742,36 @@ __device__ void epilogue_loop(const EngineParams& p, const EngineSmem& s, uint32
         } else if constexpr (MODE == MODE_GEMM) {
             // Store-only epilogue: two 32-column loads from TMEM are in flight per wait, so half of
             // the load latency is exposed compared with one load per wait.
+            if (p.peer_world > 0) {
+                // The tile goes to the accumulator of the rank that owns this row block: every thread
+                // stages 32 values of its row in shared memory and hands them to the copy engine as
+                // one 128-byte bulk add.
+                float* peer = p.peer_out[it.mblk % p.peer_world];
+                const int orow = (it.mblk / p.peer_world) * BM + q * 32 + lane;
+                const uint32_t stg = smem_u32(s.peer_stage) + uint32_t((q * 32 + lane) * PEER_ROW_PITCH);
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; ++c) {
+                    const int col0 = it.nblk * BN + c * 32;
+                    if (col0 >= p.N) break;  // warp-uniform
+                    uint32_t r0[32];
+                    tmem_ld32(taddr + c * 32, r0);
+                    bulk_wait_read_all();  // the previous request has read the staging row
+                    tmem_ld_wait();
+                    if (row_ok) {
+                        float* dst = peer + (size_t)orow * p.ldo + col0;
+                        if (col0 + 32 <= p.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                st_shared_v4(stg + 16 * j, r0[4 * j], r0[4 * j + 1], r0[4 * j + 2], r0[4 * j + 3]);
+                            fence_proxy_async();
+                            bulk_reduce_add_f32(dst, stg, 128);
+                            bulk_commit();
+                        } else {
+                            gemm_store_chunk(p, orow, col0, r0, peer);
+                        }
+                    }
+                }
+            } else {
             const int orow = (row_ok && p.row_map) ? p.row_map[row] : row;
 #pragma unroll 1
             for (int c = 0; c < BN / 32; c += 2) {
@@ -730,6 +790,7 @@ __device__ void epilogue_loop(const EngineParams& p, const EngineSmem& s, uint32
                     gemm_store_chunk(p, orow, col0, r0);
                     if (col0 + 32 < p.N) gemm_store_chunk(p, orow, col0 + 32, r1);
                 }
+            }
             }
         } else {
             uint32_t flag_bits = 0;  // MODE_PGRAD: activity of the current 64-column group
@@ -875,6 +936,8 @@ __device__ void epilogue_loop(const EngineParams& p, const EngineSmem& s, uint32
             if (it.last && row_ok) p.partial[(size_t)it.band * p.M + row] = make_float2(run_m, run_s);
         }
     }
+    // bulk adds still in flight read this CTA's shared memory: they finish before the thread leaves
+    if (MODE == MODE_GEMM && p.peer_world > 0) bulk_wait_all();
     if (kTrace && p.wait_cycles && lane == 0) atomicAdd(p.wait_cycles + 3, (unsigned long long)(waited_epi / 4));
 }
 
@@ -895,6 +958,7 @@ engine_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
     s.tmem_base = reinterpret_cast<uint32_t*>(bars + 2 * NSTAGE + 5);
     s.abort_flag = reinterpret_cast<int*>(s.tmem_base + 1);
     s.acc_empty = s.abort_flag + 1;
+    s.peer_stage = p.peer_world > 0 ? base + NSTAGE * STAGE_BYTES + 256 : nullptr;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;

@@ -256,6 +256,7 @@ pair_engine_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     s.tmem_base = reinterpret_cast<uint32_t*>(bars + 2 * P_NST + 5);
     s.abort_flag = reinterpret_cast<int*>(s.tmem_base + 1);
     s.acc_empty = s.abort_flag + 1;
+    s.peer_stage = p.peer_world > 0 ? base + P_NST * P_STAGE_BYTES + 256 : nullptr;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();

@@ -185,6 +185,23 @@ __device__ __forceinline__ void st_global_v8(void* addr, const uint32_t* v) {
                  : "memory");
 }
 
+// Bulk add of `bytes` (a multiple of 16) fp32 values from this CTA's shared memory into global memory
+// (which may be another GPU's): one asynchronous request of the copy engine instead of one atomic
+// per 16 bytes.  Both addresses 16-byte aligned.  The issuing thread orders its own shared-memory
+// writes before the request with fence_proxy_async().
+__device__ __forceinline__ void bulk_reduce_add_f32(void* gdst, uint32_t smem_src, uint32_t bytes) {
+    asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(gdst),
+                 "r"(smem_src), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// this thread's bulk requests have read their shared-memory source / have completed
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
 // ------------------------------------------------------------- descriptors
 // Shared-memory matrix descriptor, 128-byte swizzle (layout type 2), version 1.
 // lbo/sbo are byte offsets (multiples of 16).

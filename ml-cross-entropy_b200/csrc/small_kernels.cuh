@@ -1,6 +1,7 @@
 // Bandwidth-bound helper kernels around the tensor-core pipeline: row gather/pad,
 // correct-token gather-dot, log-sum-exp merge, column sums and the final cast/scatter.
 #pragma once
+#include <cooperative_groups.h>
 #include "engine.cuh"
 
 namespace cce {
@@ -613,6 +614,50 @@ __global__ void scatter_cast_kernel(const float* __restrict__ src, long long ld_
     }
 }
 
+// dE summed across ranks by the product kernels themselves (EngineParams::peer_world): this rank's
+// accumulator `acc` [acc_rows][D] fp32 holds the finished sums of the row blocks it owns.  Writes
+// them to `slice` in the output type and clears the accumulator for the next step.  A non-zero
+// status word (one of this rank's kernels abandoned a wait, so its contributions are missing
+// everywhere) turns the slice into NaN, which the exchange that follows carries to every rank.
+template <typename T>
+__global__ void peer_collect_kernel(float* __restrict__ acc, long long n, T* __restrict__ slice,
+                                    const int* __restrict__ status) {
+    const bool bad = status && *status != 0;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n / 4; i += stride) {
+        float4 v = reinterpret_cast<float4*>(acc)[i];
+        reinterpret_cast<float4*>(acc)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (bad) v.x = v.y = v.z = v.w = __int_as_float(0x7fc00000);
+        if constexpr (sizeof(T) == 4) {
+            reinterpret_cast<float4*>(slice)[i] = v;
+        } else {
+            T o[4] = {T(v.x), T(v.y), T(v.z), T(v.w)};
+            reinterpret_cast<uint2*>(slice)[i] = *reinterpret_cast<const uint2*>(o);
+        }
+    }
+}
+
+// The gathered slices [world][acc_rows][D] back to the caller's rows: packed row i belongs to row
+// block m = i / 128, owned by rank m % world at rows (m / world) * 128 + i % 128 of its slice.
+template <typename T>
+__global__ void peer_scatter_kernel(const T* __restrict__ gathered, int world, long long acc_rows, long long D,
+                                    const void* __restrict__ rows, int rows_i64, T* __restrict__ dst,
+                                    long long n_rows, const long long* __restrict__ n_dev) {
+    const long long i = blockIdx.x;
+    if (i >= actual_rows(n_rows, n_dev)) return;
+    const long long r = rows ? load_index(rows, rows_i64, i) : i;
+    const long long m = i / 128;
+    const T* s = gathered + ((m % world) * acc_rows + (m / world) * 128 + (i % 128)) * D;
+    T* d = dst + r * D;
+    constexpr int VEC = 16 / sizeof(T);
+    if (D % VEC == 0 && ((reinterpret_cast<uintptr_t>(s) | reinterpret_cast<uintptr_t>(d)) & 15) == 0) {
+        for (long long j = threadIdx.x; j < D / VEC; j += blockDim.x)
+            reinterpret_cast<uint4*>(d)[j] = reinterpret_cast<const uint4*>(s)[j];
+    } else {
+        for (long long j = threadIdx.x; j < D; j += blockDim.x) d[j] = s[j];
+    }
+}
+
 // Tail of the forward pass in one block: merges the per-rank statistics, forms the negative
 // log-likelihood of every row and reduces or scatters it.
 //   stats[r][0][i] = log-sum-exp of row i over rank r's vocabulary shard, stats[r][1][i] = minus the
@@ -623,16 +668,18 @@ __global__ void scatter_cast_kernel(const float* __restrict__ src, long long ld_
 //   lse_rows (optional) [n_rows] receives lse_i; lse_scatter (optional) receives lse_i at pos_i.
 // Positions that no row maps to are cleared by the caller before the launch.
 constexpr int TAIL_THREADS = 1024;
-__global__ void __launch_bounds__(TAIL_THREADS)
+constexpr int TAIL_CTAS = 8;  // one cluster; rows are dealt to its CTAs 1024 at a time
+__global__ void __cluster_dims__(TAIL_CTAS, 1, 1) __launch_bounds__(TAIL_THREADS)
 loss_tail_kernel(const float* __restrict__ stats, int world, long long n_rows, const void* __restrict__ rows,
                  int rows_i64, long long shift, int reduction, float* __restrict__ lse_rows,
                  float* __restrict__ loss_out, float* __restrict__ lse_scatter, const int* __restrict__ status,
                  const long long* __restrict__ n_dev) {
     __shared__ double warp_sum[TAIL_THREADS / 32];
+    __shared__ double cta_sum;
     const bool bad = status && *status != 0;
     double acc = 0.0;
     const long long n_act = actual_rows(n_rows, n_dev);  // `stats` keeps the pitch n_rows
-    for (long long i = threadIdx.x; i < n_act; i += TAIL_THREADS) {
+    for (long long i = (long long)blockIdx.x * TAIL_THREADS + threadIdx.x; i < n_act; i += TAIL_CTAS * TAIL_THREADS) {
         float m = -INFINITY, neg = 0.0f;
         for (int r = 0; r < world; ++r) {
             m = fmaxf(m, stats[(size_t)r * 2 * n_rows + i]);
@@ -652,7 +699,8 @@ loss_tail_kernel(const float* __restrict__ stats, int world, long long n_rows, c
         if (reduction == 2) loss_out[pos] = nll;
         acc += (double)nll;
     }
-    if (reduction == 2) return;
+    if (reduction == 2) return;  // uniform over the cluster
+    // fixed summation order (lanes, warps, CTAs): the same inputs always give the same bits
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
     if ((threadIdx.x & 31) == 0) warp_sum[threadIdx.x >> 5] = acc;
@@ -660,8 +708,16 @@ loss_tail_kernel(const float* __restrict__ stats, int world, long long n_rows, c
     if (threadIdx.x == 0) {
         double t = 0.0;
         for (int w = 0; w < TAIL_THREADS / 32; ++w) t += warp_sum[w];
+        cta_sum = t;
+    }
+    cooperative_groups::cluster_group cluster = cooperative_groups::this_cluster();
+    cluster.sync();
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        double t = 0.0;
+        for (int r = 0; r < TAIL_CTAS; ++r) t += *cluster.map_shared_rank(&cta_sum, r);
         loss_out[0] = float(reduction == 0 ? t / double(n_act) : t);
     }
+    cluster.sync();  // no CTA leaves while its sum may still be read
 }
 
 // One warp waits on an mbarrier at which nobody ever arrives, with a caller-chosen cycle limit: the

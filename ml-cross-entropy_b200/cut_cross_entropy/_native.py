@@ -18,6 +18,8 @@ LIB_PATH = Path(__file__).resolve().parent / "libcce_b200.so"
 
 DT_F16, DT_BF16, DT_F32 = 0, 1, 2
 IDX_I32, IDX_I64 = 0, 1
+MAX_PEERS = 8  # CCE_B200_MAX_PEERS
+PEER_HANDLE_BYTES = 64  # CCE_B200_PEER_HANDLE_BYTES
 
 _DTYPE_CODE = {torch.float16: DT_F16, torch.bfloat16: DT_BF16, torch.float32: DT_F32}
 
@@ -36,6 +38,13 @@ EXPORTS = (
     "cce_b200_valid_rows",
     "cce_b200_backward_workspace_bytes",
     "cce_b200_backward",
+    "cce_b200_peer_buffer_create",
+    "cce_b200_peer_buffer_open",
+    "cce_b200_peer_buffer_close",
+    "cce_b200_peer_buffer_destroy",
+    "cce_b200_de_peer_rows",
+    "cce_b200_de_peer_collect",
+    "cce_b200_de_peer_scatter",
     "cce_b200_gemm",
     "cce_b200_read_status",
     "cce_b200_lse_forward_static_status",
@@ -99,6 +108,9 @@ class BackwardArgs(Structure):
         ("e_packed", c_void_p),
         ("e_packed_ld", c_int64),
         ("de_ready_event", c_void_p),
+        ("de_peer_world", c_int32),
+        ("exchange_sms", c_int32),
+        ("de_peer_acc", c_void_p * MAX_PEERS),
     ]
 
 
@@ -162,6 +174,22 @@ def lib() -> ctypes.CDLL:
     L.cce_b200_backward_workspace_bytes.argtypes = [POINTER(BackwardArgs)]
     L.cce_b200_backward.restype = c_int32
     L.cce_b200_backward.argtypes = [POINTER(BackwardArgs), c_void_p, c_size_t, c_void_p]
+    L.cce_b200_peer_buffer_create.restype = c_int32
+    L.cce_b200_peer_buffer_create.argtypes = [c_size_t, POINTER(c_void_p), c_void_p]
+    L.cce_b200_peer_buffer_open.restype = c_int32
+    L.cce_b200_peer_buffer_open.argtypes = [c_void_p, POINTER(c_void_p)]
+    L.cce_b200_peer_buffer_close.restype = c_int32
+    L.cce_b200_peer_buffer_close.argtypes = [c_void_p]
+    L.cce_b200_peer_buffer_destroy.restype = c_int32
+    L.cce_b200_peer_buffer_destroy.argtypes = [c_void_p]
+    L.cce_b200_de_peer_rows.restype = c_int64
+    L.cce_b200_de_peer_rows.argtypes = [c_int64, c_int32]
+    L.cce_b200_de_peer_collect.restype = c_int32
+    L.cce_b200_de_peer_collect.argtypes = [c_void_p, c_int64, c_int64, c_void_p, c_int32, c_void_p, c_void_p]
+    L.cce_b200_de_peer_scatter.restype = c_int32
+    L.cce_b200_de_peer_scatter.argtypes = [
+        c_void_p, c_int32, c_int64, c_int64, c_int32, c_void_p, c_int32, c_int64, c_void_p, c_void_p, c_void_p,
+    ]  # fmt: skip
     L.cce_b200_gemm.restype = c_int32
     L.cce_b200_gemm.argtypes = [
         c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,

@@ -9,10 +9,13 @@ tensor-core products (dC = G^T E, dE += G C) that skip blocks the filter cleared
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import _native
 from .utils import TensorInfo
+from .vocab_parallel.peer_reduce import finish_peer_reduce, peer_accumulators
 from .vocab_parallel.utils import vp_reduce_e_grad_, vp_reduce_e_grad_cast
 
 
@@ -27,10 +30,22 @@ def _reduce_stream(dev: torch.device) -> "torch.cuda.Stream":
     return _REDUCE_STREAMS[key]
 
 
+def _exchange_sms() -> int:
+    """SMs the last dC product leaves to the collective kernels that exchange dE beside it
+    (``CCE_B200_EXCHANGE_SMS``, default 32).  The product is a persistent kernel with one CTA per SM:
+    without free SMs the exchange would only start when the product ends."""
+    try:
+        return max(0, int(os.environ.get("CCE_B200_EXCHANGE_SMS", "32")))
+    except ValueError:
+        return 32
+
+
 def _launch(do, dlse, e, c, bias, lse, valids, softcap, filter_eps, targets, shift, grad_scale,
             filter_e, filter_c, vocab_start, de, dc, dbias, tile_max=None, vocab_ordering=None, col_max=None,
-            n_rows_dev=None, scale_by_inv_rows=False, packed_e=None, de_ready=None) -> None:
-    """Fill the (pre-allocated, possibly ``None``) outputs ``de``/``dc``/``dbias`` through the C ABI."""
+            n_rows_dev=None, scale_by_inv_rows=False, packed_e=None, de_ready=None, peers=None) -> torch.Tensor:
+    """Fill the (pre-allocated, possibly ``None``) outputs ``de``/``dc``/``dbias`` through the C ABI.
+    With ``peers`` (:class:`PeerAccumulators`) the dE products add into the ranks' accumulators
+    instead of writing ``de``.  Returns the call's workspace (its first word is the status word)."""
     dev = e.device
     a = _native.BackwardArgs()
     a.op = _native.make_operands(e, c, bias, valids, softcap, n_rows_dev)
@@ -47,6 +62,11 @@ def _launch(do, dlse, e, c, bias, lse, valids, softcap, filter_eps, targets, shi
         a.e_packed, a.e_packed_ld = packed_e.data_ptr(), packed_e.stride(0)
     if de_ready is not None:
         a.de_ready_event = de_ready.cuda_event
+        a.exchange_sms = _exchange_sms()
+    if peers is not None:
+        a.de_peer_world = peers.world
+        for r, ptr in enumerate(peers.ptrs):
+            a.de_peer_acc[r] = ptr
     a.has_filter = int(filter_eps is not None)
     a.filter_eps = float(filter_eps) if filter_eps is not None else 0.0
     a.filter_e = int(filter_e)
@@ -65,6 +85,7 @@ def _launch(do, dlse, e, c, bias, lse, valids, softcap, filter_eps, targets, shi
         rc = L.cce_b200_backward(a, ws.data_ptr(), ws.numel(), _native.stream_ptr(dev))
     _native.check(rc, "cce_b200_backward")
     _native.finish(ws, "cce_b200_backward")
+    return ws
 
 
 def cce_backward_kernel(
@@ -147,40 +168,58 @@ def cce_backward_kernel(
     want_de = e_info.requires_grad
     want_dc = c_info.requires_grad
     want_dbias = bias is not None and bias_info is not None and bias_info.requires_grad
-    de_f32 = bool(reduce_e_grad and want_de)
+    reduce_de = bool(reduce_e_grad and want_de)
+
+    # The cross-rank sum of dE.  On one NVLink node the dE product adds its tiles straight into the
+    # owning ranks' accumulators (vocab_parallel/peer_reduce.py) and de keeps e's type; otherwise the
+    # partial dE is produced in fp32 and summed by the process group.
+    n_rows_bound = valids.size(0) if valids is not None else e.size(0)
+    peers, acc_rows = None, 0
+    if reduce_de and dev.type == "cuda" and n_rows_bound > 0:
+        acc_rows = int(_native.lib().cce_b200_de_peer_rows(n_rows_bound, torch.distributed.get_world_size(pg)))
+        peers = peer_accumulators(pg, dev, acc_rows * e.size(1) * 4)
+    de_f32 = reduce_de and peers is None
 
     de = torch.empty(e.shape, dtype=torch.float32 if de_f32 else e.dtype, device=dev) if want_de else None
     dc = torch.empty((c.size(0), c.size(1)), dtype=c.dtype, device=dev) if want_dc else None
     dbias = torch.empty((c.size(0),), dtype=torch.float32, device=dev) if want_dbias else None
 
     # With a cross-rank sum of dE to do, the library is asked to finish dE before the last dC product
-    # and to record an event there: the all-reduce then runs on a side stream beside that product.
-    overlap = de_f32 and dev.type == "cuda"
+    # and to record an event there: the exchange then runs on a side stream beside that product.
+    overlap = reduce_de and dev.type == "cuda"
     de_ready = None
     if overlap:
         de_ready = torch.cuda.Event()
         de_ready.record(torch.cuda.current_stream(dev))  # creates the handle; the library records it again
+    ws = None
     if want_de or want_dc or want_dbias:
-        _launch(do, dlse, e, c, bias, lse, valids, softcap, filter_eps, targets, int(shift), float(grad_scale),
-                bool(filter_e_grad), bool(filter_c_grad), int(vocab_start), de, dc, dbias, tile_max,
-                vocab_ordering, col_max, n_rows_dev, bool(scale_by_inv_rows), packed_e, de_ready)
+        ws = _launch(do, dlse, e, c, bias, lse, valids, softcap, filter_eps, targets, int(shift), float(grad_scale),
+                     bool(filter_e_grad), bool(filter_c_grad), int(vocab_start), de, dc, dbias, tile_max,
+                     vocab_ordering, col_max, n_rows_dev, bool(scale_by_inv_rows), packed_e, de_ready, peers)
 
-    if de_f32:
+    if reduce_de:
         assert de is not None
         if overlap:
             main, side = torch.cuda.current_stream(dev), _reduce_stream(dev)
             side.wait_event(de_ready)
             with torch.cuda.stream(side):
-                if e_info.dtype in (torch.float16, torch.bfloat16):
+                if peers is not None:
+                    # barrier, cast of the rows this rank owns, 16-bit all-gather, rows to their places
+                    # (ws and de are used on the side stream without record_stream: the main stream
+                    # waits for the side stream below, before anything can reuse their memory)
+                    assert ws is not None
+                    finish_peer_reduce(peers, pg, de, acc_rows, valids, n_rows_bound, n_rows_dev, ws)
+                elif e_info.dtype in (torch.float16, torch.bfloat16):
                     # fp32 reduce-scatter, cast, 16-bit all-gather: the fp32 sum of the reference with less traffic
                     reduced = vp_reduce_e_grad_cast(de, e_info.dtype, pg)
                     de.record_stream(side)
                     de = reduced
                 else:
                     vp_reduce_e_grad_(de, pg)
-            de.record_stream(main)
-            de.record_stream(side)
-            main.wait_stream(side)  # enqueued after the last dC product, which therefore overlaps the reduction
+            if peers is None:
+                de.record_stream(main)
+                de.record_stream(side)
+            main.wait_stream(side)  # enqueued after the last dC product, which therefore overlaps the exchange
         else:
             vp_reduce_e_grad_(de, pg)
 

@@ -7,6 +7,7 @@ equal the matching slice of the single-GPU dC, and dE (summed over ranks in fp32
 
 from __future__ import annotations
 
+import os
 import sys
 from pathlib import Path
 
@@ -102,6 +103,22 @@ def _worker(rank: int, world: int, init_method: str, impl: str, z_loss: bool, q)
         mx = got[2].float().clone()
         dist.all_reduce(mx, op=dist.ReduceOp.MAX)
         torch.testing.assert_close(mx, got[2].float(), rtol=0, atol=0)
+        # dE was summed by the product kernels through the ranks' mapped accumulators ...
+        from cut_cross_entropy.vocab_parallel import peer_reduce
+
+        states = list(peer_reduce._STATE.values())
+        assert len(states) == 1 and states[0] is not None and states[0].world == world, states
+        # ... and agrees with the sum the process group computes (fp32 sums in a different order, one rounding to bf16)
+        os.environ["CCE_B200_PEER_REDUCE"] = "0"
+        try:
+            by_group = run(vp)
+        finally:
+            os.environ["CCE_B200_PEER_REDUCE"] = "1"
+        scale = by_group[2].float().abs().max().item()
+        assert (got[2].float() - by_group[2].float()).abs().max().item() <= 2.0 ** -7 * scale
+        again = run(vp)  # the accumulators were left clear: a second step gives the same sums
+        assert (again[2].float() - got[2].float()).abs().max().item() <= 2.0 ** -7 * scale
+        peer_reduce.release_peer_accumulators(None)
         q.put((rank, "ok"))
     except Exception as ex:
         import traceback

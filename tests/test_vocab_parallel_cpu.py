@@ -90,7 +90,8 @@ def _install_cpu_stand_ins():
 
     def launch(do, dlse, e, c, bias, lse, valids, softcap, filter_eps, targets, shift, grad_scale,
                filter_e, filter_c, vocab_start, de, dc, dbias, tile_max=None, vocab_ordering=None, col_max=None,
-               n_rows_dev=None, scale_by_inv_rows=False, packed_e=None, de_ready=None):
+               n_rows_dev=None, scale_by_inv_rows=False, packed_e=None, de_ready=None, peers=None):
+        assert peers is None  # accumulators in peer memory exist on GPUs only
         # restates one rank of cce_backward.py:182-310 with the global lse
         n = e.size(0)
         rows = torch.arange(n) if valids is None else valids.long()
