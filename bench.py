@@ -23,8 +23,8 @@ kernel), ``phases_ms`` and ``op_mem_mb`` (forward / backward / both, the method 
 recomputes), ``variants.cce_exact`` (nothing filtered), ``sustained`` (a loop of at least two
 seconds), ``ref_gpu`` (the reference's implementations in the same process), ``peaked`` (a workload
 with a peaked softmax, with and without vocabulary ordering), and for N > 1 ``vp_parity`` (gradient
-parity of the sharded run against an unsharded ``cce_exact`` on the same rank) and
-``vocab_parallel_head`` (the 32768 x 4096 x 262144 configuration sharded over the same ranks).
+parity of the sharded run against an unsharded ``cce_exact`` on the same rank), ``de_exchange`` (how
+dE was summed over the ranks) and ``vocab_parallel_head`` (the 32768 x 4096 x 262144 configuration sharded over the same ranks).
 """
 
 from __future__ import annotations
@@ -744,6 +744,14 @@ def main() -> None:
         except Exception as ex:  # keep the bench line even if the check cannot run
             extras_vp = {"error": f"{type(ex).__name__}: {str(ex)[:200]}"}
         extras["vp_parity"] = extras_vp
+        # which exchange summed dE over the ranks in the timed steps
+        from cut_cross_entropy.vocab_parallel import peer_reduce
+
+        fused = any(st is not None for st in peer_reduce._STATE.values())
+        extras["de_exchange"] = (
+            "fused: the dE product adds its tiles into the owning ranks' mapped accumulators "
+            "(cp.reduce.async.bulk over NVLink); then barrier, cast, 16-bit all-gather" if fused else
+            "process group: fp32 reduce-scatter, cast, 16-bit all-gather")
         e.grad = c.grad = None
         gc.collect()
         torch.cuda.empty_cache()

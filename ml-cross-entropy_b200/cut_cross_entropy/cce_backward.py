@@ -31,13 +31,16 @@ def _reduce_stream(dev: torch.device) -> "torch.cuda.Stream":
 
 
 def _exchange_sms() -> int:
-    """SMs the last dC product leaves to the collective kernels that exchange dE beside it
-    (``CCE_B200_EXCHANGE_SMS``, default 32).  The product is a persistent kernel with one CTA per SM:
-    without free SMs the exchange would only start when the product ends."""
+    """SMs the last dC product leaves to the kernels that exchange dE beside it
+    (``CCE_B200_EXCHANGE_SMS``, default 0).  The product is a persistent kernel with one CTA per SM,
+    so with 0 the exchange starts when the product ends.  Measured on 8 GPUs at the Gemma-2-2B
+    head (1.36 ms per step with 0): 16 and 32 free SMs cost as much in the product as they gain in
+    overlap (1.38, 1.37 ms), 48 gain 1.5 % (1.34 ms): CTAs of the product that find their SM taken
+    start late and, with tiles dealt out in a fixed order, finish late."""
     try:
-        return max(0, int(os.environ.get("CCE_B200_EXCHANGE_SMS", "32")))
+        return max(0, int(os.environ.get("CCE_B200_EXCHANGE_SMS", "0")))
     except ValueError:
-        return 32
+        return 0
 
 
 def _launch(do, dlse, e, c, bias, lse, valids, softcap, filter_eps, targets, shift, grad_scale,
