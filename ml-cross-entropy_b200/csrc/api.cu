@@ -77,6 +77,15 @@ EncodeTiledFn get_encode() {
 }
 
 // The dense launches run on CTA pairs (engine_pair.cuh) unless CCE_B200_PAIR=0; read once.
+// CCE_B200_TILE_QUEUE=0: block-list products take every gridDim.x-th tile instead of drawing from a counter
+bool tile_queue_enabled() {
+    static const bool on = [] {
+        const char* e = getenv("CCE_B200_TILE_QUEUE");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
+
 bool pair_enabled() {
     static const bool on = [] {
         const char* env = getenv("CCE_B200_PAIR");
@@ -474,7 +483,7 @@ struct BwdPlan {
     long long Dkp;  // row length (elements) of the reordered classifier copy
     size_t off_cperm, off_bias_perm, off_inv_order, off_tile_colmax;
     // both
-    size_t off_g, off_de32, total;
+    size_t off_g, off_de32, off_tile_ctr, total;
 };
 
 bool wants_sparse(const cce_b200_backward_args* a) {
@@ -518,6 +527,8 @@ BwdPlan plan_bwd(const cce_b200_backward_args* a) {
         pl.off_row_slots = off;
         off = align_up(off + (size_t)total_tiles * 4, 256);
         pl.off_pass = off;
+        off = align_up(off + (size_t)pl.max_pass * 4 * sizeof(int), 256);
+        pl.off_tile_ctr = off;  // [max_pass][4] tile counters of the product launches; cleared together with the flags
         off = align_up(off + (size_t)pl.max_pass * 4 * sizeof(int), 256);
         pl.off_sflags = off;  // [capacity][4] for dE, then [capacity][4] for dC
         off = align_up(off + (size_t)pl.capacity * 8, 256);
@@ -1108,6 +1119,7 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
         if (r != CCE_OK || !split) return r;
         p.b_mn_off = int(2 * sg.blk);
         p.accumulate = 2;
+        if (p.tile_counter) ++p.tile_counter;
         return launch_engine<MODE_GEMM>(tmA, tmB, p, sms_dc, st, pair);
     };
     auto run_de = [&](EngineParams p, const CUtensorMap& tmA) -> int {
@@ -1118,6 +1130,7 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
         if (r != CCE_OK || !split) return r;
         p.b_mn_off = int(sg.blk);
         p.accumulate = 2;
+        if (p.tile_counter) ++p.tile_counter;
         return launch_engine<MODE_GEMM>(tmA, tmB, p, dev->sms, st, pair);
     };
 
@@ -1230,7 +1243,9 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
         rc = make_tmap_mn(&tmP_mn, g_buf, cdt, BN, (long long)pl.capacity * BM, BN, BM / 64, tma3_enabled(), &p_is3);
         if (rc != CCE_OK) return rc;
 
-        CCE_CUDA(cudaMemsetAsync(sflag_e, 0, (size_t)pl.capacity * 8, st));  // later passes: cleared by their reader
+        // slot flags (later passes: cleared by their reader) and, in front of them, the tile counters
+        int* tile_ctr = tile_queue_enabled() ? reinterpret_cast<int*>(ws + pl.off_tile_ctr) : nullptr;
+        CCE_CUDA(cudaMemsetAsync(ws + pl.off_tile_ctr, 0, (pl.off_sflags - pl.off_tile_ctr) + (size_t)pl.capacity * 8, st));
         for (int ps = 0; ps < pl.max_pass; ++ps) {
             const int* pinfo = pass_info + 4 * ps;
             {
@@ -1265,6 +1280,7 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
                 p.kcount = dc_cnt;
                 p.a_tma3 = p_is3;
                 p.row_map = inv_order ? a->vocab_order : nullptr;
+                if (tile_ctr) p.tile_counter = tile_ctr + 4 * ps;
                 return run_dc(p, tmP_mn);
             };
             auto pass_de = [&]() -> int {  // dE[rb] += sum over the slots of row rb (in this pass) of G C
@@ -1284,6 +1300,7 @@ int cce_b200_backward(const cce_b200_backward_args* a, void* workspace, size_t w
                 p.kcount = de_cnt;
                 p.m_dev = ndev;
                 set_peers(p);
+                if (tile_ctr) p.tile_counter = tile_ctr + 4 * ps + 2;
                 return run_de(p, tmP_k);
             };
             // in the last pass dE goes first when the caller wants to start reducing it early

@@ -136,6 +136,10 @@ struct EngineParams {
     int accumulate;  // fp32 out only: 0 store, 1 read-add-store, 2 vector red.add (out pre-zeroed)
     const uint8_t* kflags;  // null or [n_mblk][ld_kflags]
     int ld_kflags;
+    // Null, or a zeroed counter of this launch (block-list MODE_GEMM launches): the CTAs draw their
+    // tiles from it instead of taking every gridDim.x-th one, so that a CTA that starts late or
+    // meets long reductions does not hold the launch up (see TileIter).
+    int* tile_counter;
     // Cross-rank sum fused into the store (dE under vocabulary parallelism): with peer_world > 0 the
     // tile of row block m is added (red.add, fp32) into the accumulator of rank m % peer_world, a
     // buffer of that rank's memory mapped into this process, at rows (m / peer_world) * 128 + r with
@@ -168,7 +172,15 @@ struct EngineSmem {
     int* abort_flag;
     int* acc_empty;  // [2] accumulator holds no product (all K blocks skipped)
     uint8_t* peer_stage;  // null, or PEER_STAGE_BYTES behind the barriers
+    // tile queue of a launch with EngineParams::tile_counter: the producer thread draws a tile
+    // number and publishes it to the MMA thread and the epilogue warps
+    uint64_t* qfull;   // [TILE_QUEUE] producer -> consumers
+    uint64_t* qempty;  // [TILE_QUEUE] consumers (MMA thread + 4 epilogue warps) -> producer
+    int* qitem;        // [TILE_QUEUE]
 };
+constexpr int TILE_QUEUE = 4;
+constexpr int kNoTile = 0x7fffffff;
+enum { ROLE_PRODUCER = 0, ROLE_MMA = 1, ROLE_EPILOGUE = 2 };
 
 struct PassInfo {
     int vt_lo, vt_hi, slot_lo, slot_hi;
@@ -210,6 +222,43 @@ struct TileIter {
     int item, n_items, sub, sub_end;
     int mblk, nblk, band, slot;
     bool first, last;
+    // tile queue (launches with p.tile_counter): set by attach()
+    const EngineSmem* sm = nullptr;
+    int role = 0, qslot = 0;
+    uint32_t qphase = 0;
+    __device__ void attach(const EngineSmem* s_, int role_) {
+        sm = s_;
+        role = role_;
+    }
+    // Next tile number of this CTA from the queue (kNoTile: none left, or a wait was abandoned).
+    // The producer thread draws it from the launch's counter and publishes it; the MMA thread and
+    // every epilogue thread read it and hand the queue slot back (one arrival per epilogue warp).
+    __device__ int fetch() {
+        int v;
+        if (role == ROLE_PRODUCER) {
+            if (!mbar_wait(smem_u32(&sm->qempty[qslot]), qphase ^ 1u, sm->abort_flag, p.status, ERR_WAIT_TILE_QUEUE))
+                return kNoTile;
+            v = atomicAdd(p.tile_counter, 1);
+            if (v >= n_items) v = kNoTile;
+            *reinterpret_cast<volatile int*>(&sm->qitem[qslot]) = v;
+            mbar_arrive(smem_u32(&sm->qfull[qslot]));
+        } else {
+            if (!mbar_wait(smem_u32(&sm->qfull[qslot]), qphase, sm->abort_flag, p.status, ERR_WAIT_TILE_QUEUE))
+                return kNoTile;
+            v = *reinterpret_cast<volatile int*>(&sm->qitem[qslot]);
+            if (role == ROLE_EPILOGUE) {
+                __syncwarp();
+                if ((threadIdx.x & 31) == 0) mbar_arrive(smem_u32(&sm->qempty[qslot]));
+            } else {
+                mbar_arrive(smem_u32(&sm->qempty[qslot]));
+            }
+        }
+        if (++qslot == TILE_QUEUE) {
+            qslot = 0;
+            qphase ^= 1u;
+        }
+        return v;
+    }
     __device__ TileIter(const EngineParams& p_, const PassInfo& pass_, const Dyn& dyn)
         : p(p_), pass(pass_), n_mblk(dyn.n_mblk) {
         item = int(blockIdx.x) - int(gridDim.x);
@@ -246,7 +295,10 @@ struct TileIter {
             last = (sub + 1 == sub_end);
             return true;
         } else {
-            item += gridDim.x;
+            if (MODE == MODE_GEMM && p.tile_counter)
+                item = fetch();
+            else
+                item += gridDim.x;
             if (item >= n_items) return false;
             if (MODE == MODE_PGRAD) {
                 if (p.sparse) {
@@ -401,6 +453,7 @@ __device__ void producer_loop(const CUtensorMap* tmA, const CUtensorMap* tmB, co
     const PassInfo pass = load_pass(p);
     const Dyn dyn = load_dyn(p);
     TileIter<MODE> it(p, pass, dyn);
+    it.attach(&s, ROLE_PRODUCER);
     const bool plain = (MODE != MODE_GEMM) || (!p.sparse && !p.kflags);  // every K block of every tile
     if (plain) {
         // One lane runs the whole loop: no ballots or shuffles on the per-K-block path.
@@ -468,6 +521,7 @@ __device__ void mma_loop(const EngineParams& p, const EngineSmem& s, uint32_t tm
     const PassInfo pass = load_pass(p);
     const Dyn dyn = load_dyn(p);
     TileIter<MODE> it(p, pass, dyn);
+    it.attach(&s, ROLE_MMA);
     const bool plain = (MODE != MODE_GEMM) || (!p.sparse && !p.kflags);  // every K block of every tile
     if (plain && dyn.n_kblk > 0) {
         if (lane == 0) {
@@ -959,6 +1013,9 @@ engine_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
     s.abort_flag = reinterpret_cast<int*>(s.tmem_base + 1);
     s.acc_empty = s.abort_flag + 1;
     s.peer_stage = p.peer_world > 0 ? base + NSTAGE * STAGE_BYTES + 256 : nullptr;
+    s.qfull = reinterpret_cast<uint64_t*>(base + NSTAGE * STAGE_BYTES + 128);
+    s.qempty = s.qfull + TILE_QUEUE;
+    s.qitem = reinterpret_cast<int*>(s.qempty + TILE_QUEUE);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -985,6 +1042,10 @@ engine_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
             mbar_init(smem_u32(&s.tempty[i]), 4);  // one arrival per epilogue warp
         }
         mbar_init(smem_u32(s.tdown), 1);
+        for (int i = 0; i < TILE_QUEUE; ++i) {
+            mbar_init(smem_u32(&s.qfull[i]), 1);
+            mbar_init(smem_u32(&s.qempty[i]), 5);  // the MMA thread and one arrival per epilogue warp
+        }
         *s.abort_flag = 0;
         s.acc_empty[0] = 0;
         s.acc_empty[1] = 0;
@@ -1010,6 +1071,7 @@ engine_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
         const PassInfo pass = load_pass(p);
         const Dyn dyn = load_dyn(p);
         TileIter<MODE> it(p, pass, dyn);
+        it.attach(&s, ROLE_EPILOGUE);
         const uint32_t tempty_bar[2] = {smem_u32(&s.tempty[0]), smem_u32(&s.tempty[1])};  // this CTA's own
         epilogue_loop<MODE>(p, s, tmem_base, it, dyn, tempty_bar);
     }

@@ -60,6 +60,7 @@ enum : int {
     ERR_WAIT_TMEM_EMPTY = 3,
     ERR_WAIT_TMEM_FULL = 4,
     ERR_WAIT_TEARDOWN = 5,
+    ERR_WAIT_TILE_QUEUE = 6,
 };
 
 // ~2 s at 2 GHz; far above any legitimate wait in these kernels.
