@@ -281,6 +281,13 @@ int64_t cce_b200_de_peer_rows(int64_t n_rows, int32_t world);
  * into NaN when a kernel of this rank abandoned a wait), or NULL. */
 int cce_b200_de_peer_collect(float* acc, int64_t acc_rows, int64_t D, void* slice_out, int32_t dtype,
                              const void* status_workspace, void* stream);
+/* cce_b200_de_peer_collect with the exchange built in: writes this rank's sums, in `dtype`, to slot
+ * `rank` of every rank's gather buffer gather[r] = [world][acc_rows][D] (buffers from
+ * cce_b200_peer_buffer_create / _open, 16-byte aligned; gather[rank] is this rank's own), and clears
+ * the accumulator.  After a second barrier over the ranks gather[rank] holds what the all-gather of
+ * the slices would have produced and goes to cce_b200_de_peer_scatter. */
+int cce_b200_de_peer_collect_push(float* acc, int64_t acc_rows, int64_t D, void* const* gather, int32_t world,
+                                  int32_t rank, int32_t dtype, const void* status_workspace, void* stream);
 /* gathered: the ranks' slices in rank order [world][acc_rows][D]; copies row i of the reduced dE to
  * d_e[rows[i]] (rows NULL: d_e[i]); rows the list does not name are left as cce_b200_backward cleared them. */
 int cce_b200_de_peer_scatter(const void* gathered, int32_t world, int64_t acc_rows, int64_t D, int32_t dtype,

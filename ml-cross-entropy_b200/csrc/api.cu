@@ -702,6 +702,39 @@ int cce_b200_de_peer_collect(float* acc, int64_t acc_rows, int64_t D, void* slic
     return CCE_OK;
 }
 
+int cce_b200_de_peer_collect_push(float* acc, int64_t acc_rows, int64_t D, void* const* gather, int32_t world,
+                                  int32_t rank, int32_t dtype, const void* status_workspace, void* stream) {
+    if (!acc || !gather || acc_rows < 0 || D <= 0 || acc_rows % BM != 0 || world < 1 || world > kMaxPeers || rank < 0 ||
+        rank >= world)
+        return CCE_ERR_ARG;
+    PeerPtrs ptrs{};
+    for (int r = 0; r < world; ++r) {
+        if (!gather[r]) return CCE_ERR_ARG;
+        if (reinterpret_cast<uintptr_t>(gather[r]) & 15) return CCE_ERR_ALIGN;
+        ptrs.p[r] = gather[r];
+    }
+    if (reinterpret_cast<uintptr_t>(acc) & 15) return CCE_ERR_ALIGN;
+    DeviceInfo* dev = nullptr;
+    int rc = device_info(&dev);
+    if (rc != CCE_OK) return rc;
+    const long long n = acc_rows * D;  // a multiple of 128
+    if (n == 0) return CCE_OK;
+    const int* status = reinterpret_cast<const int*>(status_workspace);
+    cudaStream_t st = (cudaStream_t)stream;
+    const long long per = dtype == CCE_DT_F32 ? 4 : 8;
+    const unsigned grid = (unsigned)std::min<long long>(cdiv(n / per, 256), (long long)dev->sms * 8);
+    if (dtype == CCE_DT_F32)
+        peer_collect_push_kernel<float><<<grid, 256, 0, st>>>(acc, n, ptrs, world, rank, status);
+    else if (dtype == CCE_DT_BF16)
+        peer_collect_push_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(acc, n, ptrs, world, rank, status);
+    else if (dtype == CCE_DT_F16)
+        peer_collect_push_kernel<__half><<<grid, 256, 0, st>>>(acc, n, ptrs, world, rank, status);
+    else
+        return CCE_ERR_ARG;
+    CCE_LAUNCH_CHECK();
+    return CCE_OK;
+}
+
 int cce_b200_de_peer_scatter(const void* gathered, int32_t world, int64_t acc_rows, int64_t D, int32_t dtype,
                              const void* rows, int32_t rows_dtype, int64_t n_rows, const int64_t* n_rows_dev,
                              void* d_e, void* stream) {

@@ -637,6 +637,46 @@ __global__ void peer_collect_kernel(float* __restrict__ acc, long long n, T* __r
     }
 }
 
+// peer_collect_kernel with the exchange built in: the cast rows go straight to slot `rank` of every
+// rank's gather buffer [world][n] (mapped peer memory, 16-byte stores), so that no collective has to
+// move them afterwards.  n is a multiple of 8.
+struct PeerPtrs {
+    void* p[kMaxPeers];
+};
+template <typename T>
+__global__ void peer_collect_push_kernel(float* __restrict__ acc, long long n, PeerPtrs gath, int world, int rank,
+                                         const int* __restrict__ status) {
+    const bool bad = status && *status != 0;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    constexpr int PER = 16 / sizeof(T);  // values per 16-byte store: 8 (16-bit) or 4 (fp32)
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n / PER; i += stride) {
+        float v[PER];
+#pragma unroll
+        for (int j = 0; j < PER / 4; ++j) {
+            const float4 x = reinterpret_cast<float4*>(acc)[i * (PER / 4) + j];
+            reinterpret_cast<float4*>(acc)[i * (PER / 4) + j] = make_float4(0.f, 0.f, 0.f, 0.f);
+            v[4 * j] = x.x; v[4 * j + 1] = x.y; v[4 * j + 2] = x.z; v[4 * j + 3] = x.w;
+        }
+        if (bad) {
+#pragma unroll
+            for (int j = 0; j < PER; ++j) v[j] = __int_as_float(0x7fc00000);
+        }
+        uint4 out;
+        if constexpr (sizeof(T) == 4) {
+            out = make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]), __float_as_uint(v[2]), __float_as_uint(v[3]));
+        } else {
+            T o[PER];
+#pragma unroll
+            for (int j = 0; j < PER; ++j) o[j] = T(v[j]);
+            out = *reinterpret_cast<const uint4*>(o);
+        }
+        for (int r = 0; r < world; ++r) {
+            const int dst = (rank + 1 + r) % world;  // ranks start at different peers; the own copy goes last
+            reinterpret_cast<uint4*>(reinterpret_cast<T*>(gath.p[dst]) + (long long)rank * n)[i] = out;
+        }
+    }
+}
+
 // The gathered slices [world][acc_rows][D] back to the caller's rows: packed row i belongs to row
 // block m = i / 128, owned by rank m % world at rows (m / world) * 128 + i % 128 of its slice.
 template <typename T>

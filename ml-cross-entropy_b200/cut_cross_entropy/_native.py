@@ -44,6 +44,7 @@ EXPORTS = (
     "cce_b200_peer_buffer_destroy",
     "cce_b200_de_peer_rows",
     "cce_b200_de_peer_collect",
+    "cce_b200_de_peer_collect_push",
     "cce_b200_de_peer_scatter",
     "cce_b200_gemm",
     "cce_b200_read_status",
@@ -186,6 +187,10 @@ def lib() -> ctypes.CDLL:
     L.cce_b200_de_peer_rows.argtypes = [c_int64, c_int32]
     L.cce_b200_de_peer_collect.restype = c_int32
     L.cce_b200_de_peer_collect.argtypes = [c_void_p, c_int64, c_int64, c_void_p, c_int32, c_void_p, c_void_p]
+    L.cce_b200_de_peer_collect_push.restype = c_int32
+    L.cce_b200_de_peer_collect_push.argtypes = [
+        c_void_p, c_int64, c_int64, POINTER(c_void_p), c_int32, c_int32, c_int32, c_void_p, c_void_p,
+    ]  # fmt: skip
     L.cce_b200_de_peer_scatter.restype = c_int32
     L.cce_b200_de_peer_scatter.argtypes = [
         c_void_p, c_int32, c_int64, c_int64, c_int32, c_void_p, c_int32, c_int64, c_void_p, c_void_p, c_void_p,

@@ -180,7 +180,8 @@ def cce_backward_kernel(
     peers, acc_rows = None, 0
     if reduce_de and dev.type == "cuda" and n_rows_bound > 0:
         acc_rows = int(_native.lib().cce_b200_de_peer_rows(n_rows_bound, torch.distributed.get_world_size(pg)))
-        peers = peer_accumulators(pg, dev, acc_rows * e.size(1) * 4)
+        world = torch.distributed.get_world_size(pg)
+        peers = peer_accumulators(pg, dev, acc_rows * e.size(1) * 4, world * acc_rows * e.size(1) * e.element_size())
     de_f32 = reduce_de and peers is None
 
     de = torch.empty(e.shape, dtype=torch.float32 if de_f32 else e.dtype, device=dev) if want_de else None

@@ -7,8 +7,11 @@ NVLink/NVSwitch node this package lets the ``dE`` product do the first half of t
 each rank owns every ``world``-th block of 128 rows, holds an fp32 accumulator for the blocks it
 owns, maps the other ranks' accumulators into its own address space (CUDA inter-process memory
 handles), and the product's epilogue adds each finished tile into the owner's accumulator with
-``red.add`` (``cce_b200_backward_args.de_peer_world``).  What is left afterwards is a barrier, a
-cast of the owned rows and a 16-bit all-gather (:func:`finish_peer_reduce`).
+bulk adds (``cce_b200_backward_args.de_peer_world``).  What is left afterwards
+(:func:`finish_peer_reduce`) is a barrier, a cast of the owned rows and their exchange: either a
+16-bit all-gather of the process group, or (``CCE_B200_PEER_GATHER=1``, the default) stores of the cast
+rows straight into a gather buffer of every rank, which sits behind the accumulator in the same
+mapped allocation, followed by a second barrier.
 
 The accumulators are plain device memory and every load or store that touches a peer's memory is
 an ordinary global-memory instruction.  ``CCE_B200_PEER_REDUCE=0`` switches the path off; the
@@ -32,13 +35,18 @@ def _enabled() -> bool:
     return os.environ.get("CCE_B200_PEER_REDUCE", "1") not in ("", "0")
 
 
+def _push_gather() -> bool:
+    return os.environ.get("CCE_B200_PEER_GATHER", "1") not in ("", "0")
+
+
 @dataclass
 class PeerAccumulators:
     """The ranks' accumulators as seen from this process (``ptrs[rank]`` is this rank's own)."""
 
     world: int
     rank: int
-    nbytes: int
+    nbytes: int  # of each rank's allocation: accumulator, then gather buffer
+    acc_bytes: int  # room for the accumulator; the gather buffer starts there
     ptrs: list[int]
     token: torch.Tensor  # one element; its all-reduce is the barrier between the adds and the collect
     opened: list[int] = field(default_factory=list)
@@ -77,9 +85,11 @@ def _release(st: PeerAccumulators, pg, dev: torch.device) -> None:
     L.cce_b200_peer_buffer_destroy(st.ptrs[st.rank])
 
 
-def _create(pg, dev: torch.device, nbytes: int) -> PeerAccumulators | None:
+def _create(pg, dev: torch.device, acc_bytes: int, gather_bytes: int) -> PeerAccumulators | None:
     L = _native.lib()
     world, rank = dist.get_world_size(pg), dist.get_rank(pg)
+    acc_bytes = -(-acc_bytes // 256) * 256
+    nbytes = acc_bytes + max(gather_bytes, 256)
     own = ctypes.c_void_p()
     handle = (ctypes.c_uint8 * _native.PEER_HANDLE_BYTES)()
     with torch.cuda.device(dev):
@@ -113,26 +123,30 @@ def _create(pg, dev: torch.device, nbytes: int) -> PeerAccumulators | None:
             L.cce_b200_peer_buffer_destroy(own)
         return None
     token = torch.zeros(1, dtype=torch.float32, device=dev)
-    return PeerAccumulators(world, rank, nbytes, ptrs, token, opened)
+    return PeerAccumulators(world, rank, nbytes, acc_bytes, ptrs, token, opened)
 
 
-def peer_accumulators(pg, dev: torch.device, nbytes: int) -> PeerAccumulators | None:
-    """The group's accumulators with room for ``nbytes`` each, or ``None`` when the path is off or
-    unusable (switched off, not NCCL, more than ``MAX_PEERS`` ranks, ranks on several hosts, or the
-    buffers cannot be mapped).  Collective on first use and whenever the buffers have to grow; all
-    ranks call it with the same arguments."""
+def peer_accumulators(pg, dev: torch.device, acc_bytes: int, gather_bytes: int) -> PeerAccumulators | None:
+    """The group's buffers with room for an accumulator of ``acc_bytes`` and a gather buffer of
+    ``gather_bytes`` on each rank, or ``None`` when the path is off or unusable (switched off, not
+    NCCL, more than ``MAX_PEERS`` ranks, ranks on several hosts, or the buffers cannot be mapped).
+    Collective on first use and whenever the buffers have to grow; all ranks call it with the same
+    arguments."""
     if not _enabled() or dev.type != "cuda" or not dist.is_available() or not dist.is_initialized():
         return None
     key = _key(pg, dev)
     if key in _STATE:
         st = _STATE[key]
-        if st is None or st.nbytes >= nbytes:
+        if st is None or (st.acc_bytes >= acc_bytes and st.nbytes - st.acc_bytes >= gather_bytes):
             return st
+        acc_bytes = max(acc_bytes, st.acc_bytes)
+        gather_bytes = max(gather_bytes, st.nbytes - st.acc_bytes)
         _release(st, pg, dev)
         del _STATE[key]
     world = dist.get_world_size(pg)
-    usable = 1 < world <= _native.MAX_PEERS and dist.get_backend(pg) == "nccl" and _same_host(pg, dev)
-    _STATE[key] = _create(pg, dev, nbytes) if usable else None
+    with torch.cuda.device(dev):
+        usable = 1 < world <= _native.MAX_PEERS and dist.get_backend(pg) == "nccl" and _same_host(pg, dev)
+        _STATE[key] = _create(pg, dev, acc_bytes, gather_bytes) if usable else None
     return _STATE[key]
 
 
@@ -155,24 +169,34 @@ def finish_peer_reduce(
     status_ws: torch.Tensor,
 ) -> None:
     """Second half of the fused reduction, on the current stream: barrier over the ranks (every
-    rank's adds have landed), this rank's sums cast to ``de``'s type (the accumulator is cleared),
-    all-gather of the slices, rows copied to their places in ``de`` ``[n_total, D]``."""
+    rank's adds have landed), this rank's sums cast to ``de``'s type (the accumulator is cleared)
+    and handed to every rank, rows copied to their places in ``de`` ``[n_total, D]``.  The token's
+    value is never read: its all-reduce is the barrier."""
     L = _native.lib()
     dev = de.device
     D = de.size(1)
     dt = _native._DTYPE_CODE[de.dtype]
     sp = _native.stream_ptr(dev)
     dist.all_reduce(st.token, group=pg)
-    piece = torch.empty((acc_rows, D), dtype=de.dtype, device=dev)
+    rows_dt = _native.IDX_I64 if valids is not None and valids.dtype == torch.int64 else _native.IDX_I32
+    if _push_gather():
+        # cast rows go straight into every rank's gather buffer; a second barrier, then the local copy
+        gather = (ctypes.c_void_p * st.world)(*[p + st.acc_bytes for p in st.ptrs])
+        with torch.cuda.device(dev):
+            rc = L.cce_b200_de_peer_collect_push(st.ptrs[st.rank], acc_rows, D, gather, st.world, st.rank, dt,
+                                                 status_ws.data_ptr(), sp)  # fmt: skip
+        _native.check(rc, "cce_b200_de_peer_collect_push")
+        dist.all_reduce(st.token, group=pg)
+        gathered_ptr = st.ptrs[st.rank] + st.acc_bytes
+    else:
+        piece = torch.empty((acc_rows, D), dtype=de.dtype, device=dev)
+        with torch.cuda.device(dev):
+            rc = L.cce_b200_de_peer_collect(st.ptrs[st.rank], acc_rows, D, piece.data_ptr(), dt, status_ws.data_ptr(), sp)
+        _native.check(rc, "cce_b200_de_peer_collect")
+        gathered = torch.empty((st.world * acc_rows, D), dtype=de.dtype, device=dev)
+        dist.all_gather_into_tensor(gathered, piece, group=pg)
+        gathered_ptr = gathered.data_ptr()
     with torch.cuda.device(dev):
-        rc = L.cce_b200_de_peer_collect(st.ptrs[st.rank], acc_rows, D, piece.data_ptr(), dt, status_ws.data_ptr(), sp)
-    _native.check(rc, "cce_b200_de_peer_collect")
-    gathered = torch.empty((st.world * acc_rows, D), dtype=de.dtype, device=dev)
-    dist.all_gather_into_tensor(gathered, piece, group=pg)
-    with torch.cuda.device(dev):
-        rc = L.cce_b200_de_peer_scatter(
-            gathered.data_ptr(), st.world, acc_rows, D, dt,
-            _native._ptr(valids), _native.IDX_I64 if valids is not None and valids.dtype == torch.int64 else _native.IDX_I32,
-            n_rows, _native._ptr(n_rows_dev), de.data_ptr(), sp,
-        )  # fmt: skip
+        rc = L.cce_b200_de_peer_scatter(gathered_ptr, st.world, acc_rows, D, dt, _native._ptr(valids), rows_dt,
+                                        n_rows, _native._ptr(n_rows_dev), de.data_ptr(), sp)  # fmt: skip
     _native.check(rc, "cce_b200_de_peer_scatter")

@@ -116,6 +116,12 @@ def _worker(rank: int, world: int, init_method: str, impl: str, z_loss: bool, q)
             os.environ["CCE_B200_PEER_REDUCE"] = "1"
         scale = by_group[2].float().abs().max().item()
         assert (got[2].float() - by_group[2].float()).abs().max().item() <= 2.0 ** -7 * scale
+        os.environ["CCE_B200_PEER_GATHER"] = "0"  # second half by the process group's all-gather instead of peer stores
+        try:
+            by_gather = run(vp)
+        finally:
+            os.environ["CCE_B200_PEER_GATHER"] = "1"
+        assert (got[2].float() - by_gather[2].float()).abs().max().item() <= 2.0 ** -7 * scale
         again = run(vp)  # the accumulators were left clear: a second step gives the same sums
         assert (again[2].float() - got[2].float()).abs().max().item() <= 2.0 ** -7 * scale
         peer_reduce.release_peer_accumulators(None)
