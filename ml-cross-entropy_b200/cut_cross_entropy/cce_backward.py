@@ -30,17 +30,21 @@ def _reduce_stream(dev: torch.device) -> "torch.cuda.Stream":
     return _REDUCE_STREAMS[key]
 
 
-def _exchange_sms() -> int:
-    """SMs the last dC product leaves to the kernels that exchange dE beside it
-    (``CCE_B200_EXCHANGE_SMS``, default 0).  The product is a persistent kernel with one CTA per SM,
-    so with 0 the exchange starts when the product ends.  Measured on 8 GPUs at the Gemma-2-2B
-    head (1.36 ms per step with 0): 16 and 32 free SMs cost as much in the product as they gain in
-    overlap (1.38, 1.37 ms), 48 gain 1.5 % (1.34 ms): CTAs of the product that find their SM taken
-    start late and, with tiles dealt out in a fixed order, finish late."""
-    try:
-        return max(0, int(os.environ.get("CCE_B200_EXCHANGE_SMS", "0")))
-    except ValueError:
-        return 0
+def _exchange_sms(n_rows: int, d: int) -> int:
+    """SMs the last dC product leaves to the kernels that exchange dE beside it.  The product is a
+    persistent kernel with one CTA per SM, so with 0 the exchange starts only when the product ends.
+    ``CCE_B200_EXCHANGE_SMS`` sets the number; unset, 32 SMs are left free while the fp32 partial dE
+    is at most 128 MB and none above that.  Measured on 8 GPUs at the Gemma-2-2B head (dE 75 MB):
+    1.327 ms per step with 0, 1.271 with 32, 1.279 with 48 free SMs.  A large dE comes with a dC
+    product that is long compared with the exchange, which then loses more to the missing SMs than
+    the overlap returns (not measured: an estimate from the kernel times of the 32768 x 4096 head)."""
+    env = os.environ.get("CCE_B200_EXCHANGE_SMS")
+    if env is not None:
+        try:
+            return max(0, int(env))
+        except ValueError:
+            pass
+    return 32 if n_rows * d * 4 <= (128 << 20) else 0
 
 
 def _launch(do, dlse, e, c, bias, lse, valids, softcap, filter_eps, targets, shift, grad_scale,
@@ -65,7 +69,7 @@ def _launch(do, dlse, e, c, bias, lse, valids, softcap, filter_eps, targets, shi
         a.e_packed, a.e_packed_ld = packed_e.data_ptr(), packed_e.stride(0)
     if de_ready is not None:
         a.de_ready_event = de_ready.cuda_event
-        a.exchange_sms = _exchange_sms()
+        a.exchange_sms = _exchange_sms(a.op.n_rows, a.op.D)
     if peers is not None:
         a.de_peer_world = peers.world
         for r, ptr in enumerate(peers.ptrs):
