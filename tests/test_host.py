@@ -332,3 +332,39 @@ def test_mode_switches_of_the_python_layer():
         cce.set_vocab_ordering("alphabetical")
     k = torch.tensor([0.5, 3.0, -1.0, 2.0])
     assert cce.sort_logit_avg(k).tolist() == [1, 3, 0, 2] and cce.sort_logit_avg(k).dtype == torch.int32
+
+
+def test_host_side_of_the_fused_de_reduction(monkeypatch):
+    """Row ownership arithmetic, argument checks and switches of the cross-rank sum of dE that the
+    dE product performs (reference: the all-reduce of vocab_parallel/utils.py:68-76); no GPU."""
+    from cut_cross_entropy import _native, cce_backward
+    from cut_cross_entropy.vocab_parallel import peer_reduce
+
+    L = _native.lib()
+    # whole 128-row blocks dealt round-robin: rank r owns blocks r, r + world, ...
+    assert L.cce_b200_de_peer_rows(7782, 8) == 1024  # 61 blocks -> 8 per rank
+    assert L.cce_b200_de_peer_rows(7782, 2) == 31 * 128
+    assert L.cce_b200_de_peer_rows(128, 8) == 128 and L.cce_b200_de_peer_rows(0, 8) == 0
+    assert L.cce_b200_de_peer_rows(-1, 8) == 0 and L.cce_b200_de_peer_rows(10, 0) == 0
+    # the struct carries the accumulators of at most MAX_PEERS ranks, after the event handle
+    a = _native.BackwardArgs()
+    assert _native.BackwardArgs.de_peer_acc.offset == _native.BackwardArgs.de_peer_world.offset + 8
+    assert len(a.de_peer_acc) == _native.MAX_PEERS == 8
+    # argument checks reject before any CUDA call
+    p = ctypes.c_void_p()
+    assert L.cce_b200_peer_buffer_create(0, ctypes.byref(p), None) == -1
+    assert L.cce_b200_peer_buffer_open(None, ctypes.byref(p)) == -1
+    assert L.cce_b200_peer_buffer_close(None) == -1 and L.cce_b200_peer_buffer_destroy(None) == -1
+    assert L.cce_b200_de_peer_collect(None, 128, 64, None, _native.DT_BF16, None, None) == -1
+    assert L.cce_b200_de_peer_collect_push(None, 128, 64, None, 2, 0, _native.DT_BF16, None, None) == -1
+    assert L.cce_b200_de_peer_scatter(None, 2, 128, 64, _native.DT_BF16, None, 0, 100, None, None, None) == -1
+    # SMs left to the exchange: by size unless the environment says otherwise
+    monkeypatch.delenv("CCE_B200_EXCHANGE_SMS", raising=False)
+    assert cce_backward._exchange_sms(8192, 2304) == 32  # 75 MB of fp32 partial sums
+    assert cce_backward._exchange_sms(32768, 4096) == 0  # 537 MB
+    monkeypatch.setenv("CCE_B200_EXCHANGE_SMS", "48")
+    assert cce_backward._exchange_sms(32768, 4096) == 48
+    # no process group, or CPU tensors: the process group's reduction is used
+    assert peer_reduce.peer_accumulators(None, torch.device("cpu"), 1 << 20, 1 << 20) is None
+    monkeypatch.setenv("CCE_B200_PEER_REDUCE", "0")
+    assert not peer_reduce._enabled()
