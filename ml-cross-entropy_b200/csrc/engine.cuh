@@ -794,8 +794,6 @@ __device__ void epilogue_loop(const EngineParams& p, const EngineSmem& s, uint32
         if (MODE == MODE_GEMM && acc_is_empty && p.accumulate) {
             // nothing to add
         } else if constexpr (MODE == MODE_GEMM) {
-            // Store-only epilogue: two 32-column loads from TMEM are in flight per wait, so half of
-            // the load latency is exposed compared with one load per wait.
             if (p.peer_world > 0) {
                 // The tile goes to the accumulator of the rank that owns this row block: every thread
                 // stages 32 values of its row in shared memory and hands them to the copy engine as
@@ -826,25 +824,27 @@ __device__ void epilogue_loop(const EngineParams& p, const EngineSmem& s, uint32
                     }
                 }
             } else {
-            const int orow = (row_ok && p.row_map) ? p.row_map[row] : row;
+                // Store-only epilogue: two 32-column loads from TMEM are in flight per wait, so half
+                // of the load latency is exposed compared with one load per wait.
+                const int orow = (row_ok && p.row_map) ? p.row_map[row] : row;
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; c += 2) {
-                const int col0 = it.nblk * BN + c * 32;
-                if (col0 >= p.N) break;  // warp-uniform
-                uint32_t r0[32], r1[32];
-                if (!acc_is_empty) {
-                    tmem_ld32(taddr + c * 32, r0);
-                    tmem_ld32(taddr + c * 32 + 32, r1);
-                    tmem_ld_wait();
-                } else {
+                for (int c = 0; c < BN / 32; c += 2) {
+                    const int col0 = it.nblk * BN + c * 32;
+                    if (col0 >= p.N) break;  // warp-uniform
+                    uint32_t r0[32], r1[32];
+                    if (!acc_is_empty) {
+                        tmem_ld32(taddr + c * 32, r0);
+                        tmem_ld32(taddr + c * 32 + 32, r1);
+                        tmem_ld_wait();
+                    } else {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) r0[j] = r1[j] = 0u;
+                        for (int j = 0; j < 32; ++j) r0[j] = r1[j] = 0u;
+                    }
+                    if (row_ok) {
+                        gemm_store_chunk(p, orow, col0, r0);
+                        if (col0 + 32 < p.N) gemm_store_chunk(p, orow, col0 + 32, r1);
+                    }
                 }
-                if (row_ok) {
-                    gemm_store_chunk(p, orow, col0, r0);
-                    if (col0 + 32 < p.N) gemm_store_chunk(p, orow, col0 + 32, r1);
-                }
-            }
             }
         } else {
             uint32_t flag_bits = 0;  // MODE_PGRAD: activity of the current 64-column group
