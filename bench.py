@@ -748,9 +748,11 @@ def main() -> None:
         from cut_cross_entropy.vocab_parallel import peer_reduce
 
         fused = any(st is not None for st in peer_reduce._STATE.values())
+        second = ("peer stores of the cast rows into every rank's gather buffer, barrier" if peer_reduce._push_gather()
+                  else "16-bit all-gather")
         extras["de_exchange"] = (
             "fused: the dE product adds its tiles into the owning ranks' mapped accumulators "
-            "(cp.reduce.async.bulk over NVLink); then barrier, cast, 16-bit all-gather" if fused else
+            f"(cp.reduce.async.bulk over NVLink); then barrier, cast, {second}" if fused else
             "process group: fp32 reduce-scatter, cast, 16-bit all-gather")
         e.grad = c.grad = None
         gc.collect()
