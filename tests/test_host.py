@@ -360,10 +360,11 @@ def test_host_side_of_the_fused_de_reduction(monkeypatch):
     assert L.cce_b200_de_peer_scatter(None, 2, 128, 64, _native.DT_BF16, None, 0, 100, None, None, None) == -1
     # SMs left to the exchange: by size unless the environment says otherwise
     monkeypatch.delenv("CCE_B200_EXCHANGE_SMS", raising=False)
-    assert cce_backward._exchange_sms(8192, 2304) == 32  # 75 MB of fp32 partial sums
-    assert cce_backward._exchange_sms(32768, 4096) == 0  # 537 MB
+    assert cce_backward._exchange_sms(8192, 2304, True) == 32  # 75 MB of fp32 partial sums
+    assert cce_backward._exchange_sms(8192, 2304, False) == 0  # the process group's reduction keeps every SM busy itself
+    assert cce_backward._exchange_sms(32768, 4096, True) == 0  # 537 MB
     monkeypatch.setenv("CCE_B200_EXCHANGE_SMS", "48")
-    assert cce_backward._exchange_sms(32768, 4096) == 48
+    assert cce_backward._exchange_sms(32768, 4096, False) == 48
     # no process group, or CPU tensors: the process group's reduction is used
     assert peer_reduce.peer_accumulators(None, torch.device("cpu"), 1 << 20, 1 << 20) is None
     monkeypatch.setenv("CCE_B200_PEER_REDUCE", "0")
